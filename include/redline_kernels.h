@@ -1,0 +1,133 @@
+/*
+ * redline_kernels.h - C ABI of the B200 (sm_100a) non-GEMM decode kernels.
+ *
+ * One entry point per launcher of the reference's kernel contract
+ * (Kasamix/redline-llm, src/kernels/kernels.cuh), with that launcher's
+ * parameter list flattened to C types: FP16 tensors travel as void pointers to
+ * device memory, strides are int64 element counts, counts are int32, the stream
+ * is a cudaStream_t passed as void*. A C++ caller includes
+ * redline_llm_b200/csrc/kernels.cuh instead, which restores the reference's
+ * exact signatures in namespace redline::kernels and forwards here.
+ *
+ * Conventions (as src/kernels/kernels.cuh:12-32):
+ *   - every pointer is a device pointer; every launch is asynchronous on
+ *     `stream`; nothing synchronises internally;
+ *   - FP16 storage, FP32 accumulation in every reduction;
+ *   - one layer's KV pool slice is [num_blocks, 2 (0=K,1=V), num_kv_heads, 16,
+ *     head_dim]; block-table rows are padded with block 0 (reserved);
+ *   - zero extents return at once; odd shapes and 2-byte-aligned bases take a
+ *     scalar kernel, never an error;
+ *   - after the first call on a device (which may query device attributes and
+ *     opt in to large dynamic shared memory) a launcher issues no CUDA API call
+ *     but the launch, so it is legal inside CUDA-graph stream capture.
+ *
+ * Every function returns 0 on success, a positive cudaError_t when the launch
+ * failed, or a negative RL_E_* code when the arguments break the contract;
+ * rl_last_error() gives the text. There is no CPU fallback of any kind.
+ */
+#ifndef REDLINE_KERNELS_H_
+#define REDLINE_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RL_OK 0
+#define RL_E_NULL_POINTER (-1)
+#define RL_E_BAD_SHAPE (-2)
+#define RL_E_WORKSPACE (-3)
+#define RL_E_TOO_LARGE (-4)
+
+/* Library version string ("0.1.0"; mirrors redline.__version__, src/api/pybind.cpp:104-214). */
+const char* rl_version(void);
+
+/* Text of the last non-zero status returned on the calling thread. */
+const char* rl_last_error(void);
+
+/*
+ * Optional warm-up for `device` (-1 = current): caches the SM count, opts the
+ * attention kernel in to its dynamic shared memory and allocates the attention
+ * workspace. The launchers do the same lazily on their first call; an engine
+ * calls this (or performs one eager launch of each kernel, as the reference's
+ * bucket warm-up does, src/core/model_executor.cpp:504-521) before capture.
+ * No counterpart in the reference (its kernels keep no per-device state but
+ * RoPE's constant table, src/kernels/rope.cu:123-176).
+ */
+int rl_kernels_init(int device);
+
+/* out[t,:] = rmsnorm(input[t,:]) * weight.  Replaces LaunchRmsNorm,
+ * src/kernels/kernels.cuh:54-55 (src/kernels/rmsnorm.cu:436-450). */
+int rl_launch_rmsnorm(void* out, const void* input, const void* weight, int32_t num_tokens,
+                      int32_t hidden_size, float eps, void* stream);
+
+/* h = fp16(residual + input); residual <- h; out = fp16(fp16(h * rsqrt(mean(h^2) + eps)) * weight).
+ * out, residual and input are pairwise distinct. Replaces LaunchRmsNormResidual,
+ * src/kernels/kernels.cuh:66-68 (src/kernels/rmsnorm.cu:452-470). */
+int rl_launch_rmsnorm_residual(void* out, void* residual, const void* input, const void* weight,
+                               int32_t num_tokens, int32_t hidden_size, float eps, void* stream);
+
+/* NeoX half-rotation in place on the Q and K views. Replaces LaunchRopeInplace,
+ * src/kernels/kernels.cuh:78-81 (src/kernels/rope.cu:320-362). */
+int rl_launch_rope_inplace(void* q, void* k, int64_t q_row_stride, int64_t k_row_stride,
+                           const int32_t* positions, int32_t num_tokens, int32_t num_q_heads,
+                           int32_t num_kv_heads, int32_t head_dim, float rope_theta, void* stream);
+
+/* Bit-move of this step's K,V rows into the paged pool: p = positions[t],
+ * block = block_tables[t*block_table_row_stride + (p >> 4)], slot = p & 15.
+ * Replaces LaunchKvScatter, src/kernels/kernels.cuh:95-99 (src/kernels/kv_scatter.cu:146-176). */
+int rl_launch_kv_scatter(void* kv_pool_layer, const void* k, const void* v, int64_t k_row_stride,
+                         int64_t v_row_stride, const int32_t* block_tables,
+                         int64_t block_table_row_stride, const int32_t* positions,
+                         int32_t num_tokens, int32_t num_kv_heads, int32_t head_dim, void* stream);
+
+/*
+ * Paged grouped-query decode attention, one query token per sequence, online
+ * softmax with FP32 statistics and accumulation; rows with seq_len <= 0 are not
+ * written. head_dim must be 128 and num_q_heads == 6 * num_kv_heads (as the
+ * reference, src/kernels/paged_attention.cu:459-484,519-520). The KV axis is
+ * split across the whole grid in balanced page ranges and merged in a fixed
+ * order (the reference has no split variant; docs/DESIGN.md:884 names it as
+ * future work), so long and ragged contexts need no other entry point.
+ * Uses the per-device workspace (see rl_kernels_init).
+ * Replaces LaunchPagedAttentionDecode, src/kernels/kernels.cuh:141-146
+ * (src/kernels/paged_attention.cu:507-532).
+ */
+int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const void* q,
+                                     int64_t q_row_stride, const void* kv_pool_layer,
+                                     const int32_t* block_tables, const int32_t* seq_lens,
+                                     int32_t num_seqs, int32_t max_blocks_per_seq,
+                                     int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                     float scale, void* stream);
+
+/*
+ * Device-side health of the attention kernel on the current device: 0 when every
+ * page load it waited for arrived, 1 when a bounded wait gave up (the output of
+ * that launch is then undefined). Synchronises the device; meant for tests and
+ * post-mortems, never for the step loop. Clears the flag. No counterpart in the
+ * reference (its kernel has no asynchronous waits).
+ */
+int rl_attention_health(int* flag_out);
+
+/* Same contract, one warp per (sequence, query head), two-pass softmax on CUDA
+ * cores: a structurally independent cross-check for tests. Replaces
+ * LaunchPagedAttentionDecodeOracle, src/kernels/kernels.cuh:152-158. */
+int rl_launch_paged_attention_decode_check(void* out, int64_t out_row_stride, const void* q,
+                                           int64_t q_row_stride, const void* kv_pool_layer,
+                                           const int32_t* block_tables, const int32_t* seq_lens,
+                                           int32_t num_seqs, int32_t max_blocks_per_seq,
+                                           int32_t num_q_heads, int32_t num_kv_heads,
+                                           int32_t head_dim, float scale, void* stream);
+
+/* out[t,i] = fp16(silu(gate_up[t,i]) * gate_up[t,I+i]); out == gate_up writes in place over the
+ * gate half (row stride 2I), any other out is dense [T,I]. Replaces LaunchSiluMul,
+ * src/kernels/kernels.cuh:192-193 (src/kernels/silu_mul.cu:129-169). */
+int rl_launch_silu_mul(void* out, const void* gate_up, int32_t num_tokens,
+                       int32_t intermediate_size, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REDLINE_KERNELS_H_ */

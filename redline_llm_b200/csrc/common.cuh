@@ -1,0 +1,50 @@
+// Shared helpers of the sm_100a decode kernels: status plumbing for the C ABI,
+// per-device facts cached on first use, 128-bit access helpers.
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/redline_kernels.h"
+
+namespace rl {
+
+constexpr int kKvBlock = 16;  // tokens per KV page (src/core/types.hpp: kKvBlockSize)
+constexpr int kKvBlockShift = 4;
+
+// Records `msg` for rl_last_error() and returns `code`.
+int Fail(int code, const char* fmt, ...);
+
+// cudaGetLastError() after a launch, folded into the ABI's status convention.
+int LaunchStatus(const char* what);
+
+struct DeviceFacts {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  bool ready = false;
+};
+// Facts of the CURRENT device, queried once per device (first call happens in
+// warm-up, outside any stream capture) and a plain array read afterwards.
+const DeviceFacts& CurrentDeviceFacts();
+int CurrentDeviceIndex();
+
+inline bool Aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
+
+// 16-byte global access. .nc loads are for data this kernel never writes.
+__device__ __forceinline__ uint4 LdgStream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 Ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void Stg16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+__device__ __forceinline__ half2 AsHalf2(uint32_t u) { return *reinterpret_cast<half2*>(&u); }
+__device__ __forceinline__ uint32_t AsU32(half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+}  // namespace rl

@@ -1,0 +1,76 @@
+// KV scatter into the 16-token paged pool through block-table indirection,
+// for sm_100a. A pure bit move (NaN payloads survive): for token t,
+//   p = positions[t]; block = block_tables[t*row_stride + (p >> 4)]; slot = p & 15
+//   pool[block][0][h][slot][:] = k[t][h][:],  pool[block][1][h][slot][:] = v[t][h][:]
+// (src/kernels/kv_scatter.cu:98-137; pool index formula docs/DESIGN.md:150-155).
+// row_stride == 0 shares one table row among all tokens (prefill).
+//
+// Mapping: one warp per token; a token's K and V rows are 2*H*D/8 16-byte
+// words (64 for 2 heads x 128), dealt lane-contiguously so both the read and
+// the 256-byte pool rows are fully coalesced. A 2-byte-word variant of the
+// same body covers odd strides and unaligned bases.
+#include "common.cuh"
+
+namespace rl {
+namespace {
+
+template <typename Word>
+__global__ void __launch_bounds__(128)
+KvScatterKernel(half* __restrict__ pool, const half* __restrict__ k, const half* __restrict__ v,
+                int64_t k_row_stride, int64_t v_row_stride, const int32_t* __restrict__ tables,
+                int64_t table_row_stride, const int32_t* __restrict__ positions, int num_tokens,
+                int num_kv_heads, int head_dim) {
+  constexpr int kPer = sizeof(Word) / sizeof(half);
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= num_tokens) return;
+  const int lane = threadIdx.x & 31;
+  const int p = positions[t];
+  const int64_t block = tables[t * table_row_stride + (p >> kKvBlockShift)];
+  const int slot = p & (kKvBlock - 1);
+
+  const int words_per_head = head_dim / kPer;
+  const int words_per_side = num_kv_heads * words_per_head;
+  const Word* ksrc = reinterpret_cast<const Word*>(k + t * k_row_stride);
+  const Word* vsrc = reinterpret_cast<const Word*>(v + t * v_row_stride);
+  for (int w = lane; w < 2 * words_per_side; w += 32) {
+    const int kv = w >= words_per_side;
+    const int r = w - kv * words_per_side;
+    const int h = r / words_per_head;
+    const int dw = r - h * words_per_head;
+    const int64_t row = (((block * 2 + kv) * num_kv_heads + h) * kKvBlock + slot) *
+                        static_cast<int64_t>(head_dim);
+    reinterpret_cast<Word*>(pool + row)[dw] = (kv ? vsrc : ksrc)[r];
+  }
+}
+
+}  // namespace
+}  // namespace rl
+
+extern "C" int rl_launch_kv_scatter(void* kv_pool_layer, const void* k, const void* v,
+                                    int64_t k_row_stride, int64_t v_row_stride,
+                                    const int32_t* block_tables, int64_t block_table_row_stride,
+                                    const int32_t* positions, int32_t num_tokens,
+                                    int32_t num_kv_heads, int32_t head_dim, void* stream) {
+  using namespace rl;
+  if (num_tokens <= 0 || num_kv_heads <= 0 || head_dim <= 0) return RL_OK;
+  if (!kv_pool_layer || !k || !v || !block_tables || !positions)
+    return Fail(RL_E_NULL_POINTER, "kv_scatter: null device pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int wpb = num_tokens >= 4 * CurrentDeviceFacts().sm_count ? 4 : 1;
+  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
+  half* pool = static_cast<half*>(kv_pool_layer);
+  const half* kk = static_cast<const half*>(k);
+  const half* vv = static_cast<const half*>(v);
+  const bool vec = head_dim % 8 == 0 && k_row_stride % 8 == 0 && v_row_stride % 8 == 0 &&
+                   Aligned16(pool) && Aligned16(k) && Aligned16(v);
+  if (vec) {
+    KvScatterKernel<uint4><<<grid, block, 0, s>>>(pool, kk, vv, k_row_stride, v_row_stride,
+                                                  block_tables, block_table_row_stride, positions,
+                                                  num_tokens, num_kv_heads, head_dim);
+  } else {
+    KvScatterKernel<half><<<grid, block, 0, s>>>(pool, kk, vv, k_row_stride, v_row_stride,
+                                                 block_tables, block_table_row_stride, positions,
+                                                 num_tokens, num_kv_heads, head_dim);
+  }
+  return LaunchStatus("kv_scatter");
+}

@@ -1,0 +1,744 @@
+// Paged grouped-query decode attention for sm_100a (B200).
+//
+// Contract: src/kernels/kernels.cuh:125-146 of the reference; the math is that
+// of its decode kernel (src/kernels/paged_attention.cu:122-375): scores
+// q.k * scale, SELECT-style masking of slots past seq_len (garbage or NaN in
+// unwritten pool slots never reaches a result), online softmax with FP32
+// statistics, FP32 accumulation, one FP16 rounding of acc / l. Rows with
+// seq_len <= 0 are not written. head_dim 128, 6 query heads per KV head.
+//
+// What is different, and why (B200: 148 SMs, ~6.5 TB/s measured HBM):
+//  * The KV axis is split across the WHOLE grid. All (sequence, kv head) items
+//    are laid end to end in 16-token pages and the page range is cut into one
+//    equal contiguous share per CTA (one persistent CTA per SM). A batch of 64
+//    short sequences and a batch holding a few 32k-token sequences both load
+//    every SM equally; the reference walks one (sequence, head) per CTA serially
+//    and names the split as future work (docs/DESIGN.md:884). The launch shape
+//    depends only on the SM count, never on device-side seq_lens, so it can be
+//    frozen in a CUDA graph.
+//  * A CTA writes an item it covers completely straight to `out`. An item cut
+//    by a CTA boundary leaves (o, m, l) partials in a small per-device
+//    workspace (at most two per CTA), and a second kernel merges them in CTA
+//    order - a fixed order, so results are bit-reproducible run to run.
+//  * K/V pages are fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle) into
+//    a private 3-deep ring per warp, completion tracked by mbarriers; no warp
+//    waits on another except at item boundaries. Loads never use cluster
+//    multicast and never touch another GPU's memory.
+//  * The 6-query x 16-token dot products and the P.V products run on tensor
+//    cores (mma.sync m16n8k16, FP16 in / FP32 accumulate) in the transposed
+//    form S^T = K.Q^T, O^T = V^T.P^T so the 6 queries sit in the N=8 dimension
+//    and the 16 tokens of a page fill M=16 exactly. CUDA-core FMAs cannot keep
+//    up with the HBM stream here: 24.6k FMAs per 8 KiB page is ~48 TFLOP/s of
+//    FP32 at 8 TB/s.
+//  * The running max is only re-reduced across lanes when some lane sees a
+//    score above it (one warp vote per page otherwise); probabilities are
+//    rounded to FP16 for the P.V product, their sum is kept in FP32.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace rl {
+namespace attn {
+
+constexpr int kHeadDim = 128;
+constexpr int kGroup = 6;               // query heads per KV head
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 3;              // pages in flight per warp
+constexpr int kPageBytes = kKvBlock * kHeadDim * 2;  // 4096: one (block, kv, head) tile
+constexpr int kStageBytes = 2 * kPageBytes;          // K tile + V tile
+constexpr int kMaxSeqsPerLaunch = 1024;
+constexpr int kORowPad = 132;           // floats per query row in the merge buffer (bank spread)
+constexpr int kPartialFloats = kGroup * kHeadDim + 16;  // o[6][128], m[6], l[6], pad
+constexpr int kMaxCtas = 256;           // workspace is sized for this many CTAs
+
+// Shared-memory carve (offsets from a 1024-byte aligned base).
+constexpr int kRingOff = 0;
+constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 196608
+constexpr int kOBufOff = kRingOff + kRingBytes;
+constexpr int kOBufBytes = kWarps * kGroup * kORowPad * 4;  // 25344
+constexpr int kMlOff = kOBufOff + kOBufBytes;               // m[8][8], l[8][8]
+constexpr int kMlBytes = 2 * kWarps * 8 * 4;
+constexpr int kBarOff = kMlOff + kMlBytes;
+constexpr int kBarBytes = kWarps * kStages * 8;
+constexpr int kPrefixOff = kBarOff + kBarBytes;
+constexpr int kPrefixBytes = (kMaxSeqsPerLaunch + 8) * 4;
+constexpr int kSmemBytes = kPrefixOff + kPrefixBytes + 1024;  // + slack to align the base
+static_assert(kSmemBytes <= 227 * 1024, "attention shared memory exceeds the 227 KB per-CTA limit");
+
+// Workspace (one per device): meta ints, then kMaxCtas * 2 partial records.
+constexpr int kMetaInts = kMaxSeqsPerLaunch + 16;  // [0]=error flag, [8..] page prefix, total
+constexpr size_t kWorkspaceBytes =
+    static_cast<size_t>(kMetaInts) * 4 + static_cast<size_t>(kMaxCtas) * 2 * kPartialFloats * 4;
+
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: a load that never lands sets the error flag
+
+struct Params {
+  half* out;
+  int64_t out_stride;
+  const half* q;
+  int64_t q_stride;
+  const int32_t* tables;
+  const int32_t* seq_lens;
+  int num_seqs;
+  int max_blocks;
+  int kv_heads;
+  float scale_log2e;
+  int* meta;        // workspace meta
+  float* partials;  // workspace partial records
+};
+
+// ------------------------------------------------------------------ PTX
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void MbarInit(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, int parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the phase never completed within kWaitCycles.
+__device__ __forceinline__ bool MbarWait(uint32_t bar, int parity) {
+  if (MbarTryWait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!MbarTryWait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+// One 16-row x 64-half (2 KiB) box of the pool, 128-byte swizzled, into this CTA's shared memory.
+__device__ __forceinline__ void TmaLoadBox(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                           uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void Ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void Ldsm4T(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t MovmT(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void Mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float Exp2(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t PackHalf2(float lo, float hi) {
+  return AsU32(__floats2half2_rn(lo, hi));
+}
+
+// ------------------------------------------------------- work partition
+
+// First flattened page index of CTA c's share when `total` pages are cut into `ctas` shares.
+__host__ __device__ __forceinline__ long long ShareBegin(long long c, long long total, int ctas) {
+  return c * total / ctas;
+}
+// The CTA whose share holds flattened page t.
+__host__ __device__ __forceinline__ int ShareOf(long long t, long long total, int ctas) {
+  return static_cast<int>(((t + 1) * ctas - 1) / total);
+}
+
+// Position in the flattened page order: sequence-major, then KV head, then page.
+struct Cursor {
+  int seq;
+  int head;
+  int page;
+  int pages;  // pages of `seq`
+};
+
+__device__ __forceinline__ Cursor Locate(long long t, const int* prefix, int num_seqs, int heads) {
+  int lo = 0, hi = num_seqs - 1;
+  while (lo < hi) {  // first seq with heads * prefix[seq+1] > t (empty sequences skipped)
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<long long>(heads) * prefix[mid + 1] <= t) lo = mid + 1; else hi = mid;
+  }
+  Cursor c;
+  c.seq = lo;
+  c.pages = prefix[lo + 1] - prefix[lo];
+  const int rem = static_cast<int>(t - static_cast<long long>(heads) * prefix[lo]);
+  c.head = rem / c.pages;
+  c.page = rem - c.head * c.pages;
+  return c;
+}
+
+// Moves `c` forward by `delta` pages; the caller guarantees the target exists.
+__device__ __forceinline__ void Advance(Cursor& c, int delta, const int* prefix, int num_seqs,
+                                        int heads) {
+  c.page += delta;
+  while (c.page >= c.pages) {
+    c.page -= c.pages;
+    if (++c.head == heads) {
+      c.head = 0;
+      do {
+        ++c.seq;
+        c.pages = prefix[c.seq + 1] - prefix[c.seq];
+      } while (c.pages == 0 && c.seq < num_seqs - 1);
+    }
+  }
+}
+
+// --------------------------------------------------------------- kernel
+
+__global__ void __launch_bounds__(kThreads, 1)
+PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap pool_map) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t ring = SmemAddr(smem + kRingOff);
+  float* obuf = reinterpret_cast<float*>(smem + kOBufOff);
+  float* mbuf = reinterpret_cast<float*>(smem + kMlOff);
+  float* lbuf = mbuf + kWarps * 8;
+  const uint32_t bars = SmemAddr(smem + kBarOff);
+  int* prefix = reinterpret_cast<int*>(smem + kPrefixOff);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int heads = p.kv_heads;
+  const int num_seqs = p.num_seqs;
+
+  // ---- page prefix over sequences (every CTA computes the same table) ----
+  {
+    __shared__ int warp_tot[kWarps];
+    int n[4], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int s = tid * 4 + i;
+      int len = s < num_seqs ? p.seq_lens[s] : 0;
+      len = min(len, p.max_blocks * kKvBlock);
+      n[i] = len > 0 ? (len + kKvBlock - 1) >> kKvBlockShift : 0;
+      sum += n[i];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += warp_tot[w];
+    int run = base + incl - sum;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int s = tid * 4 + i;
+      if (s <= num_seqs) prefix[s] = run;
+      run += n[i];
+    }
+    if (tid == kThreads - 1 && num_seqs == kMaxSeqsPerLaunch) prefix[num_seqs] = run;
+    if (tid < kStages * kWarps) MbarInit(bars + tid * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+  }
+  const long long total = static_cast<long long>(heads) * prefix[num_seqs];
+  if (blockIdx.x == 0) {  // the merge kernel reads the same prefix
+    for (int s = tid; s <= num_seqs; s += kThreads) p.meta[8 + s] = prefix[s];
+  }
+  if (total == 0) return;
+  const long long share_begin = ShareBegin(blockIdx.x, total, gridDim.x);
+  const long long share_end = ShareBegin(blockIdx.x + 1, total, gridDim.x);
+  if (share_begin >= share_end) return;
+
+  // ---- this warp's pages: share_begin + warp, + kWarps, ... ----
+  const uint32_t my_ring = ring + warp * (kStages * kStageBytes);
+  const uint32_t my_bars = bars + warp * (kStages * 8);
+  long long t_issue = share_begin + warp;  // next page to fetch
+  long long t_use = t_issue;               // next page to consume
+  int n_issue = 0, n_use = 0;
+  bool failed = false;
+  Cursor ic{0, 0, 0, 1};
+  int next_block = 0;
+  if (t_issue < share_end) {
+    ic = Locate(t_issue, prefix, num_seqs, heads);
+    next_block = p.tables[static_cast<int64_t>(ic.seq) * p.max_blocks + ic.page];
+  }
+  // Issues the fetch of page t_issue (block id already in next_block), then looks up the next one.
+  auto issue_one = [&]() {
+    const int stage = n_issue % kStages;
+    if (lane == 0) {
+      const uint32_t dst = my_ring + stage * kStageBytes;
+      const uint32_t bar = my_bars + stage * 8;
+      const int row_k = ((next_block * 2 + 0) * heads + ic.head) * kKvBlock;
+      const int row_v = ((next_block * 2 + 1) * heads + ic.head) * kKvBlock;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      MbarExpectTx(bar, kStageBytes);
+      TmaLoadBox(dst, &pool_map, 0, row_k, bar);
+      TmaLoadBox(dst + 2048, &pool_map, 64, row_k, bar);
+      TmaLoadBox(dst + 4096, &pool_map, 0, row_v, bar);
+      TmaLoadBox(dst + 6144, &pool_map, 64, row_v, bar);
+    }
+    ++n_issue;
+    t_issue += kWarps;
+    if (t_issue < share_end) {
+      Advance(ic, kWarps, prefix, num_seqs, heads);
+      next_block = p.tables[static_cast<int64_t>(ic.seq) * p.max_blocks + ic.page];
+    }
+  };
+#pragma unroll 1
+  for (int i = 0; i < kStages && t_issue < share_end; ++i) issue_one();
+
+  // ldmatrix lane geometry (fixed per lane).
+  const int k_row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row for the K (A operand) loads
+  const int k_chunk_sel = lane >> 4;                      // which of the two 8-dim chunks of a k-step
+  const int v_row = (lane & 7) + (lane >> 4) * 8;         // token row for the V^T loads
+  const int v_chunk_sel = (lane >> 3) & 1;
+
+  // ---- walk the share one (sequence, head) segment at a time ----
+  long long seg_begin = share_begin;
+#pragma unroll 1
+  while (seg_begin < share_end) {
+    const Cursor sc = Locate(seg_begin, prefix, num_seqs, heads);
+    const long long item_begin = static_cast<long long>(heads) * prefix[sc.seq] +
+                                 static_cast<long long>(sc.head) * sc.pages;
+    const long long item_end = item_begin + sc.pages;
+    const long long seg_end = item_end < share_end ? item_end : share_end;
+    const int seq_len = min(p.seq_lens[sc.seq], p.max_blocks * kKvBlock);
+
+    // Q fragments of this item: B operand of S^T = K.Q^T, query g (< 6) in column g.
+    uint32_t qb[8][2];
+    {
+      const half* qrow = p.q + static_cast<int64_t>(sc.seq) * p.q_stride +
+                         (static_cast<int64_t>(sc.head) * kGroup + g) * kHeadDim + 2 * tig;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        qb[kk][0] = g < kGroup ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk) : 0u;
+        qb[kk][1] = g < kGroup ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8) : 0u;
+      }
+    }
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+#pragma unroll 1
+    while (t_use < seg_end) {
+      const int stage = n_use % kStages;
+      const int parity = (n_use / kStages) & 1;
+      const uint32_t st = my_ring + stage * kStageBytes;
+      if (!failed && !MbarWait(my_bars + stage * 8, parity)) {
+        failed = true;
+        if (lane == 0) atomicExch(p.meta, 1);
+      }
+      if (!failed) {
+        const int page = static_cast<int>(t_use - item_begin);
+        const int valid = seq_len - page * kKvBlock;  // >= 1; >= 16 for a full page
+
+        // S^T[token][query] = sum_d K[token][d] * Q[query][d]
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const int chunk = ((kk & 3) << 1) + k_chunk_sel;
+          uint32_t a[4];
+          Ldsm4(st + (kk >> 2) * 2048 + k_row * 128 + ((chunk ^ (k_row & 7)) << 4), a);
+          Mma16816(s, a, qb[kk][0], qb[kk][1]);
+        }
+        // scale into the log2 domain; SELECT masking of slots past seq_len
+        s[0] = g < valid ? s[0] * p.scale_log2e : -INFINITY;
+        s[1] = g < valid ? s[1] * p.scale_log2e : -INFINITY;
+        s[2] = g + 8 < valid ? s[2] * p.scale_log2e : -INFINITY;
+        s[3] = g + 8 < valid ? s[3] * p.scale_log2e : -INFINITY;
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+        if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+          }
+          const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+          const float a0 = Exp2(m0 - n0), a1 = Exp2(m1 - n1);  // exp2(-inf) = 0 on the first page
+          m0 = n0;
+          m1 = n1;
+          l0 *= a0;
+          l1 *= a1;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            o[i][0] *= a0;
+            o[i][1] *= a1;
+            o[i][2] *= a0;
+            o[i][3] *= a1;
+          }
+        }
+        const float p0 = Exp2(s[0] - m0), p1 = Exp2(s[1] - m1);
+        const float p2 = Exp2(s[2] - m0), p3 = Exp2(s[3] - m1);
+        l0 += p0 + p2;
+        l1 += p1 + p3;
+        // P^T as the B operand of O^T = V^T.P^T: transpose the two 8x8 [token][query] blocks.
+        const uint32_t b0 = MovmT(PackHalf2(p0, p1));
+        const uint32_t b1 = MovmT(PackHalf2(p2, p3));
+        if (valid >= kKvBlock) {
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            const int chunk = 2 * mt + v_chunk_sel;
+            uint32_t a[4];
+            Ldsm4T(st + 4096 + (chunk >> 3) * 2048 + v_row * 128 + (((chunk & 7) ^ (v_row & 7)) << 4), a);
+            Mma16816(o[mt], a, b0, b1);
+          }
+        } else {
+          // Last, partial page: V rows past seq_len may hold NaN and 0 * NaN would poison the
+          // accumulator, so those token columns of V^T are cleared in registers.
+          const uint32_t k01 = (2 * tig < valid ? 0x0000FFFFu : 0u) | (2 * tig + 1 < valid ? 0xFFFF0000u : 0u);
+          const uint32_t k23 = (2 * tig + 8 < valid ? 0x0000FFFFu : 0u) | (2 * tig + 9 < valid ? 0xFFFF0000u : 0u);
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            const int chunk = 2 * mt + v_chunk_sel;
+            uint32_t a[4];
+            Ldsm4T(st + 4096 + (chunk >> 3) * 2048 + v_row * 128 + (((chunk & 7) ^ (v_row & 7)) << 4), a);
+            a[0] &= k01;
+            a[1] &= k01;
+            a[2] &= k23;
+            a[3] &= k23;
+            Mma16816(o[mt], a, b0, b1);
+          }
+        }
+      }
+      ++n_use;
+      t_use += kWarps;
+      __syncwarp();  // every lane is done reading this stage before it is refilled
+      if (!failed && t_issue < share_end) issue_one();
+    }
+
+    // ---- merge the 8 warps' partial (o, m, l) of this segment ----
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    if (tig < 3) {
+      float* ob = obuf + warp * (kGroup * kORowPad);
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        ob[(2 * tig) * kORowPad + 16 * mt + g] = o[mt][0];
+        ob[(2 * tig + 1) * kORowPad + 16 * mt + g] = o[mt][1];
+        ob[(2 * tig) * kORowPad + 16 * mt + g + 8] = o[mt][2];
+        ob[(2 * tig + 1) * kORowPad + 16 * mt + g + 8] = o[mt][3];
+      }
+      if (g == 0) {
+        mbuf[warp * 8 + 2 * tig] = m0;
+        mbuf[warp * 8 + 2 * tig + 1] = m1;
+        lbuf[warp * 8 + 2 * tig] = l0;
+        lbuf[warp * 8 + 2 * tig + 1] = l1;
+      }
+    }
+    __syncthreads();
+    {
+      const bool whole = seg_begin == item_begin && seg_end == item_end;
+      const int d = tid & 127;
+      // slot 0: the item started in an earlier CTA; slot 1: it starts here and runs on
+      float* rec = p.partials +
+                   (static_cast<size_t>(blockIdx.x) * 2 + (item_begin < share_begin ? 0 : 1)) * kPartialFloats;
+#pragma unroll
+      for (int qi = 0; qi < 3; ++qi) {
+        const int qh = (tid >> 7) + 2 * qi;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mbuf[w * 8 + qh]);
+        float acc = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float f = Exp2(mbuf[w * 8 + qh] - mx);  // 0 for a warp that saw no page
+          acc = fmaf(f, obuf[(w * kGroup + qh) * kORowPad + d], acc);
+          den = fmaf(f, lbuf[w * 8 + qh], den);
+        }
+        if (whole) {
+          p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
+                (static_cast<int64_t>(sc.head) * kGroup + qh) * kHeadDim + d] = __float2half_rn(acc / den);
+        } else {
+          rec[qh * kHeadDim + d] = acc;
+          if (d == 0) {
+            rec[kGroup * kHeadDim + qh] = mx;
+            rec[kGroup * kHeadDim + 8 + qh] = den;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    seg_begin = seg_end;
+  }
+  // A warp that gave up on a load still owns copies in flight: give them one more bounded
+  // chance to land before the CTA's shared memory is released.
+  if (failed) {
+    for (; n_use < n_issue; ++n_use) MbarWait(my_bars + (n_use % kStages) * 8, (n_use / kStages) & 1);
+  }
+}
+
+// One block per (sequence, kv head) item that was cut by a CTA boundary: merges
+// the partial records in CTA order. Items written directly by the split kernel,
+// and padded rows, return at once.
+__global__ void __launch_bounds__(128)
+PagedAttentionMergeKernel(const Params p, int split_ctas) {
+  const int seq = blockIdx.x / p.kv_heads, head = blockIdx.x % p.kv_heads;
+  const int* prefix = p.meta + 8;
+  const int pages = prefix[seq + 1] - prefix[seq];
+  if (pages == 0) return;
+  const long long total = static_cast<long long>(p.kv_heads) * prefix[p.num_seqs];
+  const long long item_begin = static_cast<long long>(p.kv_heads) * prefix[seq] +
+                               static_cast<long long>(head) * pages;
+  const int c_first = ShareOf(item_begin, total, split_ctas);
+  const int c_last = ShareOf(item_begin + pages - 1, total, split_ctas);
+  if (c_first == c_last) return;
+  const int d = threadIdx.x;
+  for (int qh = 0; qh < kGroup; ++qh) {
+    float mx = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) {
+      if (ShareBegin(c, total, split_ctas) == ShareBegin(c + 1, total, split_ctas)) continue;  // empty share
+      const int slot = item_begin < ShareBegin(c, total, split_ctas) ? 0 : 1;
+      mx = fmaxf(mx, p.partials[(static_cast<size_t>(c) * 2 + slot) * kPartialFloats + kGroup * kHeadDim + qh]);
+    }
+    float acc = 0.0f, den = 0.0f;
+    for (int c = c_first; c <= c_last; ++c) {
+      if (ShareBegin(c, total, split_ctas) == ShareBegin(c + 1, total, split_ctas)) continue;
+      const int slot = item_begin < ShareBegin(c, total, split_ctas) ? 0 : 1;
+      const float* rec = p.partials + (static_cast<size_t>(c) * 2 + slot) * kPartialFloats;
+      const float f = Exp2(rec[kGroup * kHeadDim + qh] - mx);
+      acc = fmaf(f, rec[qh * kHeadDim + d], acc);
+      den = fmaf(f, rec[kGroup * kHeadDim + 8 + qh], den);
+    }
+    p.out[static_cast<int64_t>(seq) * p.out_stride + (static_cast<int64_t>(head) * kGroup + qh) * kHeadDim + d] =
+        __float2half_rn(acc / den);
+  }
+}
+
+// Cross-check kernel for tests: one warp per (sequence, query head), textbook
+// two-pass softmax on CUDA cores straight from global memory.
+__global__ void __launch_bounds__(32)
+PagedAttentionCheckKernel(half* out, int64_t out_stride, const half* q, int64_t q_stride,
+                          const half* pool, const int32_t* tables, const int32_t* seq_lens,
+                          int max_blocks, int kv_heads, int group, float scale) {
+  const int seq = blockIdx.x, qh = blockIdx.y, lane = threadIdx.x;
+  const int len = min(seq_lens[seq], max_blocks * kKvBlock);
+  if (len <= 0) return;
+  const int kvh = qh / group;
+  const int32_t* row = tables + static_cast<int64_t>(seq) * max_blocks;
+  float qv[4];
+  for (int i = 0; i < 4; ++i) qv[i] = __half2float(q[seq * q_stride + qh * kHeadDim + lane * 4 + i]);
+  auto tile = [&](int t, int kv) {
+    const int64_t b = row[t >> kKvBlockShift];
+    return pool + ((((b * 2 + kv) * kv_heads + kvh) * kKvBlock) + (t & (kKvBlock - 1))) * kHeadDim;
+  };
+  auto score = [&](int t) {
+    const half* kr = tile(t, 0);
+    float dot = 0.0f;
+    for (int i = 0; i < 4; ++i) dot = fmaf(qv[i], __half2float(kr[lane * 4 + i]), dot);
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    return dot * scale;
+  };
+  float mx = -INFINITY;
+  for (int t = 0; t < len; ++t) mx = fmaxf(mx, score(t));
+  float den = 0.0f, acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int t = 0; t < len; ++t) {
+    const float w = expf(score(t) - mx);
+    den += w;
+    const half* vr = tile(t, 1);
+    for (int i = 0; i < 4; ++i) acc[i] = fmaf(w, __half2float(vr[lane * 4 + i]), acc[i]);
+  }
+  for (int i = 0; i < 4; ++i)
+    out[seq * out_stride + qh * kHeadDim + lane * 4 + i] = __float2half_rn(acc[i] / den);
+}
+
+// ----------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  void* workspace = nullptr;
+  int ctas = 0;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_state[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mutex;
+
+// First call per device: driver entry point, shared-memory opt-in, workspace.
+int EnsureReady(DeviceState** out_state) {
+  const int dev = CurrentDeviceIndex();
+  DeviceState& st = g_state[dev];
+  *out_state = &st;
+  if (st.ready) return RL_OK;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (st.ready) return RL_OK;
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return Fail(e != cudaSuccess ? static_cast<int>(e) : RL_E_WORKSPACE,
+                  "paged_attention: cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const DeviceFacts& facts = CurrentDeviceFacts();
+  if (facts.max_smem_optin < kSmemBytes)
+    return Fail(RL_E_WORKSPACE, "paged_attention: device offers %d B of shared memory per block, %d needed",
+                facts.max_smem_optin, kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(PagedAttentionSplitKernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention: shared-memory opt-in: %s", cudaGetErrorString(e));
+  e = cudaMalloc(&st.workspace, kWorkspaceBytes);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention: workspace: %s", cudaGetErrorString(e));
+  e = cudaMemset(st.workspace, 0, kWorkspaceBytes);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention: workspace clear: %s", cudaGetErrorString(e));
+  st.ctas = facts.sm_count < kMaxCtas ? facts.sm_count : kMaxCtas;
+  st.ready = true;
+  return RL_OK;
+}
+
+// The pool slice as a 2-D tensor of 256-byte rows (one token row of one head);
+// boxes are 16 rows x 64 halves, 128-byte swizzled. The row count is not part
+// of the launch contract, so the map claims the largest extent a 180 GB device
+// can hold; only rows of real pages are ever requested.
+int EncodePoolMap(const void* pool, CUtensorMap* map) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kHeadDim), 1ull << 30};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kHeadDim) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kKvBlock)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(pool), dims,
+                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_attention: tensor map encode failed (CUresult %d)", static_cast<int>(r));
+  return RL_OK;
+}
+
+int CheckContract(const char* fn, const void* out, int64_t out_stride, const void* q,
+                  int64_t q_stride, const void* pool, const void* tables, const void* lens,
+                  int max_blocks, int q_heads, int kv_heads, int head_dim) {
+  if (!out || !q || !pool || !tables || !lens) return Fail(RL_E_NULL_POINTER, "%s: null device pointer", fn);
+  if (head_dim != kHeadDim) return Fail(RL_E_BAD_SHAPE, "%s: head_dim must be 128", fn);
+  if (kv_heads < 1 || q_heads < kv_heads || q_heads % kv_heads != 0)
+    return Fail(RL_E_BAD_SHAPE, "%s: num_q_heads must be a positive multiple of num_kv_heads", fn);
+  if (max_blocks < 1) return Fail(RL_E_BAD_SHAPE, "%s: max_blocks_per_seq must be >= 1", fn);
+  const int64_t width = static_cast<int64_t>(q_heads) * head_dim;
+  if (q_stride < width || out_stride < width) return Fail(RL_E_BAD_SHAPE, "%s: row stride smaller than the row", fn);
+  return RL_OK;
+}
+
+}  // namespace attn
+}  // namespace rl
+
+extern "C" int rl_kernels_init(int device) {
+  if (device >= 0) {
+    const cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return rl::Fail(static_cast<int>(e), "rl_kernels_init: %s", cudaGetErrorString(e));
+  }
+  rl::CurrentDeviceFacts();
+  rl::attn::DeviceState* st;
+  return rl::attn::EnsureReady(&st);
+}
+
+extern "C" int rl_attention_health(int* flag_out) {
+  using namespace rl;
+  using namespace rl::attn;
+  if (!flag_out) return Fail(RL_E_NULL_POINTER, "rl_attention_health: null pointer");
+  *flag_out = 0;
+  DeviceState& st = g_state[CurrentDeviceIndex()];
+  if (!st.ready) return RL_OK;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(flag_out, st.workspace, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && *flag_out != 0) e = cudaMemset(st.workspace, 0, sizeof(int));
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "rl_attention_health: %s", cudaGetErrorString(e));
+  return RL_OK;
+}
+
+extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const void* q,
+                                                int64_t q_row_stride, const void* kv_pool_layer,
+                                                const int32_t* block_tables, const int32_t* seq_lens,
+                                                int32_t num_seqs, int32_t max_blocks_per_seq,
+                                                int32_t num_q_heads, int32_t num_kv_heads,
+                                                int32_t head_dim, float scale, void* stream) {
+  using namespace rl;
+  using namespace rl::attn;
+  if (num_seqs <= 0) return RL_OK;
+  int rc = CheckContract("paged_attention_decode", out, out_row_stride, q, q_row_stride, kv_pool_layer,
+                         block_tables, seq_lens, max_blocks_per_seq, num_q_heads, num_kv_heads, head_dim);
+  if (rc != RL_OK) return rc;
+  if (num_q_heads != num_kv_heads * kGroup)
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: needs 6 query heads per KV head");
+  if ((q_row_stride & 1) || (reinterpret_cast<uintptr_t>(q) & 3))
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: q rows must be 4-byte aligned");
+  if (!Aligned16(kv_pool_layer))
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: the pool slice must be 16-byte aligned");
+  DeviceState* st;
+  if ((rc = EnsureReady(&st)) != RL_OK) return rc;
+  CUtensorMap map;
+  if ((rc = EncodePoolMap(kv_pool_layer, &map)) != RL_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int first = 0; first < num_seqs; first += kMaxSeqsPerLaunch) {
+    const int n = num_seqs - first < kMaxSeqsPerLaunch ? num_seqs - first : kMaxSeqsPerLaunch;
+    Params p;
+    p.out = static_cast<half*>(out) + static_cast<int64_t>(first) * out_row_stride;
+    p.out_stride = out_row_stride;
+    p.q = static_cast<const half*>(q) + static_cast<int64_t>(first) * q_row_stride;
+    p.q_stride = q_row_stride;
+    p.tables = block_tables + static_cast<int64_t>(first) * max_blocks_per_seq;
+    p.seq_lens = seq_lens + first;
+    p.num_seqs = n;
+    p.max_blocks = max_blocks_per_seq;
+    p.kv_heads = num_kv_heads;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.meta = static_cast<int*>(st->workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
+    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, map);
+    PagedAttentionMergeKernel<<<n * num_kv_heads, 128, 0, s>>>(p, st->ctas);
+  }
+  return LaunchStatus("paged_attention_decode");
+}
+
+extern "C" int rl_launch_paged_attention_decode_check(void* out, int64_t out_row_stride, const void* q,
+                                                      int64_t q_row_stride, const void* kv_pool_layer,
+                                                      const int32_t* block_tables, const int32_t* seq_lens,
+                                                      int32_t num_seqs, int32_t max_blocks_per_seq,
+                                                      int32_t num_q_heads, int32_t num_kv_heads,
+                                                      int32_t head_dim, float scale, void* stream) {
+  using namespace rl;
+  using namespace rl::attn;
+  if (num_seqs <= 0) return RL_OK;
+  const int rc = CheckContract("paged_attention_decode_check", out, out_row_stride, q, q_row_stride,
+                               kv_pool_layer, block_tables, seq_lens, max_blocks_per_seq, num_q_heads,
+                               num_kv_heads, head_dim);
+  if (rc != RL_OK) return rc;
+  PagedAttentionCheckKernel<<<dim3(num_seqs, num_q_heads), 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<half*>(out), out_row_stride, static_cast<const half*>(q), q_row_stride,
+      static_cast<const half*>(kv_pool_layer), block_tables, seq_lens, max_blocks_per_seq, num_kv_heads,
+      num_q_heads / num_kv_heads, scale);
+  return LaunchStatus("paged_attention_decode_check");
+}

@@ -1,0 +1,171 @@
+// RMSNorm and fused residual-add + RMSNorm for sm_100a.
+//
+// Contract and rounding points follow the reference launchers
+// (src/kernels/rmsnorm.cu:436-470 and the kernels at :159-254):
+//   h   = fp16(residual + input)          rounding point 1 (a native half add)
+//   residual <- h
+//   ms  = mean(f32(h)^2), FP32             over the ROUNDED h
+//   out = fp16( fp16(f32(h) * rsqrtf(ms + eps)) * weight )   rounding point 2 before the weight
+//
+// Mapping: one warp owns one row and keeps it in registers as packed halves
+// between the two passes (16-byte loads, row read once, written once); the
+// sum of squares is reduced with one xor-shuffle tree, so there is no shared
+// memory and no block barrier. Rows are independent: identical inputs give
+// identical bits at every batch size. A scalar block-per-row kernel covers odd
+// widths and 2-byte-aligned bases.
+#include "common.cuh"
+
+#if defined(__USE_FAST_MATH__)
+#error "the norm's rounding contract needs the precise math path"
+#endif
+
+namespace rl {
+namespace {
+
+constexpr int kMaxChunksPerLane = 8;  // 8 chunks x 8 halves x 32 lanes = 2048 columns
+
+template <int CPL, bool kResidual>
+__global__ void __launch_bounds__(256)
+RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const half* __restrict__ input,
+                  const half* __restrict__ weight, int num_tokens, int hidden, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (row >= num_tokens) return;
+  const int lane = threadIdx.x & 31;
+  const int chunks = hidden >> 3;
+  const size_t base = static_cast<size_t>(row) * hidden;
+
+  uint4 hv[CPL];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) {
+    const int c = i * 32 + lane;
+    if (c < chunks) {
+      uint4 x = LdgStream16(input + base + c * 8);
+      if (kResidual) {
+        const uint4 r = Ldg16(residual + base + c * 8);
+        x.x = AsU32(__hadd2_rn(AsHalf2(r.x), AsHalf2(x.x)));
+        x.y = AsU32(__hadd2_rn(AsHalf2(r.y), AsHalf2(x.y)));
+        x.z = AsU32(__hadd2_rn(AsHalf2(r.z), AsHalf2(x.z)));
+        x.w = AsU32(__hadd2_rn(AsHalf2(r.w), AsHalf2(x.w)));
+        Stg16(residual + base + c * 8, x);
+      }
+      hv[i] = x;
+      const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(AsHalf2(words[j]));
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) {
+    const int c = i * 32 + lane;
+    if (c < chunks) {
+      const uint4 w = Ldg16(weight + c * 8);
+      const uint32_t hw[4] = {hv[i].x, hv[i].y, hv[i].z, hv[i].w};
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(AsHalf2(hw[j]));
+        const half2 normed = __floats2half2_rn(f.x * inv, f.y * inv);
+        // fp16 x fp16 is exact in FP32, so one half multiply == fp16(f32(n) * f32(w)).
+        o[j] = AsU32(__hmul2_rn(normed, AsHalf2(ww[j])));
+      }
+      Stg16(out + base + c * 8, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+}
+
+// Any width, any 2-byte alignment: one block per row, two passes over global
+// memory (the second re-reads what the same thread wrote).
+template <bool kResidual>
+__global__ void __launch_bounds__(256)
+RmsNormScalarKernel(half* out, half* residual, const half* input, const half* weight, int hidden,
+                    float eps) {
+  __shared__ float warp_sums[8];
+  __shared__ float total_s;
+  const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    half h = input[base + c];
+    if (kResidual) {
+      h = __hadd_rn(residual[base + c], h);
+      residual[base + c] = h;
+    }
+    const float f = __half2float(h);
+    ss = fmaf(f, f, ss);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t += warp_sums[w];
+    total_s = t;
+  }
+  __syncthreads();
+  const float inv = rsqrtf(total_s / static_cast<float>(hidden) + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const half h = kResidual ? residual[base + c] : input[base + c];
+    const half normed = __float2half_rn(__half2float(h) * inv);
+    out[base + c] = __hmul_rn(normed, weight[c]);
+  }
+}
+
+template <bool kResidual>
+int Launch(half* out, half* residual, const half* input, const half* weight, int num_tokens,
+           int hidden, float eps, cudaStream_t stream) {
+  if (num_tokens <= 0 || hidden <= 0) return RL_OK;
+  if (!out || !input || !weight || (kResidual && !residual))
+    return Fail(RL_E_NULL_POINTER, "rmsnorm: null device pointer");
+  const bool vec = (hidden % 8 == 0) && (hidden / 8 <= 32 * kMaxChunksPerLane) && Aligned16(out) &&
+                   Aligned16(input) && Aligned16(weight) && (!kResidual || Aligned16(residual));
+  if (!vec) {
+    RmsNormScalarKernel<kResidual><<<num_tokens, 256, 0, stream>>>(out, residual, input, weight,
+                                                                   hidden, eps);
+    return LaunchStatus("rmsnorm (scalar)");
+  }
+  // Few rows: one warp per block so the rows spread over the SMs; many rows: 8 per block.
+  const int sms = CurrentDeviceFacts().sm_count;
+  const int wpb = num_tokens >= 8 * sms ? 8 : (num_tokens >= 2 * sms ? 2 : 1);
+  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
+  const int cpl = (hidden / 8 + 31) / 32;
+#define RL_NORM_CASE(N)                                                                          \
+  case N:                                                                                        \
+    RmsNormWarpKernel<N, kResidual><<<grid, block, 0, stream>>>(out, residual, input, weight,    \
+                                                                num_tokens, hidden, eps);        \
+    break;
+  switch (cpl) {
+    RL_NORM_CASE(1) RL_NORM_CASE(2) RL_NORM_CASE(3) RL_NORM_CASE(4) RL_NORM_CASE(5)
+    RL_NORM_CASE(6) RL_NORM_CASE(7) RL_NORM_CASE(8)
+  }
+#undef RL_NORM_CASE
+  return LaunchStatus("rmsnorm");
+}
+
+}  // namespace
+}  // namespace rl
+
+extern "C" int rl_launch_rmsnorm(void* out, const void* input, const void* weight,
+                                 int32_t num_tokens, int32_t hidden_size, float eps, void* stream) {
+  return rl::Launch<false>(static_cast<half*>(out), nullptr, static_cast<const half*>(input),
+                           static_cast<const half*>(weight), num_tokens, hidden_size, eps,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rl_launch_rmsnorm_residual(void* out, void* residual, const void* input,
+                                          const void* weight, int32_t num_tokens,
+                                          int32_t hidden_size, float eps, void* stream) {
+  return rl::Launch<true>(static_cast<half*>(out), static_cast<half*>(residual),
+                          static_cast<const half*>(input), static_cast<const half*>(weight),
+                          num_tokens, hidden_size, eps, static_cast<cudaStream_t>(stream));
+}

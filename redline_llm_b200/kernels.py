@@ -1,0 +1,132 @@
+"""Host-side mirror of the reference's kernel launch contract over the C ABI.
+
+Function names, argument order and meaning follow
+Kasamix/redline-llm src/kernels/kernels.cuh (LaunchRmsNorm ... LaunchSiluMul);
+tensors are torch CUDA tensors (FP16 data as float16 or as int16/uint16 bit
+patterns) used only as device memory. Every call goes to libredline_b200.so;
+there is no other implementation behind these names, so a missing library or a
+non-zero status raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libredline_b200.so")
+_lib = None
+
+ABI_SYMBOLS = (
+    "rl_version", "rl_last_error", "rl_kernels_init", "rl_launch_rmsnorm",
+    "rl_launch_rmsnorm_residual", "rl_launch_rope_inplace", "rl_launch_kv_scatter",
+    "rl_launch_paged_attention_decode", "rl_launch_paged_attention_decode_check",
+    "rl_launch_silu_mul", "rl_attention_health",
+)
+
+
+class KernelError(RuntimeError):
+    """A launcher returned a non-zero status (mirrors the RuntimeError the reference's
+    Python binding raises for component errors, src/api/pybind.cpp:15-20)."""
+
+
+def lib() -> C.CDLL:
+    """Loads the CUDA library; raises if it was never built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise KernelError(f"{_LIB_PATH} is missing: run `python -m redline_llm_b200.build` "
+                              "(nvcc, sm_100a); there is no CPU or PyTorch fallback")
+        L = C.CDLL(_LIB_PATH)
+        vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+        L.rl_version.restype = C.c_char_p
+        L.rl_last_error.restype = C.c_char_p
+        L.rl_kernels_init.argtypes = [C.c_int]
+        L.rl_launch_rmsnorm.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+        L.rl_launch_rmsnorm_residual.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
+        L.rl_launch_rope_inplace.argtypes = [vp, vp, i64, i64, vp, i32, i32, i32, i32, f32, vp]
+        L.rl_launch_kv_scatter.argtypes = [vp, vp, vp, i64, i64, vp, i64, vp, i32, i32, i32, vp]
+        att = [vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]
+        L.rl_launch_paged_attention_decode.argtypes = att
+        L.rl_launch_paged_attention_decode_check.argtypes = att
+        L.rl_launch_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+        L.rl_attention_health.argtypes = [C.POINTER(C.c_int)]
+        for name in ABI_SYMBOLS[2:]:
+            getattr(L, name).restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: status {status}: {lib().rl_last_error().decode()}")
+
+
+def _ptr(t, offset_elems: int = 0) -> int:
+    return t.data_ptr() + 2 * offset_elems if t is not None else 0
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+def version() -> str:
+    return lib().rl_version().decode()
+
+
+def init(device: int = -1) -> None:
+    _check(lib().rl_kernels_init(device), "rl_kernels_init")
+
+
+def launch_rms_norm(out, input, weight, num_tokens, hidden_size, eps, stream=None):
+    _check(lib().rl_launch_rmsnorm(_ptr(out), _ptr(input), _ptr(weight), num_tokens, hidden_size,
+                                   eps, _stream(stream)), "LaunchRmsNorm")
+
+
+def launch_rms_norm_residual(out, residual, input, weight, num_tokens, hidden_size, eps, stream=None):
+    _check(lib().rl_launch_rmsnorm_residual(_ptr(out), _ptr(residual), _ptr(input), _ptr(weight),
+                                            num_tokens, hidden_size, eps, _stream(stream)),
+           "LaunchRmsNormResidual")
+
+
+def launch_rope_inplace(q, k, q_row_stride, k_row_stride, positions, num_tokens, num_q_heads,
+                        num_kv_heads, head_dim, rope_theta, stream=None, q_offset=0, k_offset=0):
+    """q/k may be the same buffer with element offsets (q = qkv+0, k = qkv+1536)."""
+    _check(lib().rl_launch_rope_inplace(_ptr(q, q_offset), _ptr(k, k_offset), q_row_stride,
+                                        k_row_stride, positions.data_ptr(), num_tokens,
+                                        num_q_heads, num_kv_heads, head_dim, rope_theta,
+                                        _stream(stream)), "LaunchRopeInplace")
+
+
+def launch_kv_scatter(kv_pool_layer, k, v, k_row_stride, v_row_stride, block_tables,
+                      block_table_row_stride, positions, num_tokens, num_kv_heads, head_dim,
+                      stream=None, k_offset=0, v_offset=0):
+    _check(lib().rl_launch_kv_scatter(_ptr(kv_pool_layer), _ptr(k, k_offset), _ptr(v, v_offset),
+                                      k_row_stride, v_row_stride, block_tables.data_ptr(),
+                                      block_table_row_stride, positions.data_ptr(), num_tokens,
+                                      num_kv_heads, head_dim, _stream(stream)), "LaunchKvScatter")
+
+
+def launch_paged_attention_decode(out, out_row_stride, q, q_row_stride, kv_pool_layer, block_tables,
+                                  seq_lens, num_seqs, max_blocks_per_seq, num_q_heads, num_kv_heads,
+                                  head_dim, scale, stream=None, check_kernel=False, q_offset=0):
+    fn = (lib().rl_launch_paged_attention_decode_check if check_kernel
+          else lib().rl_launch_paged_attention_decode)
+    _check(fn(_ptr(out), out_row_stride, _ptr(q, q_offset), q_row_stride, _ptr(kv_pool_layer),
+              block_tables.data_ptr(), seq_lens.data_ptr(), num_seqs, max_blocks_per_seq,
+              num_q_heads, num_kv_heads, head_dim, scale, _stream(stream)),
+           "LaunchPagedAttentionDecode")
+
+
+def attention_health() -> int:
+    """0 if every page load of the attention kernel arrived since the last query (synchronises)."""
+    flag = C.c_int(0)
+    _check(lib().rl_attention_health(C.byref(flag)), "rl_attention_health")
+    return flag.value
+
+
+def launch_silu_mul(out, gate_up, num_tokens, intermediate_size, stream=None):
+    _check(lib().rl_launch_silu_mul(_ptr(out), _ptr(gate_up), num_tokens, intermediate_size,
+                                    _stream(stream)), "LaunchSiluMul")

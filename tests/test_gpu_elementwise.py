@@ -1,0 +1,315 @@
+"""GPU parity of the norm / RoPE / scatter / SiLU kernels, called through the C ABI.
+
+Cases mirror the reference's kernel suite (tests/test_kernels.cu: row sweeps, both stride
+modes, the RMSNorm half-ULP boundary fixture with mutants, the HF RoPE capture, full-pool
+scatter mirrors, in-place SiLU) with the tighter gates this build is held to: bit moves
+exact; norm / RoPE / SiLU within 1 FP16 ulp of FP32-order compute."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import oracle  # noqa: E402
+from redline_llm_b200 import kernels as K  # noqa: E402
+from redline_llm_b200 import workloads as wl  # noqa: E402
+from tests.gpu_util import assert_within_one_ulp, dev, host, is_nan_bits, ulp_of  # noqa: E402
+
+EPS = 1e-6
+ROWS = [1, 3, 8, 15, 16, 17, 63, 64, 65, 257]  # tests/test_kernels.cu:452
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    K.init()
+
+
+# ------------------------------------------------------------------ RMSNorm
+
+@pytest.mark.parametrize("rows", ROWS)
+def test_rmsnorm_row_sweep(own, rows):
+    x = own.uniform_half(0x51C + rows, rows * 1536, -1.0, 1.0).reshape(rows, 1536)
+    w = own.uniform_half(0x71C, 1536, 0.5, 1.5)
+    d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
+    K.launch_rms_norm(d_out, dev(x), dev(w), rows, 1536, EPS)
+    got = host(d_out)
+    assert_within_one_ulp(got, own.rmsnorm(x, w, EPS), "rmsnorm vs FP64", min_exact=0.995)
+    assert_within_one_ulp(got, own.rmsnorm_f32(None, x, w, EPS)[0], "rmsnorm vs FP32 order", min_exact=0.995)
+
+
+@pytest.mark.parametrize("rows", ROWS)
+def test_rmsnorm_residual_row_sweep(own, rows):
+    x = own.uniform_half(0x52C + rows, rows * 1536, -1.0, 1.0).reshape(rows, 1536)
+    r = own.uniform_half(0x62C + rows, rows * 1536, -1.0, 1.0).reshape(rows, 1536)
+    w = own.uniform_half(0x72C, 1536, 0.5, 1.5)
+    d_res, d_x = dev(r), dev(x)
+    d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
+    K.launch_rms_norm_residual(d_out, d_res, d_x, dev(w), rows, 1536, EPS)
+    exp_out, exp_res, _, _ = own.rmsnorm_residual(r, x, w, EPS)
+    assert np.array_equal(host(d_res), exp_res), "residual write-back must be bit-exact"
+    assert np.array_equal(host(d_x), x), "input must not be written"
+    assert_within_one_ulp(host(d_out), exp_out, "fused rmsnorm vs FP64", min_exact=0.995)
+
+
+@pytest.mark.parametrize("hidden", [1, 2, 7, 8, 24, 250, 1535, 1544, 2048, 2056, 4100])
+def test_rmsnorm_odd_widths_and_unaligned_bases(own, hidden):
+    rows = 5
+    x = own.uniform_half(0x900 + hidden, rows * hidden, -2.0, 2.0).reshape(rows, hidden)
+    r = own.uniform_half(0xA00 + hidden, rows * hidden, -2.0, 2.0).reshape(rows, hidden)
+    w = own.uniform_half(0xB00 + hidden, hidden, 0.5, 1.5)
+    exp_out, exp_res, _, _ = own.rmsnorm_residual(r, x, w, EPS)
+    for shift in (0, 1):  # shift 1: every base is only 2-byte aligned -> scalar kernel
+        pad = lambda a: dev(np.concatenate([np.zeros(shift, np.uint16), a.reshape(-1), np.full(8, 0x7E00, np.uint16)]))
+        d_x, d_r, d_w = pad(x), pad(r), pad(w)
+        d_out = torch.full((shift + rows * hidden + 8,), 0x1234, dtype=torch.int16, device="cuda")
+        L = K.lib()
+        st = L.rl_launch_rmsnorm_residual(d_out.data_ptr() + 2 * shift, d_r.data_ptr() + 2 * shift,
+                                          d_x.data_ptr() + 2 * shift, d_w.data_ptr() + 2 * shift,
+                                          rows, hidden, EPS, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        out = host(d_out)
+        assert_within_one_ulp(out[shift:shift + rows * hidden].reshape(rows, hidden), exp_out, f"H={hidden} shift={shift}")
+        assert np.array_equal(host(d_r)[shift:shift + rows * hidden].reshape(rows, hidden), exp_res)
+        assert (out[:shift] == 0x1234).all() and (out[shift + rows * hidden:] == 0x1234).all(), "guard band written"
+
+
+def test_rmsnorm_zero_row_stays_finite(own):
+    x = np.zeros((2, 1536), np.uint16)
+    w = own.uniform_half(1, 1536, 0.5, 1.5)
+    d_out = torch.full((2, 1536), 0x7E00, dtype=torch.int16, device="cuda")
+    K.launch_rms_norm(d_out, dev(x), dev(w), 2, 1536, EPS)
+    assert (host(d_out) == 0).all()  # eps inside the rsqrt keeps 0 * rsqrt(eps) = 0
+
+
+def test_rmsnorm_boundary_fixture_rounding_order(own):
+    """tests/test_kernels.cu:602-660: residual bit-exact everywhere, output bit-exact on every
+    column whose pre-rounding value is not within 1e-5 (relative) of an FP16 midpoint."""
+    res, inp, w, isb = own.boundary_fixture(1)
+    exp_out, exp_res, _, exc = own.rmsnorm_residual(res, inp, w, EPS, rel_floor=1e-5)
+    d_res = dev(res)
+    d_out = torch.zeros(8, 1536, dtype=torch.int16, device="cuda")
+    K.launch_rms_norm_residual(d_out, d_res, dev(inp), dev(w), 8, 1536, EPS)
+    got = host(d_out)
+    assert np.array_equal(host(d_res), exp_res)
+    keep = exc == 0
+    assert np.array_equal(got[keep], exp_out[keep])
+    assert oracle.ulp_distance(got, exp_out).max() <= 1
+    # and the kernel is told apart from both wrong operation orders
+    for which in ("unrounded", "single"):
+        m = own.rmsnorm_mutant(which, res, inp, w, EPS)
+        assert ((got != m) & keep).sum(axis=1).min() >= 16
+
+
+def test_rmsnorm_deterministic_and_batch_invariant(own):
+    c = wl.config_rmsnorm(64)
+    outs = []
+    for rows in (64, 64, 5):
+        d_res = dev(c["residual"][:rows])
+        d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
+        K.launch_rms_norm_residual(d_out, d_res, dev(c["x"][:rows]), dev(c["weight"]), rows, 1536, EPS)
+        outs.append(host(d_out))
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[0][:5], outs[2])
+
+
+def test_rmsnorm_config1_shape_and_large_T(own):
+    for rows in (64, 4096):
+        c = wl.config_rmsnorm(rows)
+        d_res = dev(c["residual"])
+        d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
+        K.launch_rms_norm_residual(d_out, d_res, dev(c["x"]), dev(c["weight"]), rows, 1536, EPS)
+        exp_out, exp_res, _, _ = own.rmsnorm_residual(c["residual"], c["x"], c["weight"], EPS)
+        assert np.array_equal(host(d_res), exp_res)
+        assert_within_one_ulp(host(d_out), exp_out, f"config 1 T={rows}", min_exact=0.995)
+
+
+# --------------------------------------------------------------------- RoPE
+
+def run_rope(q_in, k_in, positions, theta, strided, q_heads=12, kv_heads=2, hd=128):
+    t = len(positions)
+    qw, kw = q_heads * hd, kv_heads * hd
+    d_pos = dev(np.asarray(positions, np.int32))
+    if not strided:
+        d_q, d_k = dev(q_in), dev(k_in)
+        K.launch_rope_inplace(d_q, d_k, qw, kw, d_pos, t, q_heads, kv_heads, hd, theta)
+        return host(d_q).reshape(t, qw), host(d_k).reshape(t, kw)
+    stride = 2048
+    image = wl.uniform_half(0x517AB1E, t * stride, -1.0, 1.0).reshape(t, stride)
+    image[:, :qw] = q_in
+    image[:, qw:qw + kw] = k_in
+    before = image.copy()
+    d_img = dev(image)
+    K.launch_rope_inplace(d_img, d_img, stride, stride, d_pos, t, q_heads, kv_heads, hd, theta, k_offset=qw)
+    after = host(d_img).reshape(t, stride)
+    assert np.array_equal(after[:, qw + kw:], before[:, qw + kw:]), "V region / tail must not be touched"
+    return after[:, :qw], after[:, qw:qw + kw]
+
+
+def rope_gate(got, ref_bits, x_in, what):
+    """<= 1 FP16 ulp, the ulp taken at the larger magnitude of the rotated pair (the two product
+    terms can cancel, so an ulp of a term may be many ulps of a small result)."""
+    hd2 = 64
+    g = oracle.half_bits_to_f64(got).reshape(-1, 2, hd2)
+    r = oracle.half_bits_to_f64(ref_bits).reshape(-1, 2, hd2)
+    x = np.abs(oracle.half_bits_to_f64(x_in).reshape(-1, 2, hd2))
+    scale = ulp_of(np.maximum(x[:, :1, :], x[:, 1:, :]))
+    assert (np.abs(g - r) <= scale + 1e-12).all(), what
+    return float((got == ref_bits).mean())
+
+
+@pytest.mark.parametrize("strided", [False, True])
+def test_rope_matches_hf_capture(golden, strided):
+    _, cap = golden
+    q, k = run_rope(cap["q_in"], cap["k_in"], cap["positions"], float(cap["theta"]), strided)
+    eq = rope_gate(q, cap["q_out"], cap["q_in"], "q vs HF capture")
+    ek = rope_gate(k, cap["k_out"], cap["k_in"], "k vs HF capture")
+    assert eq > 0.999 and ek > 0.999, (eq, ek)
+
+
+@pytest.mark.parametrize("theta", [1e6, 1e4, 5e5])
+@pytest.mark.parametrize("strided", [False, True])
+def test_rope_vs_fp32_order_oracle(own, theta, strided):
+    t = 64
+    c = wl.config_rope_scatter(tokens=t)
+    q_in = np.ascontiguousarray(c["qkv"][:, :1536])
+    k_in = np.ascontiguousarray(c["qkv"][:, 1536:1792])
+    pos = c["positions"]
+    q, k = run_rope(q_in, k_in, pos, theta, strided)
+    exact = []
+    for got, x, heads in ((q, q_in, 12), (k, k_in, 2)):
+        exact.append(rope_gate(got, own.rope(x, pos, heads, 128, theta, f32=True), x, "vs FP32 order"))
+        err = np.abs(oracle.half_bits_to_f64(got) - oracle.half_bits_to_f64(own.rope(x, pos, heads, 128, theta)))
+        assert err.max() <= 1e-2 and err.mean() <= 1e-3  # the reference's own gate vs FP64
+    assert min(exact) > 0.999, exact
+
+
+def test_rope_position_zero_is_identity_and_long_positions(own):
+    q_in = wl.uniform_half(7, 4 * 1536, -4.0, 4.0).reshape(4, 1536)
+    k_in = wl.uniform_half(8, 4 * 256, -4.0, 4.0).reshape(4, 256)
+    q, k = run_rope(q_in, k_in, [0, 0, 0, 0], 1e6, False)
+    assert np.array_equal(q, q_in) and np.array_equal(k, k_in)
+    pos = [32767, 33023, 100000, 1]
+    q, k = run_rope(q_in, k_in, pos, 1e6, True)
+    rope_gate(q, own.rope(q_in, pos, 12, 128, 1e6, f32=True), q_in, "long positions")
+
+
+def test_rope_odd_head_dim_takes_scalar_path(own):
+    t, qh, kh, hd = 3, 3, 1, 20
+    q_in = wl.uniform_half(17, t * qh * hd, -1.0, 1.0).reshape(t, qh * hd)
+    k_in = wl.uniform_half(18, t * kh * hd, -1.0, 1.0).reshape(t, kh * hd)
+    pos = np.array([5, 77, 4000], np.int32)
+    d_q, d_k = dev(q_in), dev(k_in)
+    K.launch_rope_inplace(d_q, d_k, qh * hd, kh * hd, dev(pos), t, qh, kh, hd, 1e4)
+    d = oracle.ulp_distance(host(d_q).reshape(t, -1), own.rope(q_in, pos, qh, hd, 1e4, f32=True))
+    assert (d <= 1).mean() > 0.99
+
+
+# --------------------------------------------------------------- KV scatter
+
+def scatter_case(own, tokens, positions, tables, table_stride, k, v, ks, vs, num_blocks, k_off=0, v_off=0, shift=0):
+    n = num_blocks * 2 * 2 * 16 * 128
+    nan = np.array([0x7E00, 0x7C01, 0x7FFF, 0xFE00, 0xFFFF, 0xFDAB], np.uint16)
+    mirror = nan[np.arange(n) % 6].copy()
+    pool_img = np.concatenate([np.full(shift, 0x1111, np.uint16), mirror, np.full(8, 0x2222, np.uint16)])
+    d_pool = dev(pool_img)
+    d_k, d_v = dev(k), dev(v)
+    L = K.lib()
+    st = L.rl_launch_kv_scatter(d_pool.data_ptr() + 2 * shift, d_k.data_ptr() + 2 * k_off,
+                                d_v.data_ptr() + 2 * v_off, ks, vs, dev(tables).data_ptr(), table_stride,
+                                dev(positions).data_ptr(), tokens, 2, 128,
+                                torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    kk = k.reshape(-1)[k_off:]
+    vv = v.reshape(-1)[v_off:]
+    own.kv_scatter(mirror, np.ascontiguousarray(kk), np.ascontiguousarray(vv), ks, vs, tables, table_stride,
+                   positions, 2, 128)
+    got = host(d_pool)
+    assert np.array_equal(got[shift:shift + n], mirror), "pool differs from the CPU mirror (stray or missing writes)"
+    assert (got[:shift] == 0x1111).all() and (got[shift + n:] == 0x2222).all()
+
+
+def test_scatter_decode_mode_config2_strided_and_packed(own):
+    c = wl.config_rope_scatter(tokens=64, num_blocks=8192)
+    qkv = c["qkv"]
+    scatter_case(own, 64, c["positions"], c["tables"], c["tables"].shape[1], qkv, qkv, 2048, 2048, 8192,
+                 k_off=1536, v_off=1792)
+    k = np.ascontiguousarray(qkv[:, 1536:1792])
+    v = np.ascontiguousarray(qkv[:, 1792:2048])
+    scatter_case(own, 64, c["positions"], c["tables"], c["tables"].shape[1], k, v, 256, 256, 8192)
+
+
+def test_scatter_prefill_mode_shares_one_row(own):
+    tokens = 257
+    k = wl.uniform_half(31, tokens * 256, -1.0, 1.0).reshape(tokens, 256)
+    v = wl.uniform_half(32, tokens * 256, -1.0, 1.0).reshape(tokens, 256)
+    row = (wl.permutation(33, 40)[:17] + 1).astype(np.int32).reshape(1, 17)
+    scatter_case(own, tokens, np.arange(tokens, dtype=np.int32), row, 0, k, v, 256, 256, 48)
+
+
+def test_scatter_padded_row_lands_in_block_zero_and_boundaries(own):
+    pos = np.array([0, 15, 16, 17, 31, 32, 0], np.int32)  # last row = padded slot (position 0, dummy table)
+    tables = np.array([[3, 4, 5]] * 6 + [[0, 0, 0]], np.int32)
+    tables[1:6, :] = [[6, 7, 8], [9, 10, 11], [12, 13, 14], [15, 16, 17], [18, 19, 20]]
+    k = wl.uniform_half(41, 7 * 256, -1.0, 1.0).reshape(7, 256)
+    v = wl.uniform_half(42, 7 * 256, -1.0, 1.0).reshape(7, 256)
+    scatter_case(own, 7, pos, tables, 3, k, v, 256, 256, 24)
+
+
+def test_scatter_odd_strides_and_unaligned_bases(own):
+    tokens = 9
+    k = wl.uniform_half(51, tokens * 263 + 4, -1.0, 1.0)
+    v = wl.uniform_half(52, tokens * 259 + 4, -1.0, 1.0)
+    pos = wl.randint(53, tokens, 0, 63)
+    tables = (wl.permutation(54, 60)[:tokens * 4] + 1).astype(np.int32).reshape(tokens, 4)
+    scatter_case(own, tokens, pos, tables, 4, k, v, 263, 259, 64, k_off=1, v_off=3)
+    scatter_case(own, tokens, pos, tables, 4, k, v, 263, 259, 64, k_off=1, v_off=3, shift=1)
+
+
+# ----------------------------------------------------------------- SiLU*mul
+
+@pytest.mark.parametrize("tokens", [1, 3, 64, 512])
+def test_silu_separate_and_in_place(own, tokens):
+    gu = wl.config_silu(tokens)["gate_up"]
+    exp64 = own.silu_mul(gu)
+    exp32 = own.silu_mul(gu, f32=True)
+    d_gu = dev(gu)
+    d_out = torch.zeros(tokens, 8960, dtype=torch.int16, device="cuda")
+    K.launch_silu_mul(d_out, d_gu, tokens, 8960)
+    got = host(d_out)
+    assert np.array_equal(host(d_gu), gu), "separate mode must not write gate_up"
+    assert_within_one_ulp(got, exp64, "silu vs FP64", min_exact=0.999)
+    assert_within_one_ulp(got, exp32, "silu vs FP32 order", min_exact=0.9995)
+    K.launch_silu_mul(d_gu, d_gu, tokens, 8960)  # aliased: in place over the gate half
+    after = host(d_gu)
+    assert np.array_equal(after[:, :8960], got), "in-place result differs from the separate one"
+    assert np.array_equal(after[:, 8960:], gu[:, 8960:]), "up half must stay untouched"
+
+
+@pytest.mark.parametrize("inter", [1, 7, 8, 250, 8961])
+def test_silu_odd_sizes_take_scalar_path(own, inter):
+    rows = 4
+    gu = wl.uniform_half(0x5111 + inter, rows * 2 * inter, -3.0, 3.0).reshape(rows, 2 * inter)
+    d_out = torch.full((rows * inter + 8,), 0x1234, dtype=torch.int16, device="cuda")
+    K.launch_silu_mul(d_out, dev(gu), rows, inter)
+    got = host(d_out)
+    assert_within_one_ulp(got[:rows * inter].reshape(rows, inter), own.silu_mul(gu), f"I={inter}")
+    assert (got[rows * inter:] == 0x1234).all()
+
+
+def test_silu_extremes_and_config4_largest(own):
+    # saturating gates: silu(+big) = big, silu(-big) = -0 / tiny, NaN propagates
+    vals = np.array([0x7BFF, 0xFBFF, 0x4D00, 0xCD00, 0x0001, 0x8001, 0x0000, 0x8000], np.uint16)
+    gu = np.concatenate([vals, np.full(8, 0x3C00, np.uint16)]).reshape(1, 16)
+    d_out = torch.zeros(1, 8, dtype=torch.int16, device="cuda")
+    K.launch_silu_mul(d_out, dev(gu), 1, 8)
+    assert_within_one_ulp(host(d_out), own.silu_mul(gu), "extremes")
+    # T = 4096 (220 MB of traffic): every row against the CPU checker
+    gu = wl.config_silu(4096)["gate_up"]
+    d_gu = dev(gu)
+    K.launch_silu_mul(d_gu, d_gu, 4096, 8960)
+    got = host(d_gu)
+    assert np.array_equal(got[:, 8960:], gu[:, 8960:])
+    assert_within_one_ulp(got[:, :8960], own.silu_mul(gu, f32=True), "config 4 T=4096", min_exact=0.9995)
