@@ -354,3 +354,30 @@ def ulp_distance(a_bits: np.ndarray, b_bits: np.ndarray) -> np.ndarray:
     d = np.abs(ka - kb)
     both_nan = ((a & 0x7FFF) > 0x7C00) & ((b & 0x7FFF) > 0x7C00)
     return np.where(both_nan, 0, d)
+
+
+def _step(bits: np.ndarray, delta: int) -> np.ndarray:
+    """The FP16 pattern `delta` lattice steps away (sign-magnitude order, clamped at +-max finite)."""
+    a = np.asarray(bits, np.uint16).astype(np.int32)
+    k = np.where(a & 0x8000, -(a & 0x7FFF), a & 0x7FFF) + delta
+    k = np.clip(k, -0x7BFF, 0x7BFF)
+    return np.where(k < 0, (-k) | 0x8000, k).astype(np.uint16)
+
+
+def rmsnorm_gate(got_bits, h_bits, inv_rms, w_bits):
+    """Gate for a two-rounding op: the kernel's intermediate fp16(h * inv_rms) may sit one FP16 step
+    from the FP64 one when the unrounded value is next to a rounding midpoint (FP32 vs FP64 inv_rms);
+    given that intermediate, the weight product must be exact. Returns (ok mask, exact mask)."""
+    h = half_bits_to_f64(h_bits)
+    w = half_bits_to_f64(w_bits)
+    with np.errstate(over="ignore"):
+        n0 = (h * np.asarray(inv_rms)[:, None]).astype(np.float16).view(np.uint16)
+        ok = np.zeros(n0.shape, bool)
+        exact = None
+        for delta in (0, -1, 1):
+            cand = (half_bits_to_f64(_step(n0, delta)) * w[None, :]).astype(np.float16).view(np.uint16)
+            hit = cand == np.asarray(got_bits, np.uint16)
+            ok |= hit
+            if delta == 0:
+                exact = hit
+    return ok, exact

@@ -15,6 +15,18 @@ from redline_llm_b200 import kernels as K  # noqa: E402
 from redline_llm_b200 import workloads as wl  # noqa: E402
 from tests.gpu_util import assert_within_one_ulp, dev, host, is_nan_bits, ulp_of  # noqa: E402
 
+
+def norm_gate(own, got, residual, x, w, what, min_exact=0.995):
+    """<= 1 FP16 step at the norm's second rounding point, exact weight product after it."""
+    if residual is None:
+        h = x
+        inv = 1.0 / np.sqrt((oracle.half_bits_to_f64(x) ** 2).mean(axis=1) + EPS)
+    else:
+        _, h, inv, _ = own.rmsnorm_residual(residual, x, w, EPS)
+    ok, exact = oracle.rmsnorm_gate(got, h, inv, w)
+    assert ok.all(), f"{what}: {int((~ok).sum())} elements outside the one-step gate"
+    assert exact.mean() >= min_exact, f"{what}: only {exact.mean():.5f} bit-exact vs FP64"
+
 EPS = 1e-6
 ROWS = [1, 3, 8, 15, 16, 17, 63, 64, 65, 257]  # tests/test_kernels.cu:452
 
@@ -35,8 +47,8 @@ def test_rmsnorm_row_sweep(own, rows):
     d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
     K.launch_rms_norm(d_out, dev(x), dev(w), rows, 1536, EPS)
     got = host(d_out)
-    assert_within_one_ulp(got, own.rmsnorm(x, w, EPS), "rmsnorm vs FP64", min_exact=0.995)
-    assert_within_one_ulp(got, own.rmsnorm_f32(None, x, w, EPS)[0], "rmsnorm vs FP32 order", min_exact=0.995)
+    norm_gate(own, got, None, x, w, "rmsnorm vs FP64")
+    assert (got == own.rmsnorm_f32(None, x, w, EPS)[0]).mean() > 0.999, "rmsnorm vs FP32 order"
 
 
 @pytest.mark.parametrize("rows", ROWS)
@@ -50,7 +62,7 @@ def test_rmsnorm_residual_row_sweep(own, rows):
     exp_out, exp_res, _, _ = own.rmsnorm_residual(r, x, w, EPS)
     assert np.array_equal(host(d_res), exp_res), "residual write-back must be bit-exact"
     assert np.array_equal(host(d_x), x), "input must not be written"
-    assert_within_one_ulp(host(d_out), exp_out, "fused rmsnorm vs FP64", min_exact=0.995)
+    norm_gate(own, host(d_out), r, x, w, "fused rmsnorm vs FP64")
 
 
 @pytest.mark.parametrize("hidden", [1, 2, 7, 8, 24, 250, 1535, 1544, 2048, 2056, 4100])
@@ -70,7 +82,7 @@ def test_rmsnorm_odd_widths_and_unaligned_bases(own, hidden):
                                           rows, hidden, EPS, torch.cuda.current_stream().cuda_stream)
         assert st == 0
         out = host(d_out)
-        assert_within_one_ulp(out[shift:shift + rows * hidden].reshape(rows, hidden), exp_out, f"H={hidden} shift={shift}")
+        norm_gate(own, out[shift:shift + rows * hidden].reshape(rows, hidden), r, x, w, f"H={hidden} shift={shift}", 0.98)
         assert np.array_equal(host(d_r)[shift:shift + rows * hidden].reshape(rows, hidden), exp_res)
         assert (out[:shift] == 0x1234).all() and (out[shift + rows * hidden:] == 0x1234).all(), "guard band written"
 
@@ -95,7 +107,7 @@ def test_rmsnorm_boundary_fixture_rounding_order(own):
     assert np.array_equal(host(d_res), exp_res)
     keep = exc == 0
     assert np.array_equal(got[keep], exp_out[keep])
-    assert oracle.ulp_distance(got, exp_out).max() <= 1
+    norm_gate(own, got, res, inp, w, "boundary fixture", 0.9)
     # and the kernel is told apart from both wrong operation orders
     for which in ("unrounded", "single"):
         m = own.rmsnorm_mutant(which, res, inp, w, EPS)
@@ -122,7 +134,7 @@ def test_rmsnorm_config1_shape_and_large_T(own):
         K.launch_rms_norm_residual(d_out, d_res, dev(c["x"]), dev(c["weight"]), rows, 1536, EPS)
         exp_out, exp_res, _, _ = own.rmsnorm_residual(c["residual"], c["x"], c["weight"], EPS)
         assert np.array_equal(host(d_res), exp_res)
-        assert_within_one_ulp(host(d_out), exp_out, f"config 1 T={rows}", min_exact=0.995)
+        norm_gate(own, host(d_out), c["residual"], c["x"], c["weight"], f"config 1 T={rows}")
 
 
 # --------------------------------------------------------------------- RoPE
@@ -215,10 +227,11 @@ def scatter_case(own, tokens, positions, tables, table_stride, k, v, ks, vs, num
     pool_img = np.concatenate([np.full(shift, 0x1111, np.uint16), mirror, np.full(8, 0x2222, np.uint16)])
     d_pool = dev(pool_img)
     d_k, d_v = dev(k), dev(v)
+    d_tables, d_positions = dev(tables), dev(positions)  # keep the device buffers alive across the launch
     L = K.lib()
     st = L.rl_launch_kv_scatter(d_pool.data_ptr() + 2 * shift, d_k.data_ptr() + 2 * k_off,
-                                d_v.data_ptr() + 2 * v_off, ks, vs, dev(tables).data_ptr(), table_stride,
-                                dev(positions).data_ptr(), tokens, 2, 128,
+                                d_v.data_ptr() + 2 * v_off, ks, vs, d_tables.data_ptr(), table_stride,
+                                d_positions.data_ptr(), tokens, 2, 128,
                                 torch.cuda.current_stream().cuda_stream)
     assert st == 0
     torch.cuda.synchronize()
