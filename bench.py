@@ -44,7 +44,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -55,7 +55,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._pump, daemon=True)
             self.t.start()
@@ -133,17 +133,17 @@ class AttentionWorkload:
     random-permuted block table; one step = one attention call per layer pool (28)."""
     name = "paged_attention_b64_ctx1024-1280"
 
-    def __init__(self, rank: int):
+    def __init__(self, rank: int, layers: int = LAYERS):
         import torch
         from redline_llm_b200 import kernels as K
-        self.K, self.torch = K, torch
+        self.K, self.torch, self.layers = K, torch, layers
         c = wl.config_attention(seed=wl.SEED_ATTN + 16 * rank)
         self.c = c
         self.bytes_per_launch = wl.attention_bytes(c["seq_lens"])
         self.tokens = int(np.asarray(c["seq_lens"]).sum())
         base = dev(c["pool"])
         # 28 layer pools: the same page structure, contents rotated so no two layers alias in L2
-        self.pools = [base] + [torch.roll(base, 4096 * (i + 1)) for i in range(LAYERS - 1)]
+        self.pools = [base] + [torch.roll(base, 4096 * (i + 1)) for i in range(layers - 1)]
         # live slots must stay NaN-free after the roll: refill every pool's NaN slots is unnecessary for
         # timing, but results are checked on pool 0 only (unrolled).
         self.q = dev(np.pad(c["q"], ((0, 0), (0, 512))))  # rows 2048 apart, as in the fused QKV buffer
@@ -157,7 +157,7 @@ class AttentionWorkload:
         self.h_out = torch.empty(64, 1536, dtype=torch.int16).pin_memory()
         self.h2d = self.h_q.numel() * 2 + self.h_tables.numel() * 4 + self.h_lens.numel() * 4
         self.d2h = self.h_out.numel() * 2
-        self.launches_per_step = 2 * LAYERS  # split kernel + merge kernel per call
+        self.launches_per_step = layers  # one kernel per attention call
         K.init()
 
     def attend(self, pool):
@@ -177,7 +177,7 @@ class AttentionWorkload:
         self.torch.cuda.current_stream().synchronize()
 
     def bytes_per_step(self):
-        return self.bytes_per_launch * LAYERS
+        return self.bytes_per_launch * self.layers
 
     def check(self):
         """Pool 0's result against the CPU checker on 4 sequences (cheap sanity, not the parity suite)."""
@@ -306,6 +306,7 @@ def main():
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of CUDA-graph replay")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layer pools walked per step (28 = the model)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -331,7 +332,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    w = AttentionWorkload(rank)
+    w = AttentionWorkload(rank, args.layers)
     max_abs = w.check()
     peak, peak_kind = measured_peaks()
 
@@ -359,17 +360,17 @@ def main():
         total_bytes = w.bytes_per_step() * world
         value = total_bytes * args.steps / (ms * 1e-3) / 1e9
         e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
-        per_launch_s = ms * 1e-3 / (args.steps * LAYERS)
+        per_launch_s = ms * 1e-3 / (args.steps * args.layers)
         achieved = w.bytes_per_launch / per_launch_s / 1e9
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": w.name, "batch_per_gpu": 64, "layers_per_step": LAYERS,
+            "config": {"workload": w.name, "batch_per_gpu": 64, "layers_per_step": args.layers,
                        "kv_tokens_per_layer": w.tokens, "cold_l2": "28 layer pools (2.1 GB) walked per step, larger than L2",
                        "launch": "eager" if args.no_graph else "cuda_graph_replay",
                        "pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
-            "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel+PagedAttentionMergeKernel",
+            "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "peak_kind": f"of {peak_kind}", "traffic": None,
                          "algorithmic_bytes_per_launch": w.bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 3)},

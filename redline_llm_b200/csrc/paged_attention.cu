@@ -18,8 +18,10 @@
 //    frozen in a CUDA graph.
 //  * A CTA writes an item it covers completely straight to `out`. An item cut
 //    by a CTA boundary leaves (o, m, l) partials in a small per-device
-//    workspace (at most two per CTA), and a second kernel merges them in CTA
-//    order - a fixed order, so results are bit-reproducible run to run.
+//    workspace (at most two per CTA); each contributor takes a ticket from an
+//    atomic counter and the LAST one to arrive merges all partials of the item
+//    in CTA order. Nobody waits for anybody, and the merge order is fixed, so
+//    results are bit-reproducible run to run whoever arrives last.
 //  * K/V pages are fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle) into
 //    a private 3-deep ring per warp, completion tracked by mbarriers; no warp
 //    waits on another except at item boundaries. Loads never use cluster
@@ -69,7 +71,8 @@ constexpr int kSmemBytes = kPrefixOff + kPrefixBytes + 1024;  // + slack to alig
 static_assert(kSmemBytes <= 227 * 1024, "attention shared memory exceeds the 227 KB per-CTA limit");
 
 // Workspace (one per device): meta ints, then kMaxCtas * 2 partial records.
-constexpr int kMetaInts = kMaxSeqsPerLaunch + 16;  // [0]=error flag, [8..] page prefix, total
+constexpr int kTicketOff = 16;                     // meta[0] = error flag, meta[16 + c] = tickets of
+constexpr int kMetaInts = kTicketOff + kMaxCtas;   // the item that starts in CTA c and runs on
 constexpr size_t kWorkspaceBytes =
     static_cast<size_t>(kMetaInts) * 4 + static_cast<size_t>(kMaxCtas) * 2 * kPartialFloats * 4;
 
@@ -227,6 +230,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   const uint32_t bars = SmemAddr(smem + kBarOff);
   int* prefix = reinterpret_cast<int*>(smem + kPrefixOff);
 
+  __shared__ bool merge_here;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tig = lane & 3;
   const int heads = p.kv_heads;
@@ -268,9 +272,6 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
     __syncthreads();
   }
   const long long total = static_cast<long long>(heads) * prefix[num_seqs];
-  if (blockIdx.x == 0) {  // the merge kernel reads the same prefix
-    for (int s = tid; s <= num_seqs; s += kThreads) p.meta[8 + s] = prefix[s];
-  }
   if (total == 0) return;
   const long long share_begin = ShareBegin(blockIdx.x, total, gridDim.x);
   const long long share_end = ShareBegin(blockIdx.x + 1, total, gridDim.x);
@@ -487,6 +488,45 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
           }
         }
       }
+      if (!whole) {  // uniform over the CTA
+        // Publish the record, take a ticket; the last contributor of the item merges.
+        const int ctas = gridDim.x;
+        const int c_first = item_begin < share_begin ? ShareOf(item_begin, total, ctas) : blockIdx.x;
+        const int c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
+        const bool sparse = total < ctas;  // then every non-empty share is exactly one page
+        const int contributors = sparse ? sc.pages : c_last - c_first + 1;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+          const int ticket = atomicAdd(p.meta + kTicketOff + c_first, 1);
+          merge_here = ticket == contributors - 1;
+          if (merge_here) p.meta[kTicketOff + c_first] = 0;  // everyone has arrived: re-arm
+        }
+        __syncthreads();
+        if (merge_here) {
+          __threadfence();
+#pragma unroll 1
+          for (int qi = 0; qi < 3; ++qi) {
+            const int qh = (tid >> 7) + 2 * qi;
+            float mx = -INFINITY;
+            for (int c = c_first; c <= c_last; ++c) {
+              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+              mx = fmaxf(mx, __ldcg(r + kGroup * kHeadDim + qh));
+            }
+            float acc = 0.0f, den = 0.0f;
+            for (int c = c_first; c <= c_last; ++c) {
+              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+              const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx);
+              acc = fmaf(f, __ldcg(r + qh * kHeadDim + d), acc);
+              den = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), den);
+            }
+            p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
+                  (static_cast<int64_t>(sc.head) * kGroup + qh) * kHeadDim + d] = __float2half_rn(acc / den);
+          }
+        }
+      }
     }
     __syncthreads();
     seg_begin = seg_end;
@@ -495,43 +535,6 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   // chance to land before the CTA's shared memory is released.
   if (failed) {
     for (; n_use < n_issue; ++n_use) MbarWait(my_bars + (n_use % kStages) * 8, (n_use / kStages) & 1);
-  }
-}
-
-// One block per (sequence, kv head) item that was cut by a CTA boundary: merges
-// the partial records in CTA order. Items written directly by the split kernel,
-// and padded rows, return at once.
-__global__ void __launch_bounds__(128)
-PagedAttentionMergeKernel(const Params p, int split_ctas) {
-  const int seq = blockIdx.x / p.kv_heads, head = blockIdx.x % p.kv_heads;
-  const int* prefix = p.meta + 8;
-  const int pages = prefix[seq + 1] - prefix[seq];
-  if (pages == 0) return;
-  const long long total = static_cast<long long>(p.kv_heads) * prefix[p.num_seqs];
-  const long long item_begin = static_cast<long long>(p.kv_heads) * prefix[seq] +
-                               static_cast<long long>(head) * pages;
-  const int c_first = ShareOf(item_begin, total, split_ctas);
-  const int c_last = ShareOf(item_begin + pages - 1, total, split_ctas);
-  if (c_first == c_last) return;
-  const int d = threadIdx.x;
-  for (int qh = 0; qh < kGroup; ++qh) {
-    float mx = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (ShareBegin(c, total, split_ctas) == ShareBegin(c + 1, total, split_ctas)) continue;  // empty share
-      const int slot = item_begin < ShareBegin(c, total, split_ctas) ? 0 : 1;
-      mx = fmaxf(mx, p.partials[(static_cast<size_t>(c) * 2 + slot) * kPartialFloats + kGroup * kHeadDim + qh]);
-    }
-    float acc = 0.0f, den = 0.0f;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (ShareBegin(c, total, split_ctas) == ShareBegin(c + 1, total, split_ctas)) continue;
-      const int slot = item_begin < ShareBegin(c, total, split_ctas) ? 0 : 1;
-      const float* rec = p.partials + (static_cast<size_t>(c) * 2 + slot) * kPartialFloats;
-      const float f = Exp2(rec[kGroup * kHeadDim + qh] - mx);
-      acc = fmaf(f, rec[qh * kHeadDim + d], acc);
-      den = fmaf(f, rec[kGroup * kHeadDim + 8 + qh], den);
-    }
-    p.out[static_cast<int64_t>(seq) * p.out_stride + (static_cast<int64_t>(head) * kGroup + qh) * kHeadDim + d] =
-        __float2half_rn(acc / den);
   }
 }
 
@@ -718,7 +721,6 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     p.meta = static_cast<int*>(st->workspace);
     p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
     PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, map);
-    PagedAttentionMergeKernel<<<n * num_kv_heads, 128, 0, s>>>(p, st->ctas);
   }
   return LaunchStatus("paged_attention_decode");
 }
