@@ -37,6 +37,7 @@
 //    rounded to FP16 for the P.V product, their sum is kept in FP32.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -91,6 +92,8 @@ struct Params {
   float scale_log2e;
   int* meta;        // workspace meta
   float* partials;  // workspace partial records
+  const half* pool; // the layer's pool slice (1-D bulk-copy experiment path)
+  unsigned long long* timeline;  // diagnostics build only
 };
 
 // ------------------------------------------------------------------ PTX
@@ -134,6 +137,30 @@ __device__ __forceinline__ void TmaLoadBox(uint32_t dst, const CUtensorMap* map,
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void TmaLoadBox4(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %2, %2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(0), "r"(tile), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, int bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+#ifdef RL_ATTN_TIMELINE
+__device__ __forceinline__ unsigned long long GlobalTimerNs() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define RL_STAMP(slot) \
+  if (p.timeline && lane == 0) p.timeline[(blockIdx.x * kWarps + warp) * 8 + (slot)] = GlobalTimerNs()
+#else
+#define RL_STAMP(slot)
+#endif
 __device__ __forceinline__ void Ldsm4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -200,26 +227,11 @@ __device__ __forceinline__ Cursor Locate(long long t, const int* prefix, int num
   return c;
 }
 
-// Moves `c` forward by `delta` pages; the caller guarantees the target exists.
-__device__ __forceinline__ void Advance(Cursor& c, int delta, const int* prefix, int num_seqs,
-                                        int heads) {
-  c.page += delta;
-  while (c.page >= c.pages) {
-    c.page -= c.pages;
-    if (++c.head == heads) {
-      c.head = 0;
-      do {
-        ++c.seq;
-        c.pages = prefix[c.seq + 1] - prefix[c.seq];
-      } while (c.pages == 0 && c.seq < num_seqs - 1);
-    }
-  }
-}
-
 // --------------------------------------------------------------- kernel
 
 __global__ void __launch_bounds__(kThreads, 1)
-PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap pool_map) {
+PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap pool_map,
+                          const __grid_constant__ CUtensorMap tile_map, const int tma_mode) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -235,6 +247,10 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   const int g = lane >> 2, tig = lane & 3;
   const int heads = p.kv_heads;
   const int num_seqs = p.num_seqs;
+  RL_STAMP(0);
+  if (tid == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tma_mode == 0 ? &pool_map : &tile_map) : "memory");
+  }
 
   // ---- page prefix over sequences (every CTA computes the same table) ----
   {
@@ -277,49 +293,78 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   const long long share_end = ShareBegin(blockIdx.x + 1, total, gridDim.x);
   if (share_begin >= share_end) return;
 
-  // ---- this warp's pages: share_begin + warp, + kWarps, ... ----
+  // ---- this warp's pages: share-relative indices warp, warp + kWarps, ... ----
+  const int share_len = static_cast<int>(share_end - share_begin);
+  const int n_mine = share_len > warp ? (share_len - warp + kWarps - 1) / kWarps : 0;
   const uint32_t my_ring = ring + warp * (kStages * kStageBytes);
   const uint32_t my_bars = bars + warp * (kStages * 8);
-  long long t_issue = share_begin + warp;  // next page to fetch
-  long long t_use = t_issue;               // next page to consume
-  int n_issue = 0, n_use = 0;
   bool failed = false;
-  Cursor ic{0, 0, 0, 1};
-  int next_block = 0;
-  if (t_issue < share_end) {
-    ic = Locate(t_issue, prefix, num_seqs, heads);
-    next_block = p.tables[static_cast<int64_t>(ic.seq) * p.max_blocks + ic.page];
-  }
-  // Issues the fetch of page t_issue (block id already in next_block), then looks up the next one.
+
+  // Page metadata is looked up 32 pages at a time, one page per lane: lane j of batch b holds the
+  // pool row of the K tile of this warp's page 32b + j (the V tile is heads*16 rows further).
+  // The block-table read of a batch is issued a whole batch ahead of its first use.
+  auto fetch_rows = [&](int batch) -> int {
+    const int k = 32 * batch + lane;
+    if (k >= n_mine) return 0;
+    const Cursor c = Locate(share_begin + warp + kWarps * k, prefix, num_seqs, heads);
+    const int block = __ldg(p.tables + static_cast<int64_t>(c.seq) * p.max_blocks + c.page);
+    return (block * 2 * heads + c.head) * kKvBlock;
+  };
+  int rows_cur = fetch_rows(0);
+  int rows_next = n_mine > 32 ? fetch_rows(1) : 0;
+  const int v_row_delta = heads * kKvBlock;
+  int n_issue = 0, n_use = 0;
   auto issue_one = [&]() {
-    const int stage = n_issue % kStages;
+    const int row_k = __shfl_sync(0xffffffffu, rows_cur, n_issue & 31);
     if (lane == 0) {
+      const int stage = n_issue % kStages;
       const uint32_t dst = my_ring + stage * kStageBytes;
       const uint32_t bar = my_bars + stage * 8;
-      const int row_k = ((next_block * 2 + 0) * heads + ic.head) * kKvBlock;
-      const int row_v = ((next_block * 2 + 1) * heads + ic.head) * kKvBlock;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       MbarExpectTx(bar, kStageBytes);
-      TmaLoadBox(dst, &pool_map, 0, row_k, bar);
-      TmaLoadBox(dst + 2048, &pool_map, 64, row_k, bar);
-      TmaLoadBox(dst + 4096, &pool_map, 0, row_v, bar);
-      TmaLoadBox(dst + 6144, &pool_map, 64, row_v, bar);
+      if (tma_mode == 0) {
+        TmaLoadBox(dst, &pool_map, 0, row_k, bar);
+        TmaLoadBox(dst + 2048, &pool_map, 64, row_k, bar);
+        TmaLoadBox(dst + 4096, &pool_map, 0, row_k + v_row_delta, bar);
+        TmaLoadBox(dst + 6144, &pool_map, 64, row_k + v_row_delta, bar);
+      } else if (tma_mode == 1) {
+        TmaLoadBox4(dst, &tile_map, row_k >> 4, bar);
+        TmaLoadBox4(dst + 4096, &tile_map, (row_k + v_row_delta) >> 4, bar);
+      } else if (tma_mode == 2) {
+        TmaLoadBox4(dst, &tile_map, row_k >> 4, bar);
+      } else {
+        BulkLoad(dst, p.pool + static_cast<int64_t>(row_k) * kHeadDim, kPageBytes, bar);
+        BulkLoad(dst + 4096, p.pool + static_cast<int64_t>(row_k + v_row_delta) * kHeadDim, kPageBytes, bar);
+      }
     }
     ++n_issue;
-    t_issue += kWarps;
-    if (t_issue < share_end) {
-      Advance(ic, kWarps, prefix, num_seqs, heads);
-      next_block = p.tables[static_cast<int64_t>(ic.seq) * p.max_blocks + ic.page];
+    if ((n_issue & 31) == 0) {
+      rows_cur = rows_next;
+      rows_next = fetch_rows((n_issue >> 5) + 1);
     }
   };
 #pragma unroll 1
-  for (int i = 0; i < kStages && t_issue < share_end; ++i) issue_one();
+  for (int i = 0; i < kStages && n_issue < n_mine; ++i) issue_one();
 
-  // ldmatrix lane geometry (fixed per lane).
-  const int k_row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row for the K (A operand) loads
-  const int k_chunk_sel = lane >> 4;                      // which of the two 8-dim chunks of a k-step
-  const int v_row = (lane & 7) + (lane >> 4) * 8;         // token row for the V^T loads
-  const int v_chunk_sel = (lane >> 3) & 1;
+  // ldmatrix byte offsets inside a stage, fixed per lane. K tile: k-steps j and j+4 are 2048
+  // apart (the two 64-dim boxes); V tile likewise for dim tiles j and j+4.
+  uint32_t koff[4], voff[4];
+  {
+    const int k_row = (lane & 7) + ((lane >> 3) & 1) * 8;  // token row, A operand of S^T
+    const int k_sel = lane >> 4;                            // which 8-dim chunk of the k-step
+    const int v_row = (lane & 7) + (lane >> 4) * 8;         // token row, transposed loads of V
+    const int v_sel = (lane >> 3) & 1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      koff[j] = k_row * 128 + (((2 * j + k_sel) ^ (k_row & 7)) << 4);
+      voff[j] = 4096 + v_row * 128 + (((2 * j + v_sel) ^ (v_row & 7)) << 4);
+      if (tma_mode == 3) {  // linear [16][128] tiles
+        koff[j] = k_row * 256 + ((2 * j + k_sel) << 4);
+        voff[j] = 4096 + v_row * 256 + ((2 * j + v_sel) << 4);
+      }
+    }
+  }
+  const uint32_t hi_delta = tma_mode == 3 ? 128u : 2048u;
+  RL_STAMP(1);
 
   // ---- walk the share one (sequence, head) segment at a time ----
   long long seg_begin = share_begin;
@@ -331,6 +376,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
     const long long item_end = item_begin + sc.pages;
     const long long seg_end = item_end < share_end ? item_end : share_end;
     const int seq_len = min(p.seq_lens[sc.seq], p.max_blocks * kKvBlock);
+    const int seg_end_rel = static_cast<int>(seg_end - share_begin);
+    const int item_begin_rel = static_cast<int>(item_begin - share_begin);  // may be negative
 
     // Q fragments of this item: B operand of S^T = K.Q^T, query g (< 6) in column g.
     uint32_t qb[8][2];
@@ -339,8 +386,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
                          (static_cast<int64_t>(sc.head) * kGroup + g) * kHeadDim + 2 * tig;
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        qb[kk][0] = g < kGroup ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk) : 0u;
-        qb[kk][1] = g < kGroup ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8) : 0u;
+        qb[kk][0] = g < kGroup ? __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * kk)) : 0u;
+        qb[kk][1] = g < kGroup ? __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8)) : 0u;
       }
     }
     float o[8][4];
@@ -349,32 +396,32 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 
 #pragma unroll 1
-    while (t_use < seg_end) {
+    for (int rel = warp + kWarps * n_use; rel < seg_end_rel; rel += kWarps) {
       const int stage = n_use % kStages;
-      const int parity = (n_use / kStages) & 1;
       const uint32_t st = my_ring + stage * kStageBytes;
-      if (!failed && !MbarWait(my_bars + stage * 8, parity)) {
+      if (!failed && !MbarWait(my_bars + stage * 8, (n_use / kStages) & 1)) {
         failed = true;
         if (lane == 0) atomicExch(p.meta, 1);
       }
+      if (n_use == 0) { RL_STAMP(2); }
       if (!failed) {
-        const int page = static_cast<int>(t_use - item_begin);
-        const int valid = seq_len - page * kKvBlock;  // >= 1; >= 16 for a full page
+        const int valid = seq_len - (rel - item_begin_rel) * kKvBlock;  // >= 1; >= 16 for a full page
 
-        // S^T[token][query] = sum_d K[token][d] * Q[query][d]
-        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // S^T[token][query] = sum_d K[token][d] * Q[query][d]; two chains for latency
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const int chunk = ((kk & 3) << 1) + k_chunk_sel;
-          uint32_t a[4];
-          Ldsm4(st + (kk >> 2) * 2048 + k_row * 128 + ((chunk ^ (k_row & 7)) << 4), a);
-          Mma16816(s, a, qb[kk][0], qb[kk][1]);
+        for (int j = 0; j < 4; ++j) {
+          uint32_t a[4], a2[4];
+          Ldsm4(st + koff[j], a);
+          Ldsm4(st + koff[j] + hi_delta, a2);
+          Mma16816(s, a, qb[j][0], qb[j][1]);
+          Mma16816(s2, a2, qb[j + 4][0], qb[j + 4][1]);
         }
         // scale into the log2 domain; SELECT masking of slots past seq_len
-        s[0] = g < valid ? s[0] * p.scale_log2e : -INFINITY;
-        s[1] = g < valid ? s[1] * p.scale_log2e : -INFINITY;
-        s[2] = g + 8 < valid ? s[2] * p.scale_log2e : -INFINITY;
-        s[3] = g + 8 < valid ? s[3] * p.scale_log2e : -INFINITY;
+        s[0] = g < valid ? (s[0] + s2[0]) * p.scale_log2e : -INFINITY;
+        s[1] = g < valid ? (s[1] + s2[1]) * p.scale_log2e : -INFINITY;
+        s[2] = g + 8 < valid ? (s[2] + s2[2]) * p.scale_log2e : -INFINITY;
+        s[3] = g + 8 < valid ? (s[3] + s2[3]) * p.scale_log2e : -INFINITY;
         float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
         if (__any_sync(0xffffffffu, mx0 > m0 || mx1 > m1)) {
 #pragma unroll
@@ -406,9 +453,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
         if (valid >= kKvBlock) {
 #pragma unroll
           for (int mt = 0; mt < 8; ++mt) {
-            const int chunk = 2 * mt + v_chunk_sel;
             uint32_t a[4];
-            Ldsm4T(st + 4096 + (chunk >> 3) * 2048 + v_row * 128 + (((chunk & 7) ^ (v_row & 7)) << 4), a);
+            Ldsm4T(st + voff[mt & 3] + (mt >> 2) * hi_delta, a);
             Mma16816(o[mt], a, b0, b1);
           }
         } else {
@@ -418,9 +464,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
           const uint32_t k23 = (2 * tig + 8 < valid ? 0x0000FFFFu : 0u) | (2 * tig + 9 < valid ? 0xFFFF0000u : 0u);
 #pragma unroll
           for (int mt = 0; mt < 8; ++mt) {
-            const int chunk = 2 * mt + v_chunk_sel;
             uint32_t a[4];
-            Ldsm4T(st + 4096 + (chunk >> 3) * 2048 + v_row * 128 + (((chunk & 7) ^ (v_row & 7)) << 4), a);
+            Ldsm4T(st + voff[mt & 3] + (mt >> 2) * hi_delta, a);
             a[0] &= k01;
             a[1] &= k01;
             a[2] &= k23;
@@ -430,11 +475,11 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
         }
       }
       ++n_use;
-      t_use += kWarps;
       __syncwarp();  // every lane is done reading this stage before it is refilled
-      if (!failed && t_issue < share_end) issue_one();
+      if (!failed && n_issue < n_mine) issue_one();
     }
 
+    RL_STAMP(3);
     // ---- merge the 8 warps' partial (o, m, l) of this segment ----
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -458,6 +503,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
       }
     }
     __syncthreads();
+    RL_STAMP(5);
     {
       const bool whole = seg_begin == item_begin && seg_end == item_end;
       const int d = tid & 127;
@@ -495,41 +541,55 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
         const int c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
         const bool sparse = total < ctas;  // then every non-empty share is exactly one page
         const int contributors = sparse ? sc.pages : c_last - c_first + 1;
-        __threadfence();
-        __syncthreads();
+        RL_STAMP(6);
+        __syncthreads();  // the whole record is written (CTA scope) ...
         if (tid == 0) {
+          __threadfence();  // ... and ordered before the ticket at device scope (fences are cumulative)
           const int ticket = atomicAdd(p.meta + kTicketOff + c_first, 1);
           merge_here = ticket == contributors - 1;
           if (merge_here) p.meta[kTicketOff + c_first] = 0;  // everyone has arrived: re-arm
         }
         __syncthreads();
+        RL_STAMP(7);
         if (merge_here) {
           __threadfence();
-#pragma unroll 1
+          // Two passes over the contributors' records (L2 reads, independent per contributor):
+          // running max per head, then the rescaled sums, always in CTA order.
+          const int q0 = tid >> 7;  // this thread's heads: q0, q0 + 2, q0 + 4
+          float mx[3] = {-INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 4
+          for (int c = c_first; c <= c_last; ++c) {
+            if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+            const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats +
+                             kGroup * kHeadDim + q0;
+#pragma unroll
+            for (int qi = 0; qi < 3; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + 2 * qi));
+          }
+          float acc[3] = {0.0f, 0.0f, 0.0f}, den[3] = {0.0f, 0.0f, 0.0f};
+#pragma unroll 2
+          for (int c = c_first; c <= c_last; ++c) {
+            if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+            const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+#pragma unroll
+            for (int qi = 0; qi < 3; ++qi) {
+              const int qh = q0 + 2 * qi;
+              const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx[qi]);
+              acc[qi] = fmaf(f, __ldcg(r + qh * kHeadDim + d), acc[qi]);
+              den[qi] = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), den[qi]);
+            }
+          }
+#pragma unroll
           for (int qi = 0; qi < 3; ++qi) {
-            const int qh = (tid >> 7) + 2 * qi;
-            float mx = -INFINITY;
-            for (int c = c_first; c <= c_last; ++c) {
-              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
-              mx = fmaxf(mx, __ldcg(r + kGroup * kHeadDim + qh));
-            }
-            float acc = 0.0f, den = 0.0f;
-            for (int c = c_first; c <= c_last; ++c) {
-              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
-              const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx);
-              acc = fmaf(f, __ldcg(r + qh * kHeadDim + d), acc);
-              den = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), den);
-            }
             p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
-                  (static_cast<int64_t>(sc.head) * kGroup + qh) * kHeadDim + d] = __float2half_rn(acc / den);
+                  (static_cast<int64_t>(sc.head) * kGroup + q0 + 2 * qi) * kHeadDim + d] =
+                __float2half_rn(acc[qi] / den[qi]);
           }
         }
       }
     }
     __syncthreads();
     seg_begin = seg_end;
+    RL_STAMP(4);
   }
   // A warp that gave up on a load still owns copies in flight: give them one more bounded
   // chance to land before the CTA's shared memory is released.
@@ -590,6 +650,7 @@ struct DeviceState {
 constexpr int kMaxDevices = 64;
 DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
+void* g_timeline = nullptr;  // diagnostics build only
 std::mutex g_mutex;
 
 // First call per device: driver entry point, shared-memory opt-in, workspace.
@@ -642,6 +703,23 @@ int EncodePoolMap(const void* pool, CUtensorMap* map) {
   return RL_OK;
 }
 
+// The same memory as [tile][dim-half][token][64 halves]: one box {64, 16, 2, 1} is a whole
+// (block, kv, head) tile; with a box of heads+1 tiles walked at stride `heads` it is the K tile and
+// the V tile of one head in a single copy (tile_stride > 1).
+int EncodeTileMap(const void* pool, int tile_stride, CUtensorMap* map) {
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kPageBytes)};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 2,
+                             static_cast<cuuint32_t>(tile_stride > 1 ? tile_stride + 1 : 1)};
+  const cuuint32_t estr[4] = {1, 1, 1, static_cast<cuuint32_t>(tile_stride > 1 ? tile_stride : 1)};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pool), dims,
+                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_attention: tile map encode failed (CUresult %d)", static_cast<int>(r));
+  return RL_OK;
+}
+
 int CheckContract(const char* fn, const void* out, int64_t out_stride, const void* q,
                   int64_t q_stride, const void* pool, const void* tables, const void* lens,
                   int max_blocks, int q_heads, int kv_heads, int head_dim) {
@@ -667,6 +745,21 @@ extern "C" int rl_kernels_init(int device) {
   rl::attn::DeviceState* st;
   return rl::attn::EnsureReady(&st);
 }
+
+#ifdef RL_ATTN_TIMELINE
+// Diagnostics build (-DRL_ATTN_TIMELINE): per-warp %globaltimer stamps of the last launch.
+extern "C" int rl_debug_attention_timeline(unsigned long long* host_out, int max_entries) {
+  cudaDeviceSynchronize();
+  const int n = rl::attn::kMaxCtas * rl::attn::kWarps * 8;
+  return cudaMemcpy(host_out, rl::attn::g_timeline, sizeof(unsigned long long) * (n < max_entries ? n : max_entries),
+                    cudaMemcpyDeviceToHost);
+}
+extern "C" int rl_debug_attention_timeline_init(void) {
+  const size_t bytes = sizeof(unsigned long long) * rl::attn::kMaxCtas * rl::attn::kWarps * 8;
+  if (!rl::attn::g_timeline) cudaMalloc(&rl::attn::g_timeline, bytes);
+  return cudaMemset(rl::attn::g_timeline, 0, bytes);
+}
+#endif
 
 extern "C" int rl_attention_health(int* flag_out) {
   using namespace rl;
@@ -702,8 +795,10 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: the pool slice must be 16-byte aligned");
   DeviceState* st;
   if ((rc = EnsureReady(&st)) != RL_OK) return rc;
-  CUtensorMap map;
+  CUtensorMap map, tile_map;
   if ((rc = EncodePoolMap(kv_pool_layer, &map)) != RL_OK) return rc;
+  static const int tma_mode = [] { const char* e = getenv("RL_ATTN_TMA_MODE"); return e ? atoi(e) : 0; }();
+  if ((rc = EncodeTileMap(kv_pool_layer, tma_mode == 2 ? num_kv_heads : 1, &tile_map)) != RL_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   for (int first = 0; first < num_seqs; first += kMaxSeqsPerLaunch) {
     const int n = num_seqs - first < kMaxSeqsPerLaunch ? num_seqs - first : kMaxSeqsPerLaunch;
@@ -720,7 +815,12 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     p.scale_log2e = scale * 1.4426950408889634f;
     p.meta = static_cast<int*>(st->workspace);
     p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
-    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, map);
+    p.pool = static_cast<const half*>(kv_pool_layer);
+    p.timeline = nullptr;
+#ifdef RL_ATTN_TIMELINE
+    p.timeline = static_cast<unsigned long long*>(g_timeline);
+#endif
+    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, map, tile_map, tma_mode);
   }
   return LaunchStatus("paged_attention_decode");
 }
