@@ -1,0 +1,561 @@
+"""Decode engine around the sm_100a kernels: the caller side of the hot path.
+
+Mirrors the public surface of the reference's Python binding (src/api/pybind.cpp:104-214):
+`Engine(...)`, `add_request`, `step`, `has_capacity`, `stats`, plus the pieces of src/core the
+hot path needs to run - a reservation block allocator (src/core/block_allocator.hpp:41-57), an
+FCFS continuous-batching scheduler with the {1,2,4,8,16,32,48,64} bucket ladder
+(src/core/scheduler.cpp:11-34,145-197,248-332) and a model executor that replays one CUDA graph per
+bucket (src/core/model_executor.cpp:523-633,721-782). The decode layer sequence is the reference's
+(src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library, every
+linear layer is a library GEMM (torch.matmul -> cuBLAS, unchanged on both sides of any comparison).
+
+One Engine drives one GPU; multi-GPU serving is one Engine per GPU with requests sharded on the
+host (`shard_requests`) - sequences and their KV pages never leave their GPU, so no collective exists.
+
+torch is used for device memory, streams, graphs and the GEMMs only.
+"""
+from __future__ import annotations
+
+import dataclasses
+from collections import deque
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+KV_BLOCK = 16       # src/core/types.hpp: kKvBlockSize
+DUMMY_BLOCK = 0     # reserved padding target (kDummyBlockId)
+BUCKETS = (1, 2, 4, 8, 16, 32, 48, 64)
+
+
+@dataclasses.dataclass(frozen=True)
+class ModelConfig:
+    """Architecture constants (defaults: Qwen2.5-1.5B, docs/MODEL_SPEC.md)."""
+    layers: int = 28
+    hidden: int = 1536
+    inter: int = 8960
+    q_heads: int = 12
+    kv_heads: int = 2
+    head_dim: int = 128
+    vocab: int = 151936
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    eos_token_id: int = 151645
+
+    @property
+    def qkv_width(self):
+        return (self.q_heads + 2 * self.kv_heads) * self.head_dim
+
+    @property
+    def q_width(self):
+        return self.q_heads * self.head_dim
+
+    @property
+    def kv_width(self):
+        return self.kv_heads * self.head_dim
+
+    def block_bytes(self):
+        return self.layers * 2 * self.kv_heads * KV_BLOCK * self.head_dim * 2
+
+
+def blocks_for_tokens(n: int) -> int:
+    return (n + KV_BLOCK - 1) // KV_BLOCK
+
+
+def select_bucket(n: int) -> int:
+    """Smallest bucket >= n (src/core/scheduler.cpp:11-34); 0 when none covers it."""
+    for b in BUCKETS:
+        if b >= n:
+            return b
+    return 0
+
+
+def shard_requests(num_requests: int, world: int, rank: int) -> List[int]:
+    """Indices of the requests replica `rank` serves: dealt round-robin, so every replica gets the
+    same mix of an already shuffled list. Pure host logic; no communication."""
+    return list(range(rank, num_requests, world))
+
+
+class BlockAllocator:
+    """Free-list allocator with reservations: a request reserves the blocks it can ever need at
+    admission (`reserve_full`), then turns reservations into real blocks at 16-token boundaries."""
+
+    def __init__(self, total_blocks: int):
+        if total_blocks < 2:
+            raise ValueError("the pool needs the dummy block and at least one real block")
+        self.total = total_blocks
+        self.free = list(range(total_blocks - 1, 0, -1))  # block 0 is the dummy
+        self.reserved = 0
+
+    def can_reserve(self, n: int) -> bool:
+        return len(self.free) - self.reserved >= n
+
+    def reserve(self, n: int) -> None:
+        if not self.can_reserve(n):
+            raise RuntimeError("reserve beyond capacity")
+        self.reserved += n
+
+    def unreserve(self, n: int) -> None:
+        assert n <= self.reserved
+        self.reserved -= n
+
+    def alloc_reserved(self) -> int:
+        assert self.reserved > 0 and self.free
+        self.reserved -= 1
+        return self.free.pop()
+
+    def free_block(self, b: int) -> None:
+        assert 0 < b < self.total
+        self.free.append(b)
+
+    @property
+    def free_blocks(self) -> int:
+        return len(self.free)
+
+
+@dataclasses.dataclass
+class Request:
+    req_id: int
+    prompt: List[int]
+    max_new_tokens: int
+    ignore_eos: bool = False
+    forced_tokens: Optional[List[int]] = None
+    output: List[int] = dataclasses.field(default_factory=list)
+    blocks: List[int] = dataclasses.field(default_factory=list)
+    reserved_left: int = 0
+    prefilled: int = 0          # prompt tokens whose K/V are in the cache
+    cached: int = 0             # tokens in the cache (prompt + generated, except the pending one)
+    finished: bool = False
+    reason: str = ""
+
+    @property
+    def seq_len(self) -> int:   # tokens the next decode step attends to, including the new one
+        return self.cached + 1
+
+
+class Scheduler:
+    """FCFS admission, prefill-before-decode, bucketed decode batches."""
+
+    def __init__(self, allocator: BlockAllocator, max_batch: int, max_seq_len: int, prefill_chunk: int,
+                 eos_token_id: int = 151645):
+        self.alloc, self.max_batch, self.max_seq_len, self.chunk = allocator, max_batch, max_seq_len, prefill_chunk
+        self.eos = eos_token_id
+        self.waiting: deque = deque()
+        self.running: List[Request] = []
+        self.aborts = 0
+
+    def enqueue(self, r: Request) -> None:
+        self.waiting.append(r)
+
+    def _admit(self) -> None:
+        while self.waiting and len(self.running) < self.max_batch:
+            r = self.waiting[0]
+            need = blocks_for_tokens(len(r.prompt) + r.max_new_tokens)
+            if not self.alloc.can_reserve(need):
+                if not self.running:  # can never fit: abort instead of stalling forever
+                    self.waiting.popleft()
+                    r.finished, r.reason = True, "aborted"
+                    self.aborts += 1
+                    self.running.append(r)
+                return
+            self.alloc.reserve(need)
+            r.reserved_left = need
+            self.running.append(self.waiting.popleft())
+
+    def _grow(self, r: Request, tokens: int) -> None:
+        while len(r.blocks) < blocks_for_tokens(tokens):
+            r.blocks.append(self.alloc.alloc_reserved())
+            r.reserved_left -= 1
+
+    def plan_step(self):
+        """Returns ("prefill", request, start, end) | ("decode", [requests]) | ("idle",) | ("flush", [aborted])."""
+        self._admit()
+        dead = [r for r in self.running if r.finished]
+        if dead:
+            return ("flush", dead)
+        for r in self.running:
+            if r.prefilled < len(r.prompt):
+                end = min(len(r.prompt), r.prefilled + self.chunk)
+                self._grow(r, end)
+                return ("prefill", r, r.prefilled, end)
+        if not self.running:
+            return ("idle",)
+        batch = self.running[: BUCKETS[-1]]
+        for r in batch:
+            self._grow(r, r.seq_len)
+        return ("decode", batch)
+
+    def complete(self, r: Request, token: int) -> Tuple[int, int, bool, str]:
+        """Appends the sampled (or forced) token, applies the stop checks, frees blocks on finish."""
+        if r.forced_tokens is not None and len(r.output) < len(r.forced_tokens):
+            token = r.forced_tokens[len(r.output)]
+        r.output.append(int(token))
+        if len(r.output) >= r.max_new_tokens:
+            r.finished, r.reason = True, "length"
+        elif not r.ignore_eos and token == self.eos:
+            r.finished, r.reason = True, "eos"
+        if r.finished:
+            self.release(r)
+        return (r.req_id, int(token), r.finished, r.reason)
+
+    def release(self, r: Request) -> None:
+        for b in r.blocks:
+            self.alloc.free_block(b)
+        r.blocks = []
+        self.alloc.unreserve(r.reserved_left)
+        r.reserved_left = 0
+        if r in self.running:
+            self.running.remove(r)
+
+
+class ModelWeights:
+    """Random-init weights of the architecture: FP16 ~N(0, 0.02), norm weights 1 (seeded)."""
+
+    def __init__(self, cfg: ModelConfig, device, seed: int = 0x5EED, std: float = 0.02):
+        import torch
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+
+        def rnd(*shape):
+            return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).to(torch.float16)
+
+        self.embed = rnd(cfg.vocab, cfg.hidden)
+        self.lm_head = self.embed  # tied, as in the 1.5B checkpoint
+        self.final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
+        self.layers = []
+        for _ in range(cfg.layers):
+            self.layers.append(dict(
+                in_norm=torch.ones(cfg.hidden, dtype=torch.float16, device=device),
+                post_norm=torch.ones(cfg.hidden, dtype=torch.float16, device=device),
+                qkv=rnd(cfg.qkv_width, cfg.hidden), qkv_bias=rnd(cfg.qkv_width),
+                o=rnd(cfg.hidden, cfg.q_width), gate_up=rnd(2 * cfg.inter, cfg.hidden),
+                down=rnd(cfg.hidden, cfg.inter)))
+
+
+class ModelExecutor:
+    """Owns the KV pool, the step buffers and one CUDA graph per decode bucket."""
+
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, num_blocks: int, max_seq_len: int,
+                 device, enable_cuda_graphs: bool = True):
+        import torch
+        from . import kernels as K
+        self.torch, self.K, self.cfg, self.w, self.device = torch, K, cfg, weights, device
+        self.num_blocks = num_blocks
+        self.mbps = blocks_for_tokens(max_seq_len)
+        self.graphs_enabled = enable_cuda_graphs
+        f16, i32 = torch.float16, torch.int32
+        self.pool = torch.zeros(cfg.layers, num_blocks, 2, cfg.kv_heads, KV_BLOCK, cfg.head_dim, dtype=f16, device=device)
+        B = BUCKETS[-1]
+        self.ids = torch.zeros(B, dtype=i32, device=device)
+        self.positions = torch.zeros(B, dtype=i32, device=device)
+        self.seq_lens = torch.zeros(B, dtype=i32, device=device)
+        self.tables = torch.zeros(B, self.mbps, dtype=i32, device=device)
+        self.x = torch.zeros(B, cfg.hidden, dtype=f16, device=device)          # residual stream
+        self.normed = torch.zeros(B, cfg.hidden, dtype=f16, device=device)
+        self.qkv = torch.zeros(B, cfg.qkv_width, dtype=f16, device=device)
+        self.attn = torch.zeros(B, cfg.q_width, dtype=f16, device=device)
+        self.mlp = torch.zeros(B, cfg.hidden, dtype=f16, device=device)
+        self.gateup = torch.zeros(B, 2 * cfg.inter, dtype=f16, device=device)
+        self.logits = torch.zeros(B, cfg.vocab, dtype=f16, device=device)
+        self.tokens = torch.zeros(B, dtype=torch.int64, device=device)
+        # pinned mirrors (one H2D each per step, one D2H)
+        self.h_ids = torch.zeros(B, dtype=i32).pin_memory()
+        self.h_pos = torch.zeros(B, dtype=i32).pin_memory()
+        self.h_lens = torch.zeros(B, dtype=i32).pin_memory()
+        self.h_tables = torch.zeros(B, self.mbps, dtype=i32).pin_memory()
+        self.h_tokens = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self._np_ids, self._np_pos = self.h_ids.numpy(), self.h_pos.numpy()
+        self._np_lens, self._np_tables = self.h_lens.numpy(), self.h_tables.numpy()
+        self.row_owner: List[Optional[int]] = [None] * B   # request id whose table sits in row i
+        self.row_len = [0] * B
+        self.dirty_rows: List[int] = []
+        self.h2d_bytes = 0
+        self.graphs: Dict[int, object] = {}
+        self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
+        self.attention_events = None  # set by profile runs
+        K.init(device.index if device.index is not None else -1)
+
+    # ---- the decode layer sequence (src/core/model_executor.cpp:894-961)
+    def enqueue_decode(self, rows: int) -> None:
+        torch, K, cfg, w = self.torch, self.K, self.cfg, self.w
+        x, normed, qkv, attn, mlp, gu = (self.x[:rows], self.normed[:rows], self.qkv[:rows], self.attn[:rows],
+                                         self.mlp[:rows], self.gateup[:rows])
+        torch.index_select(w.embed, 0, self.ids[:rows], out=x)
+        for li, L in enumerate(w.layers):
+            if li == 0:
+                K.launch_rms_norm(normed, x, L["in_norm"], rows, cfg.hidden, cfg.eps)
+            else:
+                K.launch_rms_norm_residual(normed, x, mlp, L["in_norm"], rows, cfg.hidden, cfg.eps)
+            torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
+            K.launch_rope_inplace(qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.positions, rows, cfg.q_heads,
+                                  cfg.kv_heads, cfg.head_dim, cfg.rope_theta, k_offset=cfg.q_width)
+            K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.tables, self.mbps,
+                                self.positions, rows, cfg.kv_heads, cfg.head_dim,
+                                k_offset=cfg.q_width, v_offset=cfg.q_width + cfg.kv_width)
+            if self.attention_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            K.launch_paged_attention_decode(attn, cfg.q_width, qkv, cfg.qkv_width, self.pool[li], self.tables,
+                                            self.seq_lens, rows, self.mbps, cfg.q_heads, cfg.kv_heads,
+                                            cfg.head_dim, self.scale)
+            if self.attention_events is not None:
+                e1.record()
+                self.attention_events.append((e0, e1))
+            torch.matmul(attn, L["o"].t(), out=mlp)
+            K.launch_rms_norm_residual(normed, x, mlp, L["post_norm"], rows, cfg.hidden, cfg.eps)
+            torch.matmul(normed, L["gate_up"].t(), out=gu)
+            K.launch_silu_mul(gu, gu, rows, cfg.inter)
+            torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
+        K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, rows, cfg.hidden, cfg.eps)
+        torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
+        torch.argmax(self.logits[:rows], dim=-1, out=self.tokens[:rows])
+
+    def warm_and_capture(self, buckets: Sequence[int]) -> None:
+        """Eager warm-up of every bucket (first launches happen outside capture), then one graph each."""
+        torch = self.torch
+        self.seq_lens.fill_(1)
+        for b in buckets:
+            self.enqueue_decode(b)
+        torch.cuda.synchronize(self.device)
+        if not self.graphs_enabled:
+            return
+        for b in buckets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.enqueue_decode(b)
+            self.graphs[b] = g
+        self.seq_lens.zero_()
+
+    def fill_mirrors(self, batch: List[Request], rows: int) -> None:
+        """token = last output (or last prompt token), position = seq_len - 1, seq_len, table row; padded
+        rows get token 0 / position 0 / seq_len 0 / all-dummy row (src/core/model_executor.cpp:784-874).
+        A table row is rewritten only when its owner changed or gained a page, and only rewritten rows are
+        uploaded: at 33k-token contexts a row is 8 KiB and the whole slab would be 0.5 MB per step."""
+        ids, pos, lens, tab = self._np_ids, self._np_pos, self._np_lens, self._np_tables
+        ids[:rows] = 0; pos[:rows] = 0; lens[:rows] = 0
+        self.dirty_rows = []
+        for i in range(rows):
+            r = batch[i] if i < len(batch) else None
+            if r is None:
+                if self.row_owner[i] is not None:
+                    tab[i, :self.row_len[i]] = DUMMY_BLOCK
+                    self.row_owner[i], self.row_len[i] = None, 0
+                    self.dirty_rows.append(i)
+                continue
+            if r.seq_len > self.mbps * KV_BLOCK or len(r.blocks) < blocks_for_tokens(r.seq_len):
+                raise RuntimeError(f"request {r.req_id}: decode row outside its block table")
+            ids[i] = r.output[-1] if r.output else r.prompt[-1]
+            pos[i] = r.seq_len - 1
+            lens[i] = r.seq_len
+            nb = len(r.blocks)
+            if self.row_owner[i] != r.req_id:
+                tab[i, :max(nb, self.row_len[i])] = DUMMY_BLOCK
+                tab[i, :nb] = r.blocks
+                self.row_owner[i], self.row_len[i] = r.req_id, nb
+                self.dirty_rows.append(i)
+            elif self.row_len[i] != nb:
+                tab[i, self.row_len[i]:nb] = r.blocks[self.row_len[i]:nb]
+                self.row_len[i] = nb
+                self.dirty_rows.append(i)
+
+    def upload(self, rows: int) -> None:
+        self.ids[:rows].copy_(self.h_ids[:rows], non_blocking=True)
+        self.positions[:rows].copy_(self.h_pos[:rows], non_blocking=True)
+        self.seq_lens[:rows].copy_(self.h_lens[:rows], non_blocking=True)
+        if len(self.dirty_rows) > rows // 2:
+            self.tables[:rows].copy_(self.h_tables[:rows], non_blocking=True)
+        else:
+            for i in self.dirty_rows:
+                self.tables[i].copy_(self.h_tables[i], non_blocking=True)
+        self.h2d_bytes = 12 * rows + 4 * self.mbps * (rows if len(self.dirty_rows) > rows // 2 else len(self.dirty_rows))
+
+    def run(self, rows: int) -> None:
+        g = self.graphs.get(rows)
+        if g is not None:
+            g.replay()
+        else:
+            self.enqueue_decode(rows)
+
+    def download(self, rows: int):
+        self.h_tokens[:rows].copy_(self.tokens[:rows], non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return self.h_tokens[:rows].tolist()
+
+    # ---- prompt ingestion (not on the hot path): chunked, eager, library attention
+    def prefill_chunk(self, r: Request, start: int, end: int) -> Optional[int]:
+        torch, K, cfg, w = self.torch, self.K, self.cfg, self.w
+        import torch.nn.functional as F
+        n = end - start
+        dev = self.device
+        ids = torch.tensor(r.prompt[start:end], dtype=torch.int32, device=dev)
+        pos = torch.arange(start, end, dtype=torch.int32, device=dev)
+        row = torch.zeros(1, self.mbps, dtype=torch.int32, device=dev)
+        row[0, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32, device=dev)
+        x = w.embed.index_select(0, ids)
+        normed, mlp = torch.empty_like(x), torch.empty_like(x)
+        qkv = torch.empty(n, cfg.qkv_width, dtype=torch.float16, device=dev)
+        gu = torch.empty(n, 2 * cfg.inter, dtype=torch.float16, device=dev)
+        slots = torch.arange(end, device=dev)
+        blk = row[0, (slots // KV_BLOCK).long()].long()
+        slot = (slots % KV_BLOCK).long()
+        mask = (torch.arange(end, device=dev)[None, :] <= pos[:, None].long())
+        for li, L in enumerate(w.layers):
+            if li == 0:
+                K.launch_rms_norm(normed, x, L["in_norm"], n, cfg.hidden, cfg.eps)
+            else:
+                K.launch_rms_norm_residual(normed, x, mlp, L["in_norm"], n, cfg.hidden, cfg.eps)
+            torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
+            K.launch_rope_inplace(qkv, qkv, cfg.qkv_width, cfg.qkv_width, pos, n, cfg.q_heads, cfg.kv_heads,
+                                  cfg.head_dim, cfg.rope_theta, k_offset=cfg.q_width)
+            K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, row, 0, pos, n,
+                                cfg.kv_heads, cfg.head_dim, k_offset=cfg.q_width,
+                                v_offset=cfg.q_width + cfg.kv_width)
+            kc = self.pool[li][blk, 0, :, slot, :].permute(1, 0, 2)   # [kv_heads, end, d]
+            vc = self.pool[li][blk, 1, :, slot, :].permute(1, 0, 2)
+            q = qkv[:, :cfg.q_width].view(n, cfg.q_heads, cfg.head_dim).permute(1, 0, 2)
+            o = F.scaled_dot_product_attention(q[None], kc[None], vc[None], attn_mask=mask[None, None],
+                                               enable_gqa=True)[0]
+            attn = o.permute(1, 0, 2).reshape(n, cfg.q_width).contiguous()
+            torch.matmul(attn, L["o"].t(), out=mlp)
+            K.launch_rms_norm_residual(normed, x, mlp, L["post_norm"], n, cfg.hidden, cfg.eps)
+            torch.matmul(normed, L["gate_up"].t(), out=gu)
+            K.launch_silu_mul(gu, gu, n, cfg.inter)
+            torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
+        r.prefilled = end
+        if end < len(r.prompt):
+            return None
+        K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, n, cfg.hidden, cfg.eps)
+        logits = torch.matmul(normed[-1:], w.lm_head.t())
+        return int(torch.argmax(logits, dim=-1).item())
+
+
+class Engine:
+    """`redline.Engine` look-alike (src/api/pybind.cpp:104-214) over one GPU."""
+
+    def __init__(self, model_dir: Optional[str] = None, kv_pool_gb: float = 1.0, max_batch: int = 8,
+                 enable_cuda_graphs: bool = True, max_seq_len: int = 2048, prefill_chunk: int = 1024,
+                 admission_policy: str = "reserve_full", pad_eager_to_bucket: int = 0,
+                 debug_dump_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
+                 device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
+                 graph_buckets: Optional[Sequence[int]] = None):
+        import torch
+        if admission_policy != "reserve_full":
+            raise ValueError("only the reserve_full admission policy is provided")
+        if not 1 <= max_batch <= BUCKETS[-1]:
+            raise ValueError(f"max_batch must be in [1, {BUCKETS[-1]}]")
+        if model_dir is not None:
+            raise ValueError("checkpoint loading is outside this library: pass weights= or use random init")
+        if not torch.cuda.is_available():
+            raise RuntimeError("the decode kernels need a CUDA device; there is no CPU fallback")
+        self.cfg = config or ModelConfig()
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        num_blocks = max(2, int(kv_pool_gb * (1 << 30)) // self.cfg.block_bytes())
+        self.allocator = BlockAllocator(num_blocks)
+        self.scheduler = Scheduler(self.allocator, max_batch, max_seq_len, prefill_chunk, self.cfg.eos_token_id)
+        self.weights = weights or ModelWeights(self.cfg, self.device, seed)
+        self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
+        self.max_seq_len, self.max_batch = max_seq_len, max_batch
+        self.pad_eager_to_bucket = pad_eager_to_bucket
+        buckets = [b for b in BUCKETS if b <= select_bucket(max_batch)]
+        if graph_buckets is not None:
+            buckets = [b for b in buckets if b in set(graph_buckets)]
+        self.exec.warm_and_capture(buckets)
+        self._next_id = 0
+        self._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
+        self._hist = {b: 0 for b in BUCKETS}
+
+    def add_request(self, token_ids: Sequence[int], max_new_tokens: int, ignore_eos: bool = False,
+                    forced_tokens: Optional[Sequence[int]] = None) -> int:
+        ids = [int(t) for t in token_ids]
+        if not ids or max_new_tokens < 1:
+            raise ValueError("a request needs at least one prompt token and max_new_tokens >= 1")
+        if any(t < 0 or t >= self.cfg.vocab for t in ids):
+            raise ValueError("token id outside the vocabulary")
+        if len(ids) + max_new_tokens > self.max_seq_len:
+            raise ValueError("prompt + max_new_tokens exceeds max_seq_len")
+        r = Request(self._next_id, ids, int(max_new_tokens), bool(ignore_eos),
+                    None if forced_tokens is None else [int(t) for t in forced_tokens])
+        self._next_id += 1
+        self.scheduler.enqueue(r)
+        return r.req_id
+
+    def has_capacity(self) -> bool:
+        return len(self.scheduler.running) + len(self.scheduler.waiting) < self.max_batch
+
+    def step(self) -> List[Tuple[int, int, bool, str]]:
+        plan = self.scheduler.plan_step()
+        self._stats["steps"] += 1
+        if plan[0] == "idle":
+            return []
+        if plan[0] == "flush":
+            out = []
+            for r in plan[1]:
+                self.scheduler.release(r)
+                out.append((r.req_id, -1, True, r.reason))
+            return out
+        if plan[0] == "prefill":
+            _, r, start, end = plan
+            tok = self.exec.prefill_chunk(r, start, end)
+            self._stats["prefill_tokens"] += end - start
+            if tok is None:
+                return []
+            r.cached = len(r.prompt)
+            return [self.scheduler.complete(r, tok)]
+        batch = plan[1]
+        rows = select_bucket(max(len(batch), self.pad_eager_to_bucket))
+        self.exec.fill_mirrors(batch, rows)
+        self.exec.upload(rows)
+        self.exec.run(rows)
+        toks = self.exec.download(rows)
+        self._stats["graph_replays" if rows in self.exec.graphs else "eager_decodes"] += 1
+        self._stats["decode_tokens"] += len(batch)
+        self._hist[rows] += 1
+        out = []
+        for r, t in zip(list(batch), toks):
+            r.cached += 1
+            out.append(self.scheduler.complete(r, t))
+        return out
+
+    def stats(self) -> dict:
+        a = self.allocator
+        return dict(self._stats, waiting=len(self.scheduler.waiting), running=len(self.scheduler.running),
+                    free_blocks=a.free_blocks, reserved_blocks=a.reserved, total_blocks=a.total,
+                    aborts=self.scheduler.aborts, bucket_histogram=dict(self._hist))
+
+    def debug_block_table(self, req_id: int) -> List[int]:
+        for r in list(self.scheduler.running) + list(self.scheduler.waiting):
+            if r.req_id == req_id:
+                return list(r.blocks)
+        raise ValueError("unknown request id")
+
+    # ---- benchmark support: a request whose cache is filled with seeded synthetic K/V
+    def add_synthetic_request(self, context_len: int, max_new_tokens: int, seed: int) -> int:
+        """Admits a request as if a prompt of `context_len` tokens had been prefilled: its pages are
+        allocated and filled with ~N(0,1) FP16 K/V on the device. No prompt pass runs."""
+        torch = self.exec.torch
+        if len(self.scheduler.running) >= self.max_batch:
+            raise RuntimeError("max_batch sequences are already running")
+        if context_len + max_new_tokens > self.max_seq_len:
+            raise ValueError("context + max_new_tokens exceeds max_seq_len")
+        need = blocks_for_tokens(context_len + max_new_tokens)
+        if not self.allocator.can_reserve(need):
+            raise RuntimeError("KV pool too small for this request")
+        r = Request(self._next_id, [seed % self.cfg.vocab], max_new_tokens, ignore_eos=True)
+        self._next_id += 1
+        self.allocator.reserve(need)
+        r.reserved_left = need
+        self.scheduler._grow(r, context_len + 1)
+        nb = blocks_for_tokens(context_len)
+        if nb:
+            g = torch.Generator(device=self.device)
+            g.manual_seed(seed)
+            idx = torch.tensor(r.blocks[:nb], device=self.device)
+            cfg = self.cfg
+            for li in range(cfg.layers):
+                vals = torch.randn(nb, 2, cfg.kv_heads, KV_BLOCK, cfg.head_dim, generator=g, device=self.device,
+                                   dtype=torch.float16)
+                self.exec.pool[li].index_copy_(0, idx, vals)
+        r.prefilled, r.cached = 1, context_len
+        r.prompt = [seed % self.cfg.vocab]
+        self.scheduler.running.append(r)
+        return r.req_id

@@ -1,0 +1,138 @@
+"""Host-side logic of the decode engine (no GPU): allocator, scheduler, bucket ladder, replica
+sharding. Patterns follow the reference's CPU suites tests/test_allocator.cpp and
+tests/test_scheduler.cpp (scripted tokens stand in for the executor)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from redline_llm_b200.engine import (BUCKETS, BlockAllocator, Request, Scheduler, blocks_for_tokens,
+                                     select_bucket, shard_requests)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_bucket_ladder_and_block_math():
+    assert [select_bucket(n) for n in (1, 2, 3, 5, 9, 17, 33, 49, 64)] == [1, 2, 4, 8, 16, 32, 48, 64, 64]
+    assert select_bucket(65) == 0 and BUCKETS[-1] == 64
+    assert [blocks_for_tokens(n) for n in (0, 1, 15, 16, 17, 32768)] == [0, 1, 1, 1, 2, 2048]
+
+
+def test_allocator_reservations_and_dummy_block():
+    a = BlockAllocator(10)
+    assert a.free_blocks == 9 and a.can_reserve(9) and not a.can_reserve(10)
+    a.reserve(4)
+    got = [a.alloc_reserved() for _ in range(3)]
+    assert 0 not in got and len(set(got)) == 3 and a.reserved == 1
+    assert a.can_reserve(5) and not a.can_reserve(6)
+    with pytest.raises(RuntimeError):
+        a.reserve(6)
+    for b in got:
+        a.free_block(b)
+    a.unreserve(1)
+    assert a.free_blocks == 9 and a.reserved == 0
+
+
+def drive(s: Scheduler, scripted):
+    """Runs the scheduler to completion with scripted tokens; returns per-request outputs and the plan log."""
+    out, log = {}, []
+    for _ in range(10000):
+        plan = s.plan_step()
+        log.append(plan[0])
+        if plan[0] == "idle":
+            break
+        if plan[0] == "flush":
+            for r in plan[1]:
+                s.release(r)
+                out[r.req_id] = ("aborted", [])
+        elif plan[0] == "prefill":
+            _, r, a, b = plan
+            assert len(r.blocks) >= blocks_for_tokens(b)
+            r.prefilled = b
+            if b == len(r.prompt):
+                r.cached = len(r.prompt)
+                res = s.complete(r, scripted(r))
+                if res[2]:
+                    out[r.req_id] = (res[3], list(r.output))
+        else:
+            for r in list(plan[1]):
+                assert len(r.blocks) >= blocks_for_tokens(r.seq_len)
+                r.cached += 1
+                res = s.complete(r, scripted(r))
+                if res[2]:
+                    out[r.req_id] = (res[3], list(r.output))
+    return out, log
+
+
+def test_scheduler_fcfs_prefill_then_decode_and_stop_reasons():
+    a = BlockAllocator(64)
+    s = Scheduler(a, max_batch=4, max_seq_len=256, prefill_chunk=16, eos_token_id=7)
+    reqs = [Request(0, list(range(1, 41)), 5), Request(1, [1, 2, 3], 8), Request(2, [9] * 20, 3, ignore_eos=True),
+            Request(3, [4], 4, forced_tokens=[11, 12, 13, 14])]
+    for r in reqs:
+        s.enqueue(r)
+    script = {0: [5, 5, 5, 5, 5], 1: [5, 7, 5], 2: [7, 7, 7], 3: [0, 0, 0, 0]}
+    out, log = drive(s, lambda r: script[r.req_id][len(r.output)])
+    assert out[0] == ("length", [5, 5, 5, 5, 5])
+    assert out[1] == ("eos", [5, 7])
+    assert out[2] == ("length", [7, 7, 7])            # ignore_eos
+    assert out[3] == ("length", [11, 12, 13, 14])     # forced tokens override the sampled ones
+    assert log.count("prefill") == 3 + 1 + 2 + 1      # 40 and 20 tokens in chunks of 16
+    assert a.free_blocks == 63 and a.reserved == 0    # everything returned
+
+
+def test_scheduler_waits_for_capacity_and_aborts_the_unservable():
+    a = BlockAllocator(8)                               # 7 usable blocks = 112 tokens
+    s = Scheduler(a, max_batch=8, max_seq_len=4096, prefill_chunk=64)
+    s.enqueue(Request(0, [1] * 60, 20))                 # 5 blocks
+    s.enqueue(Request(1, [1] * 30, 10))                 # 3 blocks: must wait for request 0
+    s.enqueue(Request(2, [1] * 200, 10))                # can never fit
+    out, log = drive(s, lambda r: 3)
+    assert out[0][0] == "length" and out[1][0] == "length" and out[2][0] == "aborted"
+    assert s.aborts == 1 and a.free_blocks == 7 and a.reserved == 0
+
+
+def test_randomised_churn_never_leaks_blocks():
+    import random
+    rnd = random.Random(5)
+    a = BlockAllocator(200)
+    s = Scheduler(a, max_batch=16, max_seq_len=2048, prefill_chunk=128)
+    for i in range(60):
+        s.enqueue(Request(i, [1] * rnd.randint(1, 300), rnd.randint(1, 60), ignore_eos=True))
+    out, _ = drive(s, lambda r: 1)
+    assert len(out) == 60 and a.free_blocks == 199 and a.reserved == 0
+
+
+def test_shard_requests_partitions_without_overlap():
+    for world in (1, 2, 4, 8):
+        seen = sorted(i for r in range(world) for i in shard_requests(512, world, r))
+        assert seen == list(range(512))
+        assert {len(shard_requests(512, world, r)) for r in range(world)} == {512 // world}
+
+
+def test_two_gloo_ranks_shard_and_agree_on_totals(tmp_path):
+    """World-size-2 run on CPU: each rank takes its shard; the only cross-rank traffic is the
+    benchmark's timing reduction (max) and a token count (sum)."""
+    code = r'''
+import os, torch, torch.distributed as dist
+from redline_llm_b200.engine import shard_requests
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+mine = shard_requests(512, world, rank)
+t = torch.tensor([float(len(mine)), 1.0 + rank])
+dist.all_reduce(t[:1], op=dist.ReduceOp.SUM)
+dist.all_reduce(t[1:], op=dist.ReduceOp.MAX)
+assert t[0].item() == 512 and t[1].item() == world, t
+assert mine[0] == rank and mine[1] == rank + world
+dist.barrier(); dist.destroy_process_group()
+print("shard-ok %d\n" % rank, end="", flush=True)
+'''
+    script = tmp_path / "two_ranks.py"
+    script.write_text(code)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29731", str(script)],
+                       capture_output=True, text=True, env=env, timeout=240)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert (r.stdout + r.stderr).count("shard-ok") == 2
