@@ -190,6 +190,144 @@ class AttentionWorkload:
         return float(np.abs(oracle.half_bits_to_f64(got) - ref).max())
 
 
+class DecodeStepWorkload:
+    """Config 5: one decode step of a random-init Qwen2.5-1.5B-architecture model (28 layers, hidden 1536,
+    FFN 8960, 12 Q / 2 KV heads, d=128, vocab 151936, FP16 ~N(0,0.02)) over 512 sequences - 480 with contexts
+    U[1024,8192] and 32 of 32768 tokens - sharded evenly over the ranks and decoded in waves of 64 (the
+    engine's largest CUDA-graph bucket). One step = one new token for every sequence of the job. The KV
+    cache is filled with seeded ~N(0,1) values in place of a prompt pass (prompt ingestion is not the
+    measured path)."""
+    name = "decode_step_qwen2.5-1.5b_512seq_ctx1024-8192+32x32768"
+    TOTAL, LONG, WAVE, NEW = 512, 32, 64, 256
+
+    def __init__(self, rank: int, world: int, new_tokens: int = 256):
+        import torch
+        from redline_llm_b200.engine import Engine, ModelConfig, ModelWeights, blocks_for_tokens, shard_requests
+        self.torch = torch
+        ctx = np.concatenate([wl.randint(wl.SEED_STEP, self.TOTAL - self.LONG, 1024, 8192),
+                              np.full(self.LONG, 32768, np.int32)])
+        ctx = ctx[wl.permutation(wl.SEED_STEP + 1, self.TOTAL)]
+        mine = [int(ctx[i]) for i in shard_requests(self.TOTAL, world, rank)]
+        self.cfg = ModelConfig()
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.weights = ModelWeights(self.cfg, dev, seed=0x5EED)
+        self.engines, self.lens = [], []
+        max_seq = 32768 + new_tokens + 16
+        for w0 in range(0, len(mine), self.WAVE):
+            wave = mine[w0:w0 + self.WAVE]
+            blocks = sum(blocks_for_tokens(c + new_tokens) for c in wave) + 8
+            gb = blocks * self.cfg.block_bytes() / (1 << 30)
+            e = Engine(kv_pool_gb=gb, max_batch=self.WAVE, max_seq_len=max_seq, config=self.cfg, weights=self.weights,
+                       device=dev.index, graph_buckets=[64])
+            for j, c in enumerate(wave):
+                e.add_synthetic_request(c, new_tokens, seed=wl.SEED_STEP + 1000 * rank + w0 + j)
+            self.engines.append(e)
+            self.lens.append(wave)
+        self.tokens_per_step = len(mine)
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * 6 + 1)  # 6 own kernels per layer + final norm
+        self.h2d = self.d2h = 0
+
+    def step(self):  # inputs already resident: graph replays only
+        for e in self.engines:
+            e.exec.run(self.WAVE)
+
+    def step_e2e(self):  # the public API: host mirrors -> H2D -> replay -> D2H of the sampled tokens
+        self.h2d = self.d2h = 0
+        for e in self.engines:
+            e.step()
+            self.h2d += e.exec.h2d_bytes
+            self.d2h += 8 * self.WAVE
+
+    def profile_attention(self):
+        """Eager pass with CUDA events around every attention launch; returns (mean seconds per launch,
+        mean algorithmic bytes per launch)."""
+        torch = self.torch
+        secs, nbytes = [], []
+        for e in self.engines:
+            lens = e.exec.seq_lens[:self.WAVE].cpu().numpy()
+            e.exec.attention_events = []
+            e.exec.enqueue_decode(self.WAVE)
+            torch.cuda.synchronize()
+            secs += [a.elapsed_time(b) * 1e-3 for a, b in e.exec.attention_events]
+            nbytes += [wl.attention_bytes(lens)] * len(e.exec.attention_events)
+            e.exec.attention_events = None
+        return float(np.mean(secs)), float(np.mean(nbytes))
+
+
+def cpu_decode_step(w: "DecodeStepWorkload", rows: int, use_ref: bool):
+    """One decode step of `rows` sequences of wave 0 on the host cores: the reference's CPU functions
+    (tests/reference, compiled into oracle/_ref) for every non-GEMM stage - or this repository's C
+    restatement when those were never compiled - and BLAS FP32 GEMMs rounded to FP16. Returns
+    (seconds, tokens, logits) with weight conversion and cache download kept outside the timed part."""
+    import oracle
+    torch = w.torch
+    e, cfg = w.engines[0], w.cfg
+    ex = e.exec
+    ref = oracle.ref() if use_ref else None
+    own = oracle.own()
+    threads = ref.hardware_threads() if ref is not None else own.threads()
+    u16 = lambda t: t.detach().cpu().numpy().view(np.uint16)
+    f32 = lambda bits: np.ascontiguousarray(bits).view(np.float16).astype(np.float32)
+    h16 = lambda a: a.astype(np.float16).view(np.uint16)
+    ids = ex.ids[:rows].cpu().numpy()
+    pos = ex.positions[:rows].cpu().numpy()
+    lens = ex.seq_lens[:rows].cpu().numpy()
+    tables = ex.tables[:rows].cpu().numpy()
+    used = np.unique(tables[tables > 0])
+    remap = np.zeros(int(tables.max()) + 1, np.int32)
+    remap[used] = np.arange(1, len(used) + 1, dtype=np.int32)
+    ctab = np.ascontiguousarray(remap[tables])
+    mb = (int(lens.max()) + 15) // 16
+    ctab = np.ascontiguousarray(ctab[:, :mb])
+    idx = torch.as_tensor(np.concatenate([[0], used]), device=ex.pool.device)
+    pools = [u16(ex.pool[li].index_select(0, idx)).reshape(-1).copy() for li in range(cfg.layers)]
+    W = [{k: (f32(u16(v)) if v.dim() == 2 else u16(v).copy()) for k, v in L.items()} for L in w.weights.layers]
+    for L, T in zip(W, w.weights.layers):
+        L["qkv_bias"] = f32(u16(T["qkv_bias"]))
+    embed = u16(w.weights.embed)
+    head = f32(embed)
+    fin = u16(w.weights.final_norm).copy()
+
+    def norm(x, wt):
+        return ref.rmsnorm(x, wt, cfg.eps, threads) if ref is not None else own.rmsnorm(x, wt, cfg.eps)
+
+    def norm_res(res, x, wt):
+        o = ref.rmsnorm_residual(res, x, wt, cfg.eps, 0.0, threads) if ref is not None else own.rmsnorm_residual(res, x, wt, cfg.eps)
+        return o[0], o[1]
+
+    def rope(hb, heads):
+        return ref.rope(hb, pos, heads, cfg.head_dim, cfg.rope_theta, threads) if ref is not None else own.rope(hb, pos, heads, cfg.head_dim, cfg.rope_theta)
+
+    t0 = time.perf_counter()
+    x = np.ascontiguousarray(embed[ids])
+    mlp = None
+    for li, L in enumerate(W):
+        if li == 0:
+            normed = norm(x, L["in_norm"])
+        else:
+            normed, x = norm_res(x, mlp, L["in_norm"])
+        qkv = h16(f32(normed) @ L["qkv"].T + L["qkv_bias"])
+        q = rope(np.ascontiguousarray(qkv[:, :cfg.q_width]), cfg.q_heads)
+        k = rope(np.ascontiguousarray(qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width]), cfg.kv_heads)
+        v = np.ascontiguousarray(qkv[:, cfg.q_width + cfg.kv_width:])
+        (ref or own).kv_scatter(pools[li], k.reshape(-1), v.reshape(-1), cfg.kv_width, cfg.kv_width, ctab, mb, pos,
+                                cfg.kv_heads, cfg.head_dim)
+        if ref is not None:
+            att = ref.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim, ex.scale, threads)
+        else:
+            att = own.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim, ex.scale)
+        mlp = h16(f32(att) @ L["o"].T)
+        normed, x = norm_res(x, mlp, L["post_norm"])
+        gu = h16(f32(normed) @ L["gate_up"].T)
+        act = ref.silu_mul(gu, threads) if ref is not None else own.silu_mul(gu)
+        mlp = h16(f32(act) @ L["down"].T)
+    normed, x = norm_res(x, mlp, fin)
+    logits = f32(normed) @ head.T
+    tokens = (ref or own).argmax(h16(logits))
+    dt = time.perf_counter() - t0
+    return dt, tokens, logits, threads, ("reference" if ref is not None else "port")
+
+
 def kernel_table(peak):
     """Achieved GB/s of every kernel at its configuration shape (and a large-T shape where the stated one is
     latency-bound and L2-resident), CUDA-event timed, rotating buffers larger than L2."""
@@ -268,33 +406,172 @@ def cpu_attention(sample_seqs: int, use_ref: bool):
     return nbytes / dt / 1e9, cores, kind, f"{n} of 64 sequences of config 3, one layer pool, FP64 two-pass softmax", dt
 
 
+def reference_line(args, metric, unit, value, ms_per_step, config, cpu, dtype):
+    return {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if unit == "tok/s" else "weak", "vs_baseline": None, "dtype": dtype,
+            "data": "synthetic", "config": config, "cpu_baseline": cpu,
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
 def run_reference_arm(args, rank, world):
+    """The reference's own CPU implementation of the path on the host cores (rank 0 only)."""
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    n = min(64, max(8, 2 * cores))
-    vals = []
-    for _ in range(args.warmup):
-        cpu_attention(n, True)
-    for _ in range(args.steps):
-        gbs, cores_used, kind, sample, dt = cpu_attention(n, True)
-        vals.append((gbs, dt))
-    total_t = sum(d for _, d in vals)
-    value = float(np.mean([g for g, _ in vals]))
+    if args.workload == "attention":
+        cores = os.cpu_count() or 1
+        n = min(64, max(8, 2 * cores))
+        for _ in range(args.warmup):
+            cpu_attention(n, True)
+        runs = [cpu_attention(n, True) for _ in range(args.steps)]
+        value = float(np.mean([r[0] for r in runs]))
+        cpu = {"value": round(value, 4), "unit": "GB/s", "cores": runs[0][1], "kind": runs[0][2], "sample": runs[0][3]}
+        print(json.dumps(reference_line(
+            args, METRIC, "GB/s", round(value, 4), round(1e3 * float(np.mean([r[4] for r in runs])), 3),
+            {"workload": AttentionWorkload.name, "batch": 64, "note": "each step is a bounded sample on the host cores"},
+            cpu, "f64")), flush=True)
+        return
+    # decode step: the model and its KV cache live on the GPU only as a generator of the synthetic inputs;
+    # every timed operation below runs on the host cores.
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "the synthetic model and cache are generated on a GPU"}))
+        return
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    w = DecodeStepWorkload(0, 64, new_tokens=8)  # 8 sequences: one small wave is enough for the sample
+    for e in w.engines:
+        e.step()
+    rows = 2
+    steps = max(1, min(args.steps, 3))
+    runs = [cpu_decode_step(w, rows, True) for _ in range(steps)]
+    dt = float(np.mean([r[0] for r in runs]))
+    value = rows / dt
+    cpu = {"value": round(value, 4), "unit": "tok/s", "cores": runs[0][3], "kind": runs[0][4],
+           "sample": f"{rows} sequences x 1 decode step, all 28 layers, contexts {w.lens[0][:rows]}, BLAS FP32 GEMMs"}
+    print(json.dumps(reference_line(args, "decode tok/s", "tok/s", round(value, 4), round(1e3 * dt, 3),
+                                    {"workload": DecodeStepWorkload.name, "note": "each step is a bounded sample "
+                                     "(2 sequences) of the workload on the host cores"}, cpu, "f64 kernels / f32 GEMM")),
+          flush=True)
+
+
+def run_attention(args, rank, local_rank, world, barrier, dist):
+    import torch
+    w = AttentionWorkload(rank, args.layers)
+    max_abs = w.check()
+    peak, peak_kind = measured_peaks()
+    step = w.step if args.no_graph else graphed(w.step)
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        ms = time_region(step, args.steps, barrier)
+    for _ in range(2):
+        w.step_e2e()
+    barrier()
+    ms_e2e = time_region(w.step_e2e, args.steps, barrier)
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    health = w.K.attention_health()
+    if rank != 0:
+        return
+    total_bytes = w.bytes_per_step() * world
+    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    per_launch_s = ms * 1e-3 / (args.steps * args.layers)
+    achieved = w.bytes_per_launch / per_launch_s / 1e9
     line = {
-        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * total_t / max(1, args.steps), 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": AttentionWorkload.name, "batch": 64, "layers_per_step": LAYERS,
-                   "note": "each step is a bounded sample of the workload on the host cores"},
-        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": cores_used, "kind": kind, "sample": sample},
-        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+        "config": {"workload": w.name, "batch_per_gpu": 64, "layers_per_step": args.layers,
+                   "kv_tokens_per_layer": w.tokens,
+                   "cold_l2": f"{args.layers} layer pools walked per step ({args.layers * 0.134:.1f} GB)",
+                   "launch": "eager" if args.no_graph else "cuda_graph_replay",
+                   "pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
+        "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
+                     "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_launch": w.bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 3)},
+        "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
+        "gpu_launches": w.launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "check": {"attention_max_abs_vs_cpu_checker": max_abs, "attention_health": health},
     }
+    if not args.no_kernel_table:
+        line["kernels"] = kernel_table(peak)
+    if not args.no_cpu_baseline and world == 1:
+        cores = os.cpu_count() or 1
+        gbs, cores_used, kind, sample, dt = cpu_attention(min(64, max(8, 2 * cores)), True)
+        line["cpu_baseline"] = {"value": round(gbs, 4), "unit": "GB/s", "cores": cores_used, "kind": kind,
+                                "sample": sample, "seconds": round(dt, 2)}
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------- main
+def run_decode_step(args, rank, local_rank, world, barrier, dist):
+    import torch
+    from redline_llm_b200 import kernels as K
+    need = args.warmup + args.steps + 8
+    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need))
+    peak, peak_kind = measured_peaks()
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.warmup):
+            w.step_e2e()          # also uploads real inputs for the resident-input timing below
+        barrier()
+        ms = time_region(w.step, args.steps, barrier)
+    barrier()
+    ms_e2e = time_region(w.step_e2e, args.steps, barrier)
+    att_s, att_bytes = w.profile_attention()
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    health = K.attention_health()
+    if rank != 0:
+        return
+    tokens = DecodeStepWorkload.TOTAL
+    value = tokens * args.steps / (ms * 1e-3)
+    e2e = tokens * args.steps / (ms_e2e * 1e-3)
+    achieved = att_bytes / att_s / 1e9
+    line = {
+        "metric": "decode tok/s", "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+        "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
+                   "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
+                   "launch": "one CUDA-graph replay per wave", "gemm": "library (cuBLAS via torch.matmul), FP16",
+                   "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
+                   "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
+        "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
+                     "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                     "traffic": None, "algorithmic_bytes_per_launch": int(att_bytes),
+                     "us_per_launch": round(att_s * 1e6, 2),
+                     "timed": "CUDA events around each attention launch of an eager pass over the same step"},
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
+        "gpu_launches": w.launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "check": {"attention_health": health},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        dt, cpu_tok, cpu_logits, threads, kind = cpu_decode_step(w, 2, True)
+        e = w.engines[0]
+        e.exec.enqueue_decode(DecodeStepWorkload.WAVE)   # same inputs as the CPU sample saw
+        torch.cuda.synchronize()
+        gpu_logits = e.exec.logits[:2].float().cpu().numpy()
+        gpu_tok = e.exec.tokens[:2].cpu().numpy()
+        line["cpu_baseline"] = {"value": round(2 / dt, 4), "unit": "tok/s", "cores": threads, "kind": kind,
+                                "sample": "2 sequences of wave 0 x 1 decode step, all 28 layers", "seconds": round(dt, 2)}
+        line["check"].update({"step_logits_max_abs_vs_cpu": float(np.abs(gpu_logits - cpu_logits).max()),
+                              "step_logits_scale": float(np.abs(cpu_logits).max()),
+                              "greedy_tokens_equal_cpu": bool((gpu_tok == cpu_tok).all())})
+    if not args.no_kernel_table:
+        del w
+        torch.cuda.empty_cache()
+        line["kernels"] = kernel_table(peak)
+    print(json.dumps(line), flush=True)
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -302,13 +579,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="attention", choices=["attention"])
+    ap.add_argument("--workload", default="decode_step", choices=["decode_step", "attention"])
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="eager launches instead of CUDA-graph replay")
-    ap.add_argument("--layers", type=int, default=LAYERS, help="layer pools walked per step (28 = the model)")
+    ap.add_argument("--no-graph", action="store_true", help="attention workload: eager launches instead of graph replay")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="attention workload: layer pools walked per step")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -332,61 +610,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    w = AttentionWorkload(rank, args.layers)
-    max_abs = w.check()
-    peak, peak_kind = measured_peaks()
-
-    step = w.step if args.no_graph else graphed(w.step)
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    with ClockSampler(local_rank) as clocks:
-        ms = time_region(step, args.steps, barrier)
-    for _ in range(2):
-        w.step_e2e()
-    barrier()
-    t0 = time.perf_counter()
-    ms_e2e_dev = time_region(w.step_e2e, args.steps, barrier)
-    ms_e2e = max(ms_e2e_dev, 0.0)
-    _ = time.perf_counter() - t0
-
-    if world > 1:
-        t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
-    health = w.K.attention_health()
-
-    if rank == 0:
-        total_bytes = w.bytes_per_step() * world
-        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
-        e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
-        per_launch_s = ms * 1e-3 / (args.steps * args.layers)
-        achieved = w.bytes_per_launch / per_launch_s / 1e9
-        line = {
-            "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": w.name, "batch_per_gpu": 64, "layers_per_step": args.layers,
-                       "kv_tokens_per_layer": w.tokens, "cold_l2": "28 layer pools (2.1 GB) walked per step, larger than L2",
-                       "launch": "eager" if args.no_graph else "cuda_graph_replay",
-                       "pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
-            "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
-                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                         "peak_kind": f"of {peak_kind}", "traffic": None,
-                         "algorithmic_bytes_per_launch": w.bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 3)},
-            "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
-            "gpu_launches": w.launches_per_step * args.steps,
-            "clocks": clocks.summary(),
-            "check": {"attention_max_abs_vs_cpu_checker": max_abs, "attention_health": health},
-        }
-        if not args.no_kernel_table:
-            line["kernels"] = kernel_table(peak)
-        if not args.no_cpu_baseline and world == 1:
-            cores = os.cpu_count() or 1
-            gbs, cores_used, kind, sample, dt = cpu_attention(min(64, max(8, 2 * cores)), True)
-            line["cpu_baseline"] = {"value": round(gbs, 4), "unit": "GB/s", "cores": cores_used, "kind": kind,
-                                    "sample": sample, "seconds": round(dt, 2)}
-        print(json.dumps(line), flush=True)
+    if args.workload == "attention":
+        run_attention(args, rank, local_rank, world, barrier, dist)
+    else:
+        run_decode_step(args, rank, local_rank, world, barrier, dist)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
