@@ -22,10 +22,12 @@
 //    atomic counter and the LAST one to arrive merges all partials of the item
 //    in CTA order. Nobody waits for anybody, and the merge order is fixed, so
 //    results are bit-reproducible run to run whoever arrives last.
-//  * K/V pages are fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle) into
-//    a private 3-deep ring per warp, completion tracked by mbarriers; no warp
-//    waits on another except at item boundaries. Loads never use cluster
-//    multicast and never touch another GPU's memory.
+//  * K/V pages are fetched by TMA - one cp.async.bulk.tensor per page brings the
+//    K tile and the V tile of a head (8 KiB, 128-byte swizzle, so the ldmatrix
+//    reads are bank-conflict free) - into a private 3-deep ring per warp, with
+//    completion tracked by mbarriers; no warp waits on another except at item
+//    boundaries. Loads never use cluster multicast and never touch another
+//    GPU's memory.
 //  * The 6-query x 16-token dot products and the P.V products run on tensor
 //    cores (mma.sync m16n8k16, FP16 in / FP32 accumulate) in the transposed
 //    form S^T = K.Q^T, O^T = V^T.P^T so the 6 queries sit in the N=8 dimension
@@ -37,7 +39,6 @@
 //    rounded to FP16 for the P.V product, their sum is kept in FP32.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -92,7 +93,6 @@ struct Params {
   float scale_log2e;
   int* meta;        // workspace meta
   float* partials;  // workspace partial records
-  const half* pool; // the layer's pool slice (1-D bulk-copy experiment path)
   unsigned long long* timeline;  // diagnostics build only
 };
 
@@ -128,26 +128,13 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, int parity) {
   }
   return true;
 }
-// One 16-row x 64-half (2 KiB) box of the pool, 128-byte swizzled, into this CTA's shared memory.
-__device__ __forceinline__ void TmaLoadBox(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                           uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void TmaLoadBox4(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar) {
+// One page of one KV head - its K tile and its V tile, 8 KiB - in a single tensor copy into this CTA's
+// shared memory, 128-byte swizzled; completion is counted in bytes on `bar`. No cluster multicast.
+__device__ __forceinline__ void TmaLoadPage(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%2, %2, %2, %3}], [%4];" ::"r"(dst),
       "l"(map), "r"(0), "r"(tile), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, int bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
 #ifdef RL_ATTN_TIMELINE
@@ -230,8 +217,7 @@ __device__ __forceinline__ Cursor Locate(long long t, const int* prefix, int num
 // --------------------------------------------------------------- kernel
 
 __global__ void __launch_bounds__(kThreads, 1)
-PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap pool_map,
-                          const __grid_constant__ CUtensorMap tile_map, const int tma_mode) {
+PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap tile_map) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -249,7 +235,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   const int num_seqs = p.num_seqs;
   RL_STAMP(0);
   if (tid == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(tma_mode == 0 ? &pool_map : &tile_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
   }
 
   // ---- page prefix over sequences (every CTA computes the same table) ----
@@ -301,45 +287,32 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
   bool failed = false;
 
   // Page metadata is looked up 32 pages at a time, one page per lane: lane j of batch b holds the
-  // pool row of the K tile of this warp's page 32b + j (the V tile is heads*16 rows further).
-  // The block-table read of a batch is issued a whole batch ahead of its first use.
-  auto fetch_rows = [&](int batch) -> int {
+  // index of the K tile of this warp's page 32b + j, counted in 4 KiB (block, kv, head) tiles; the V
+  // tile is `heads` tiles further. The block-table read of a batch is issued a whole batch ahead of
+  // its first use.
+  auto fetch_tiles = [&](int batch) -> int {
     const int k = 32 * batch + lane;
     if (k >= n_mine) return 0;
     const Cursor c = Locate(share_begin + warp + kWarps * k, prefix, num_seqs, heads);
     const int block = __ldg(p.tables + static_cast<int64_t>(c.seq) * p.max_blocks + c.page);
-    return (block * 2 * heads + c.head) * kKvBlock;
+    return block * 2 * heads + c.head;
   };
-  int rows_cur = fetch_rows(0);
-  int rows_next = n_mine > 32 ? fetch_rows(1) : 0;
-  const int v_row_delta = heads * kKvBlock;
+  int tiles_cur = fetch_tiles(0);
+  int tiles_next = n_mine > 32 ? fetch_tiles(1) : 0;
   int n_issue = 0, n_use = 0;
   auto issue_one = [&]() {
-    const int row_k = __shfl_sync(0xffffffffu, rows_cur, n_issue & 31);
+    const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, n_issue & 31);
     if (lane == 0) {
       const int stage = n_issue % kStages;
       const uint32_t dst = my_ring + stage * kStageBytes;
       const uint32_t bar = my_bars + stage * 8;
       MbarExpectTx(bar, kStageBytes);
-      if (tma_mode == 0) {
-        TmaLoadBox(dst, &pool_map, 0, row_k, bar);
-        TmaLoadBox(dst + 2048, &pool_map, 64, row_k, bar);
-        TmaLoadBox(dst + 4096, &pool_map, 0, row_k + v_row_delta, bar);
-        TmaLoadBox(dst + 6144, &pool_map, 64, row_k + v_row_delta, bar);
-      } else if (tma_mode == 1) {
-        TmaLoadBox4(dst, &tile_map, row_k >> 4, bar);
-        TmaLoadBox4(dst + 4096, &tile_map, (row_k + v_row_delta) >> 4, bar);
-      } else if (tma_mode == 2) {
-        TmaLoadBox4(dst, &tile_map, row_k >> 4, bar);
-      } else {
-        BulkLoad(dst, p.pool + static_cast<int64_t>(row_k) * kHeadDim, kPageBytes, bar);
-        BulkLoad(dst + 4096, p.pool + static_cast<int64_t>(row_k + v_row_delta) * kHeadDim, kPageBytes, bar);
-      }
+      TmaLoadPage(dst, &tile_map, tile_k, bar);
     }
     ++n_issue;
     if ((n_issue & 31) == 0) {
-      rows_cur = rows_next;
-      rows_next = fetch_rows((n_issue >> 5) + 1);
+      tiles_cur = tiles_next;
+      tiles_next = fetch_tiles((n_issue >> 5) + 1);
     }
   };
 #pragma unroll 1
@@ -357,13 +330,9 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap po
     for (int j = 0; j < 4; ++j) {
       koff[j] = k_row * 128 + (((2 * j + k_sel) ^ (k_row & 7)) << 4);
       voff[j] = 4096 + v_row * 128 + (((2 * j + v_sel) ^ (v_row & 7)) << 4);
-      if (tma_mode == 3) {  // linear [16][128] tiles
-        koff[j] = k_row * 256 + ((2 * j + k_sel) << 4);
-        voff[j] = 4096 + v_row * 256 + ((2 * j + v_sel) << 4);
-      }
     }
   }
-  const uint32_t hi_delta = tma_mode == 3 ? 128u : 2048u;
+  constexpr uint32_t hi_delta = 2048;  // dims 64..127 of a tile sit one 2 KiB box further
   RL_STAMP(1);
 
   // ---- walk the share one (sequence, head) segment at a time ----
@@ -686,32 +655,17 @@ int EnsureReady(DeviceState** out_state) {
   return RL_OK;
 }
 
-// The pool slice as a 2-D tensor of 256-byte rows (one token row of one head);
-// boxes are 16 rows x 64 halves, 128-byte swizzled. The row count is not part
-// of the launch contract, so the map claims the largest extent a 180 GB device
-// can hold; only rows of real pages are ever requested.
-int EncodePoolMap(const void* pool, CUtensorMap* map) {
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kHeadDim), 1ull << 30};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kHeadDim) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kKvBlock)};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(pool), dims,
-                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_attention: tensor map encode failed (CUresult %d)", static_cast<int>(r));
-  return RL_OK;
-}
-
-// The same memory as [tile][dim-half][token][64 halves]: one box {64, 16, 2, 1} is a whole
-// (block, kv, head) tile; with a box of heads+1 tiles walked at stride `heads` it is the K tile and
-// the V tile of one head in a single copy (tile_stride > 1).
+// The pool slice as the 4-D tensor [tile][dim-half][token][64 halves] (strides 4096, 128, 256, 2
+// bytes): a box {64, 16, 2, 1} is one whole (block, kv, head) tile laid out as two 128-byte-swizzled
+// 16 x 128 B boxes. The box spans heads+1 tiles walked at element stride `heads`, so one copy brings
+// the K tile and the V tile of one head (tiles t and t + heads). The tile count is not part of the
+// launch contract, so the map claims more tiles than a 180 GB device can hold; only tiles of real
+// pages are ever requested.
 int EncodeTileMap(const void* pool, int tile_stride, CUtensorMap* map) {
   const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kPageBytes)};
-  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 2,
-                             static_cast<cuuint32_t>(tile_stride > 1 ? tile_stride + 1 : 1)};
-  const cuuint32_t estr[4] = {1, 1, 1, static_cast<cuuint32_t>(tile_stride > 1 ? tile_stride : 1)};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 2, static_cast<cuuint32_t>(tile_stride + 1)};
+  const cuuint32_t estr[4] = {1, 1, 1, static_cast<cuuint32_t>(tile_stride)};
   const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(pool), dims,
                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -795,10 +749,10 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: the pool slice must be 16-byte aligned");
   DeviceState* st;
   if ((rc = EnsureReady(&st)) != RL_OK) return rc;
-  CUtensorMap map, tile_map;
-  if ((rc = EncodePoolMap(kv_pool_layer, &map)) != RL_OK) return rc;
-  static const int tma_mode = [] { const char* e = getenv("RL_ATTN_TMA_MODE"); return e ? atoi(e) : 0; }();
-  if ((rc = EncodeTileMap(kv_pool_layer, tma_mode == 2 ? num_kv_heads : 1, &tile_map)) != RL_OK) return rc;
+  if (num_kv_heads > 8)
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode: at most 8 KV heads (tensor-copy element stride)");
+  CUtensorMap tile_map;
+  if ((rc = EncodeTileMap(kv_pool_layer, num_kv_heads, &tile_map)) != RL_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   for (int first = 0; first < num_seqs; first += kMaxSeqsPerLaunch) {
     const int n = num_seqs - first < kMaxSeqsPerLaunch ? num_seqs - first : kMaxSeqsPerLaunch;
@@ -815,12 +769,11 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     p.scale_log2e = scale * 1.4426950408889634f;
     p.meta = static_cast<int*>(st->workspace);
     p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
-    p.pool = static_cast<const half*>(kv_pool_layer);
     p.timeline = nullptr;
 #ifdef RL_ATTN_TIMELINE
     p.timeline = static_cast<unsigned long long*>(g_timeline);
 #endif
-    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, map, tile_map, tma_mode);
+    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
   }
   return LaunchStatus("paged_attention_decode");
 }
