@@ -103,6 +103,31 @@ int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const vo
                                      float scale, void* stream);
 
 /*
+ * The attention launcher for hosts that must not allocate: same arguments, same kernel and
+ * bit-identical results as rl_launch_paged_attention_decode, but the split/merge scratch is a
+ * ~1.6 MB device array built into the library image (held by every GPU that loads the library
+ * until the process exits) instead of a cudaMalloc'd workspace. Meant for callers that cannot
+ * call cudaMalloc - a process with a sealed device-memory budget, a plugin inside a host that
+ * forbids allocation after start-up. It calls no cudaMalloc, cudaFree or allocating library
+ * routine. Limits: at most 1024 sequences per call (RL_E_TOO_LARGE beyond that; the allocating
+ * launcher walks larger batches in chunks) and a device of at most 256 SMs.
+ * The first call on a device resolves the array's device address, opts the kernel in to its
+ * shared memory and looks up the tensor-map encoder; make that first call before any stream
+ * capture. Every call clears the array's counters in stream order and then reuses the same
+ * array (it keeps the previous call's contents otherwise), so two calls of THIS entry point that
+ * overlap on one GPU - issued on different streams, say - race on it; serialise them. The
+ * allocating launcher has its own workspace and does not interfere. rl_attention_health reports
+ * on the allocating launcher's workspace only.
+ * This entry point has no counterpart in the reference.
+ */
+int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, const void* q,
+                                            int64_t q_row_stride, const void* kv_pool_layer,
+                                            const int32_t* block_tables, const int32_t* seq_lens,
+                                            int32_t num_seqs, int32_t max_blocks_per_seq,
+                                            int32_t num_q_heads, int32_t num_kv_heads,
+                                            int32_t head_dim, float scale, void* stream);
+
+/*
  * Device-side health of the attention kernel on the current device: 0 when every
  * page load it waited for arrived, 1 when a bounded wait gave up (the output of
  * that launch is then undefined). Synchronises the device; meant for tests and

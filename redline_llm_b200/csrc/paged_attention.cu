@@ -778,6 +778,124 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
   return LaunchStatus("paged_attention_decode");
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the attention launcher.
+//
+// Some hosts may not allocate device memory at all: a process that was handed a
+// fixed memory budget and a sealed allocator, a plugin running inside somebody
+// else's CUDA context under a "no cudaMalloc after start-up" rule, a thread that
+// is already inside stream capture when it first needs the kernel. For them the
+// split/merge scratch lives in the library image itself: a file-scope device
+// array of kStaticScratchBytes, resident on every GPU that loads the library
+// until the process exits. Inputs and outputs are still the caller's.
+// ---------------------------------------------------------------------------
+namespace rl {
+namespace attn {
+
+constexpr size_t kStaticScratchBytes = kWorkspaceBytes;  // ~1.6 MB: flag, tickets, 2 records x 256 CTAs
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticState {
+  bool ready = false;
+  void* scratch = nullptr;  // DEVICE address of g_static_scratch on this device
+  int ctas = 0;
+};
+StaticState g_static_state[kMaxDevices];
+
+// Once per device, with that device current. In host code the name g_static_scratch is only a
+// handle for the runtime, not a device address - handing it to a kernel would fault or, where the
+// GPU can reach host memory, quietly use the wrong bytes - so the real address is asked for here.
+int EnsureStaticReady(StaticState** out_state) {
+  const int dev = CurrentDeviceIndex();
+  StaticState& st = g_static_state[dev];
+  *out_state = &st;
+  if (st.ready) return RL_OK;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (st.ready) return RL_OK;
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return Fail(e != cudaSuccess ? static_cast<int>(e) : RL_E_WORKSPACE,
+                  "paged_attention (static): cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const DeviceFacts& facts = CurrentDeviceFacts();
+  if (facts.max_smem_optin < kSmemBytes)
+    return Fail(RL_E_WORKSPACE, "paged_attention (static): %d B of shared memory per block, %d needed",
+                facts.max_smem_optin, kSmemBytes);
+  if (facts.sm_count > kMaxCtas)
+    return Fail(RL_E_TOO_LARGE, "paged_attention (static): %d SMs, the built-in scratch covers %d CTAs",
+                facts.sm_count, kMaxCtas);
+  cudaError_t e = cudaFuncSetAttribute(PagedAttentionSplitKernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess)
+    return Fail(static_cast<int>(e), "paged_attention (static): shared-memory opt-in: %s", cudaGetErrorString(e));
+  void* ptr = nullptr;
+  e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+  if (e != cudaSuccess || !ptr)
+    return Fail(e != cudaSuccess ? static_cast<int>(e) : RL_E_WORKSPACE,
+                "paged_attention (static): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+  st.scratch = ptr;
+  st.ctas = facts.sm_count;
+  st.ready = true;
+  return RL_OK;
+}
+
+}  // namespace attn
+}  // namespace rl
+
+extern "C" int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, const void* q,
+                                                       int64_t q_row_stride, const void* kv_pool_layer,
+                                                       const int32_t* block_tables, const int32_t* seq_lens,
+                                                       int32_t num_seqs, int32_t max_blocks_per_seq,
+                                                       int32_t num_q_heads, int32_t num_kv_heads,
+                                                       int32_t head_dim, float scale, void* stream) {
+  using namespace rl;
+  using namespace rl::attn;
+  if (num_seqs <= 0) return RL_OK;
+  int rc = CheckContract("paged_attention_decode_static", out, out_row_stride, q, q_row_stride, kv_pool_layer,
+                         block_tables, seq_lens, max_blocks_per_seq, num_q_heads, num_kv_heads, head_dim);
+  if (rc != RL_OK) return rc;
+  if (num_seqs > kMaxSeqsPerLaunch)
+    return Fail(RL_E_TOO_LARGE, "paged_attention_decode_static: %d sequences, at most %d per call", num_seqs,
+                kMaxSeqsPerLaunch);
+  if (num_q_heads != num_kv_heads * kGroup)
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode_static: needs 6 query heads per KV head");
+  if (num_kv_heads > 8)
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode_static: at most 8 KV heads");
+  if ((q_row_stride & 1) || (reinterpret_cast<uintptr_t>(q) & 3) || !Aligned16(kv_pool_layer))
+    return Fail(RL_E_BAD_SHAPE, "paged_attention_decode_static: q rows 4-byte, pool slice 16-byte aligned");
+  StaticState* st;
+  if ((rc = EnsureStaticReady(&st)) != RL_OK) return rc;
+  CUtensorMap tile_map;
+  if ((rc = EncodeTileMap(kv_pool_layer, num_kv_heads, &tile_map)) != RL_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left. Partial records are fully rewritten before they
+  // are read; the error flag and the ticket counters must start at zero, so they are cleared here,
+  // in stream order, before the kernel.
+  const cudaError_t e = cudaMemsetAsync(st->scratch, 0, sizeof(int) * kMetaInts, s);
+  if (e != cudaSuccess)
+    return Fail(static_cast<int>(e), "paged_attention_decode_static: clearing the counters: %s", cudaGetErrorString(e));
+  Params p;
+  p.out = static_cast<half*>(out);
+  p.out_stride = out_row_stride;
+  p.q = static_cast<const half*>(q);
+  p.q_stride = q_row_stride;
+  p.tables = block_tables;
+  p.seq_lens = seq_lens;
+  p.num_seqs = num_seqs;
+  p.max_blocks = max_blocks_per_seq;
+  p.kv_heads = num_kv_heads;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.meta = static_cast<int*>(st->scratch);
+  p.partials = reinterpret_cast<float*>(static_cast<int*>(st->scratch) + kMetaInts);
+  p.timeline = nullptr;
+  PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
+  return LaunchStatus("paged_attention_decode_static");
+}
+
 extern "C" int rl_launch_paged_attention_decode_check(void* out, int64_t out_row_stride, const void* q,
                                                       int64_t q_row_stride, const void* kv_pool_layer,
                                                       const int32_t* block_tables, const int32_t* seq_lens,

@@ -20,7 +20,7 @@ ABI_SYMBOLS = (
     "rl_version", "rl_last_error", "rl_kernels_init", "rl_launch_rmsnorm",
     "rl_launch_rmsnorm_residual", "rl_launch_rope_inplace", "rl_launch_kv_scatter",
     "rl_launch_paged_attention_decode", "rl_launch_paged_attention_decode_check",
-    "rl_launch_silu_mul", "rl_attention_health",
+    "rl_launch_silu_mul", "rl_attention_health", "rl_launch_paged_attention_decode_static",
 )
 
 
@@ -48,6 +48,7 @@ def lib() -> C.CDLL:
         att = [vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]
         L.rl_launch_paged_attention_decode.argtypes = att
         L.rl_launch_paged_attention_decode_check.argtypes = att
+        L.rl_launch_paged_attention_decode_static.argtypes = att
         L.rl_launch_silu_mul.argtypes = [vp, vp, i32, i32, vp]
         L.rl_attention_health.argtypes = [C.POINTER(C.c_int)]
         for name in ABI_SYMBOLS[2:]:
@@ -118,6 +119,19 @@ def launch_paged_attention_decode(out, out_row_stride, q, q_row_stride, kv_pool_
               block_tables.data_ptr(), seq_lens.data_ptr(), num_seqs, max_blocks_per_seq,
               num_q_heads, num_kv_heads, head_dim, scale, _stream(stream)),
            "LaunchPagedAttentionDecode")
+
+
+def launch_paged_attention_decode_static(out, out_row_stride, q, q_row_stride, kv_pool_layer, block_tables,
+                                         seq_lens, num_seqs, max_blocks_per_seq, num_q_heads, num_kv_heads,
+                                         head_dim, scale, stream=None, q_offset=0):
+    """Attention for callers that may not allocate device memory (a sealed memory budget, a host that
+    forbids cudaMalloc after start-up): identical results, scratch taken from a ~1.6 MB array built
+    into the library. At most 1024 sequences per call; calls overlapping on one GPU race on that array;
+    make the first call on a device outside stream capture."""
+    _check(lib().rl_launch_paged_attention_decode_static(
+        _ptr(out), out_row_stride, _ptr(q, q_offset), q_row_stride, _ptr(kv_pool_layer),
+        block_tables.data_ptr(), seq_lens.data_ptr(), num_seqs, max_blocks_per_seq, num_q_heads,
+        num_kv_heads, head_dim, scale, _stream(stream)), "LaunchPagedAttentionDecode (static scratch)")
 
 
 def attention_health() -> int:
