@@ -133,11 +133,13 @@ class AttentionWorkload:
     random-permuted block table; one step = one attention call per layer pool (28)."""
     name = "paged_attention_b64_ctx1024-1280"
 
-    def __init__(self, rank: int, layers: int = LAYERS):
+    def __init__(self, rank: int, layers: int = LAYERS, lo: int = 1024, hi: int = 1280):
         import torch
         from redline_llm_b200 import kernels as K
         self.K, self.torch, self.layers = K, torch, layers
-        c = wl.config_attention(seed=wl.SEED_ATTN + 16 * rank)
+        self.name = f"paged_attention_b64_ctx{lo}-{hi}"
+        blocks = max(8192, 64 * ((hi + 15) // 16) + 64)
+        c = wl.config_attention(seed=wl.SEED_ATTN + 16 * rank, lo=lo, hi=hi, num_blocks=blocks)
         self.c = c
         self.bytes_per_launch = wl.attention_bytes(c["seq_lens"])
         self.tokens = int(np.asarray(c["seq_lens"]).sum())
@@ -200,8 +202,9 @@ class DecodeStepWorkload:
     name = "decode_step_qwen2.5-1.5b_512seq_ctx1024-8192+32x32768"
     TOTAL, LONG, WAVE, NEW = 512, 32, 64, 256
 
-    def __init__(self, rank: int, world: int, new_tokens: int = 256):
+    def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512):
         import torch
+        self.TOTAL, self.LONG = total, total // 16
         from redline_llm_b200.engine import Engine, ModelConfig, ModelWeights, blocks_for_tokens, shard_requests
         self.torch = torch
         ctx = np.concatenate([wl.randint(wl.SEED_STEP, self.TOTAL - self.LONG, 1024, 8192),
@@ -328,18 +331,22 @@ def cpu_decode_step(w: "DecodeStepWorkload", rows: int, use_ref: bool):
     return dt, tokens, logits, threads, ("reference" if ref is not None else "port")
 
 
-def kernel_table(peak):
+def kernel_table(peak, only=None, eager=False):
     """Achieved GB/s of every kernel at its configuration shape (and a large-T shape where the stated one is
-    latency-bound and L2-resident), CUDA-event timed, rotating buffers larger than L2."""
+    latency-bound and L2-resident), CUDA-event timed over rotating buffers larger than L2. `only` keeps the
+    entries whose name contains it; `eager` launches directly instead of replaying a CUDA graph (profilers)."""
     import torch
     from redline_llm_b200 import kernels as K
     out = {}
+
+    def want(name):
+        return only is None or only in name
 
     def timed(fn, nbuf, iters=20):
         def sweep():
             for i in range(nbuf):
                 fn(i)
-        replay = graphed(sweep)
+        replay = sweep if eager else graphed(sweep)
         for _ in range(3):
             replay()
         t = time_region(replay, iters, torch.cuda.synchronize)
@@ -350,6 +357,8 @@ def kernel_table(peak):
                      "frac_of_measured_peak": round(nbytes / secs / 1e9 / peak, 4), "bytes": nbytes, "note": note}
 
     for t, note in ((64, "config 1; latency-bound, L2-resident"), (16384, "large-T, cold L2")):
+        if not want(f"rmsnorm_residual_T{t}"):
+            continue
         c = wl.config_rmsnorm(64)
         nbuf = max(2, min(64, int(3e8 // (t * 1536 * 8)) + 1))
         x = [dev(np.tile(c["x"], (t // 64, 1))) for _ in range(nbuf)]
@@ -359,24 +368,33 @@ def kernel_table(peak):
         secs = timed(lambda i: K.launch_rms_norm_residual(o[i], r[i], x[i], w, t, 1536, 1e-6), nbuf)
         report(f"rmsnorm_residual_T{t}", secs, 4 * t * 1536 * 2 + 1536 * 2, note)
         del x, r, o
-    c = wl.config_rope_scatter(64)
-    nbuf = 8
-    qkv = [dev(c["qkv"]) for _ in range(nbuf)]
-    pos, tab = dev(c["positions"]), dev(c["tables"])
-    pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
-    secs = timed(lambda i: K.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, 64, 12, 2, 128, 1e6, k_offset=1536), nbuf)
-    report("rope_T64", secs, 2 * 64 * 1792 * 2 + 256, "config 2; latency-bound")
-    secs = timed(lambda i: K.launch_kv_scatter(pool, qkv[i], qkv[i], 2048, 2048, tab, tab.shape[1], pos, 64, 2, 128,
-                                               k_offset=1536, v_offset=1792), nbuf)
-    report("kv_scatter_T64", secs, 64 * 1024 * 2 + 64 * 8, "config 2; latency-bound")
-    del pool, qkv
+    if want("rope_T64") or want("kv_scatter_T64"):
+        c = wl.config_rope_scatter(64)
+        nbuf = 8
+        qkv = [dev(c["qkv"]) for _ in range(nbuf)]
+        pos, tab = dev(c["positions"]), dev(c["tables"])
+        pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
+        if want("rope_T64"):
+            secs = timed(lambda i: K.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, 64, 12, 2, 128, 1e6,
+                                                         k_offset=1536), nbuf)
+            report("rope_T64", secs, 2 * 64 * 1792 * 2 + 256, "config 2; latency-bound")
+        if want("kv_scatter_T64"):
+            secs = timed(lambda i: K.launch_kv_scatter(pool, qkv[i], qkv[i], 2048, 2048, tab, tab.shape[1], pos, 64,
+                                                       2, 128, k_offset=1536, v_offset=1792), nbuf)
+            report("kv_scatter_T64", secs, 64 * 1024 * 2 + 64 * 8, "config 2; latency-bound")
+        del pool, qkv
     for t, note in ((64, "config 4; L2-resident"), (512, "config 4; L2-resident"), (4096, "config 4; HBM-bound")):
+        if not want(f"silu_mul_T{t}"):
+            continue
         g = wl.config_silu(64)["gate_up"]
-        nbuf = max(2, min(64, int(3e8 // (t * 8960 * 4)) + 1))
+        nbuf = max(2, min(64, int(3e8 // (t * 8960 * 6)) + 1))
         bufs = [dev(np.tile(g, (t // 64, 1))) for _ in range(nbuf)]
-        secs = timed(lambda i: K.launch_silu_mul(bufs[i], bufs[i], t, 8960), nbuf)
-        report(f"silu_mul_T{t}", secs, 3 * t * 8960 * 2, note)
-        del bufs
+        # dense output buffers: writing in place would feed each launch the previous launch's results, which
+        # decay towards subnormals over the timed iterations; bytes moved are the same (2 reads + 1 write)
+        outs = [torch.empty(t, 8960, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
+        secs = timed(lambda i: K.launch_silu_mul(outs[i], bufs[i], t, 8960), nbuf)
+        report(f"silu_mul_T{t}", secs, 3 * t * 8960 * 2, note + "; dense out")
+        del bufs, outs
     torch.cuda.empty_cache()
     return out
 
@@ -457,7 +475,7 @@ def run_reference_arm(args, rank, world):
 
 def run_attention(args, rank, local_rank, world, barrier, dist):
     import torch
-    w = AttentionWorkload(rank, args.layers)
+    w = AttentionWorkload(rank, args.layers, args.ctx_lo, args.ctx_hi)
     max_abs = w.check()
     peak, peak_kind = measured_peaks()
     step = w.step if args.no_graph else graphed(w.step)
@@ -514,7 +532,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     import torch
     from redline_llm_b200 import kernels as K
     need = args.warmup + args.steps + 8
-    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need))
+    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences)
     peak, peak_kind = measured_peaks()
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
@@ -531,7 +549,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     health = K.attention_health()
     if rank != 0:
         return
-    tokens = DecodeStepWorkload.TOTAL
+    tokens = w.TOTAL
     value = tokens * args.steps / (ms * 1e-3)
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
     achieved = att_bytes / att_s / 1e9
@@ -579,11 +597,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_step", choices=["decode_step", "attention"])
+    ap.add_argument("--workload", default="decode_step", choices=["decode_step", "attention", "kernels"])
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="attention workload: eager launches instead of graph replay")
     ap.add_argument("--layers", type=int, default=LAYERS, help="attention workload: layer pools walked per step")
+    ap.add_argument("--ctx-lo", type=int, default=1024, help="attention workload: shortest context")
+    ap.add_argument("--ctx-hi", type=int, default=1280, help="attention workload: longest context")
+    ap.add_argument("--sequences", type=int, default=512,
+                    help="decode_step workload: sequences in the job (512 = the configuration; fewer for profiling)")
+    ap.add_argument("--kernel", default=None, help="kernels workload: only entries whose name contains this")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -610,7 +633,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    if args.workload == "attention":
+    if args.workload == "kernels":
+        peak, kind = measured_peaks()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unit": "GB/s", "peak": peak, "peak_kind": f"of {kind}",
+                              "launch": "eager" if args.no_graph else "cuda_graph_replay",
+                              "kernels": kernel_table(peak, args.kernel, args.no_graph)}), flush=True)
+    elif args.workload == "attention":
         run_attention(args, rank, local_rank, world, barrier, dist)
     else:
         run_decode_step(args, rank, local_rank, world, barrier, dist)

@@ -7,12 +7,17 @@
 //   ms  = mean(f32(h)^2), FP32             over the ROUNDED h
 //   out = fp16( fp16(f32(h) * rsqrtf(ms + eps)) * weight )   rounding point 2 before the weight
 //
-// Mapping: one warp owns one row and keeps it in registers as packed halves
-// between the two passes (16-byte loads, row read once, written once); the
-// sum of squares is reduced with one xor-shuffle tree, so there is no shared
-// memory and no block barrier. Rows are independent: identical inputs give
-// identical bits at every batch size. A scalar block-per-row kernel covers odd
-// widths and 2-byte-aligned bases.
+// Mapping. Rows are cut into 16-byte chunks (8 halves); chunk c = 32*i + lane.
+//   many rows : one WARP per row, the row kept in registers as packed halves
+//               between the two passes (row read once, written once), no shared
+//               memory, no block barrier - the HBM-streaming shape;
+//   few rows  : one CTA per row, one chunk per thread, so a decode batch of 64
+//               rows runs on 6 x 64 warps instead of 64 and the dependent
+//               instruction chain per thread is 8 elements long, not 48.
+// Both use ONE summation order - per chunk left to right from zero, a lane-xor
+// tree over the 32 chunks of each group i, then the groups in ascending i - so a
+// row gives the same bits whichever shape ran it and whatever the batch size.
+// A scalar block-per-row kernel covers odd widths and 2-byte-aligned bases.
 #include "common.cuh"
 
 #if defined(__USE_FAST_MATH__)
@@ -23,6 +28,44 @@ namespace rl {
 namespace {
 
 constexpr int kMaxChunksPerLane = 8;  // 8 chunks x 8 halves x 32 lanes = 2048 columns
+
+// Sum of squares of one chunk, left to right from zero (the shared summation order).
+__device__ __forceinline__ float ChunkSumSq(const uint4& x) {
+  const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(AsHalf2(words[j]));
+    ss = fmaf(f.x, f.x, ss);
+    ss = fmaf(f.y, f.y, ss);
+  }
+  return ss;
+}
+
+__device__ __forceinline__ float WarpTreeSum(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+__device__ __forceinline__ uint4 AddChunk(const uint4& r, const uint4& x) {
+  return make_uint4(AsU32(__hadd2_rn(AsHalf2(r.x), AsHalf2(x.x))), AsU32(__hadd2_rn(AsHalf2(r.y), AsHalf2(x.y))),
+                    AsU32(__hadd2_rn(AsHalf2(r.z), AsHalf2(x.z))), AsU32(__hadd2_rn(AsHalf2(r.w), AsHalf2(x.w))));
+}
+
+// out chunk = fp16(fp16(h * inv) * w); fp16 x fp16 is exact in FP32, so one half multiply equals
+// fp16(f32(n) * f32(w)).
+__device__ __forceinline__ uint4 NormChunk(const uint4& h, const uint4& w, float inv) {
+  const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(AsHalf2(hw[j]));
+    o[j] = AsU32(__hmul2_rn(__floats2half2_rn(f.x * inv, f.y * inv), AsHalf2(ww[j])));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
 
 template <int CPL, bool kResidual>
 __global__ void __launch_bounds__(256)
@@ -36,52 +79,61 @@ RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const hal
   const size_t base = static_cast<size_t>(row) * hidden;
 
   uint4 hv[CPL];
-  float ss = 0.0f;
+  float part[CPL];
 #pragma unroll
   for (int i = 0; i < CPL; ++i) {
     const int c = i * 32 + lane;
+    part[i] = 0.0f;
     if (c < chunks) {
       uint4 x = LdgStream16(input + base + c * 8);
       if (kResidual) {
-        const uint4 r = Ldg16(residual + base + c * 8);
-        x.x = AsU32(__hadd2_rn(AsHalf2(r.x), AsHalf2(x.x)));
-        x.y = AsU32(__hadd2_rn(AsHalf2(r.y), AsHalf2(x.y)));
-        x.z = AsU32(__hadd2_rn(AsHalf2(r.z), AsHalf2(x.z)));
-        x.w = AsU32(__hadd2_rn(AsHalf2(r.w), AsHalf2(x.w)));
+        x = AddChunk(Ldg16(residual + base + c * 8), x);
         Stg16(residual + base + c * 8, x);
       }
       hv[i] = x;
-      const uint32_t words[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(AsHalf2(words[j]));
-        ss = fmaf(f.x, f.x, ss);
-        ss = fmaf(f.y, f.y, ss);
-      }
+      part[i] = ChunkSumSq(x);
     }
   }
+  float ss = 0.0f;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  for (int i = 0; i < CPL; ++i) ss += WarpTreeSum(part[i]);
   const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
-
 #pragma unroll
   for (int i = 0; i < CPL; ++i) {
     const int c = i * 32 + lane;
-    if (c < chunks) {
-      const uint4 w = Ldg16(weight + c * 8);
-      const uint32_t hw[4] = {hv[i].x, hv[i].y, hv[i].z, hv[i].w};
-      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(AsHalf2(hw[j]));
-        const half2 normed = __floats2half2_rn(f.x * inv, f.y * inv);
-        // fp16 x fp16 is exact in FP32, so one half multiply == fp16(f32(n) * f32(w)).
-        o[j] = AsU32(__hmul2_rn(normed, AsHalf2(ww[j])));
-      }
-      Stg16(out + base + c * 8, make_uint4(o[0], o[1], o[2], o[3]));
-    }
+    if (c < chunks) Stg16(out + base + c * 8, NormChunk(hv[i], Ldg16(weight + c * 8), inv));
   }
+}
+
+// One CTA of 32*CPL threads per row, one chunk per thread (thread = 32*i + lane).
+template <int CPL, bool kResidual>
+__global__ void __launch_bounds__(32 * CPL)
+RmsNormBlockKernel(half* __restrict__ out, half* __restrict__ residual, const half* __restrict__ input,
+                   const half* __restrict__ weight, int hidden, float eps) {
+  __shared__ float group_sum[CPL];
+  const int c = threadIdx.x;
+  const int chunks = hidden >> 3;
+  const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+  const bool live = c < chunks;
+  uint4 h = make_uint4(0, 0, 0, 0), w = h;
+  float part = 0.0f;
+  if (live) {
+    h = LdgStream16(input + base + c * 8);
+    w = Ldg16(weight + c * 8);
+    if (kResidual) {
+      h = AddChunk(Ldg16(residual + base + c * 8), h);
+      Stg16(residual + base + c * 8, h);
+    }
+    part = ChunkSumSq(h);
+  }
+  part = WarpTreeSum(part);
+  if ((c & 31) == 0) group_sum[c >> 5] = part;
+  __syncthreads();
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) ss += group_sum[i];
+  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+  if (live) Stg16(out + base + c * 8, NormChunk(h, w, inv));
 }
 
 // Any width, any 2-byte alignment: one block per row, two passes over global
@@ -134,15 +186,19 @@ int Launch(half* out, half* residual, const half* input, const half* weight, int
                                                                    hidden, eps);
     return LaunchStatus("rmsnorm (scalar)");
   }
-  // Few rows: one warp per block so the rows spread over the SMs; many rows: 8 per block.
   const int sms = CurrentDeviceFacts().sm_count;
-  const int wpb = num_tokens >= 8 * sms ? 8 : (num_tokens >= 2 * sms ? 2 : 1);
-  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
   const int cpl = (hidden / 8 + 31) / 32;
-#define RL_NORM_CASE(N)                                                                          \
-  case N:                                                                                        \
-    RmsNormWarpKernel<N, kResidual><<<grid, block, 0, stream>>>(out, residual, input, weight,    \
-                                                                num_tokens, hidden, eps);        \
+  const bool few_rows = num_tokens <= 8 * sms;  // below that a warp per row leaves SMs idle
+  const int wpb = 8;
+  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
+#define RL_NORM_CASE(N)                                                                             \
+  case N:                                                                                           \
+    if (few_rows)                                                                                   \
+      RmsNormBlockKernel<N, kResidual><<<num_tokens, 32 * N, 0, stream>>>(out, residual, input,     \
+                                                                          weight, hidden, eps);     \
+    else                                                                                            \
+      RmsNormWarpKernel<N, kResidual><<<grid, block, 0, stream>>>(out, residual, input, weight,     \
+                                                                  num_tokens, hidden, eps);         \
     break;
   switch (cpl) {
     RL_NORM_CASE(1) RL_NORM_CASE(2) RL_NORM_CASE(3) RL_NORM_CASE(4) RL_NORM_CASE(5)

@@ -115,15 +115,21 @@ def test_rmsnorm_boundary_fixture_rounding_order(own):
 
 
 def test_rmsnorm_deterministic_and_batch_invariant(own):
+    """Same row, same bits: run to run, at any batch size, and across the CTA-per-row (few rows) and
+    warp-per-row (many rows) kernels, which share one summation order."""
     c = wl.config_rmsnorm(64)
     outs = []
-    for rows in (64, 64, 5):
-        d_res = dev(c["residual"][:rows])
+    for rows in (64, 64, 5, 4096):
+        reps = -(-rows // 64)
+        x = np.tile(c["x"], (reps, 1))[:rows]
+        r = np.tile(c["residual"], (reps, 1))[:rows]
+        d_res = dev(r)
         d_out = torch.zeros(rows, 1536, dtype=torch.int16, device="cuda")
-        K.launch_rms_norm_residual(d_out, d_res, dev(c["x"][:rows]), dev(c["weight"]), rows, 1536, EPS)
+        K.launch_rms_norm_residual(d_out, d_res, dev(x), dev(c["weight"]), rows, 1536, EPS)
         outs.append(host(d_out))
     assert np.array_equal(outs[0], outs[1])
     assert np.array_equal(outs[0][:5], outs[2])
+    assert np.array_equal(outs[3][:64], outs[0]) and np.array_equal(outs[3][-64:], outs[0])
 
 
 def test_rmsnorm_config1_shape_and_large_T(own):
@@ -310,6 +316,39 @@ def test_silu_odd_sizes_take_scalar_path(own, inter):
     got = host(d_out)
     assert_within_one_ulp(got[:rows * inter].reshape(rows, inter), own.silu_mul(gu), f"I={inter}")
     assert (got[rows * inter:] == 0x1234).all()
+
+
+def test_silu_every_gate_pattern_matches_the_plain_division_kernel(own):
+    """The vector kernel spells its divide out; the scalar kernel uses the compiler's `x / (1 + expf(-x))`
+    (the reference kernel's expression). All 65536 gate bit patterns x 48 up values must agree bit for
+    bit (NaN results by class), which pins the spelled-out divide to the IEEE one by exhaustion."""
+    gates = np.arange(65536, dtype=np.uint16)
+    ups = np.concatenate([wl.normal_half(0x51, 40), np.array([0x3C00, 0xBC00, 0x7BFF, 0x0001, 0x8001, 0x0000, 0x7C00, 0x3555], np.uint16)])
+    inter = 65536
+    rows = len(ups)
+    gu = np.empty((rows, 2 * inter), np.uint16)
+    gu[:, :inter] = gates[None, :]
+    gu[:, inter:] = ups[:, None]
+    d_gu = dev(gu)
+    fast = torch.zeros(rows, inter, dtype=torch.int16, device="cuda")
+    K.launch_silu_mul(fast, d_gu, rows, inter)
+    # the scalar kernel: a 2-byte-aligned output base forces it
+    slow_img = torch.zeros(rows * inter + 1, dtype=torch.int16, device="cuda")
+    st = K.lib().rl_launch_silu_mul(slow_img.data_ptr() + 2, d_gu.data_ptr(), rows, inter,
+                                    torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    a = host(fast)
+    b = host(slow_img)[1:].reshape(rows, inter)
+    both_nan = is_nan_bits(a) & is_nan_bits(b)
+    assert np.array_equal(a[~both_nan], b[~both_nan])
+    assert np.array_equal(is_nan_bits(a), is_nan_bits(b))
+    # and the plain kernel itself against the FP64 checker wherever both are finite (FP32 underflows
+    # silu(x) to zero below x = -88.7 where FP64 does not, which only shows against an infinite `up`)
+    ref = own.silu_mul(gu)
+    finite = lambda v: (v & 0x7FFF) < 0x7C00
+    both = finite(b) & finite(ref)
+    assert both.mean() > 0.9
+    assert oracle.ulp_distance(b, ref)[both].max() <= 1
 
 
 def test_silu_extremes_and_config4_largest(own):
