@@ -227,7 +227,7 @@ class DecodeStepWorkload:
             self.engines.append(e)
             self.lens.append(wave)
         self.tokens_per_step = len(mine)
-        self.launches_per_step = len(self.engines) * (self.cfg.layers * 6 + 1)  # 6 own kernels per layer + final norm
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * 6 + 3)  # 6 own kernels per layer + embed, final norm, argmax
         self.h2d = self.d2h = 0
 
     def step(self):  # inputs already resident: graph replays only
@@ -239,7 +239,7 @@ class DecodeStepWorkload:
         for e in self.engines:
             e.step()
             self.h2d += e.exec.h2d_bytes
-            self.d2h += 8 * self.WAVE
+            self.d2h += 4 * self.WAVE
 
     def profile_attention(self):
         """Eager pass with CUDA events around every attention launch; returns (mean seconds per launch,
@@ -395,6 +395,28 @@ def kernel_table(peak, only=None, eager=False):
         secs = timed(lambda i: K.launch_silu_mul(outs[i], bufs[i], t, 8960), nbuf)
         report(f"silu_mul_T{t}", secs, 3 * t * 8960 * 2, note + "; dense out")
         del bufs, outs
+    if want("greedy_argmax_64x151936"):
+        nbuf = 8
+        lg = [dev(wl.normal_half(0xA46 + i, 64 * 151936).reshape(64, 151936)) for i in range(nbuf)]
+        tok = torch.zeros(64, dtype=torch.int32, device="cuda")
+        secs = timed(lambda i: K.launch_greedy_argmax(tok, lg[i], 64, 151936), nbuf)
+        report("greedy_argmax_64x151936", secs, 64 * 151936 * 2 + 64 * 4, "decode batch of logits; 8-CTA clusters per row")
+        del lg
+    if want("embed_gather_T64"):
+        table = dev(wl.normal_half(0xE1, 32768 * 1536).reshape(32768, 1536))
+        ids = dev(wl.randint(0xE2, 64, 0, 32767))
+        o = [torch.empty(64, 1536, dtype=torch.int16, device="cuda") for _ in range(8)]
+        secs = timed(lambda i: K.launch_embed_gather(o[i], 1536, table, ids, 64, 1536), 8)
+        report("embed_gather_T64", secs, 2 * 64 * 1536 * 2 + 64 * 4, "latency-bound")
+        del table, o
+    if want("rope_kv_scatter_fused_T64"):
+        c = wl.config_rope_scatter(64)
+        qkv = [dev(c["qkv"]) for _ in range(8)]
+        pos, tab = dev(c["positions"]), dev(c["tables"])
+        pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
+        secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pool, tab, tab.shape[1], pos, 64, 12, 2, 128, 1e6), 8)
+        report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1024 + 64 * 8 + 256, "config 2 in one launch; latency-bound")
+        del pool, qkv
     torch.cuda.empty_cache()
     return out
 

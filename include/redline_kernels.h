@@ -84,6 +84,19 @@ int rl_launch_kv_scatter(void* kv_pool_layer, const void* k, const void* v, int6
                          int32_t num_tokens, int32_t num_kv_heads, int32_t head_dim, void* stream);
 
 /*
+ * RoPE and KV scatter in ONE launch: exactly rl_launch_rope_inplace followed by
+ * rl_launch_kv_scatter (same buffers, bit-identical results in the qkv buffer and in the pool),
+ * saving a launch and a pass over K per layer. The reference runs the two launchers back to back
+ * (src/core/model_executor.cpp:924-930) and has no fused form; an executor opts in by replacing
+ * those two calls with this one.
+ */
+int rl_launch_rope_kv_scatter(void* q, void* k, const void* v, int64_t q_row_stride, int64_t k_row_stride,
+                              int64_t v_row_stride, void* kv_pool_layer, const int32_t* block_tables,
+                              int64_t block_table_row_stride, const int32_t* positions, int32_t num_tokens,
+                              int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float rope_theta,
+                              void* stream);
+
+/*
  * Paged grouped-query decode attention, one query token per sequence, online
  * softmax with FP32 statistics and accumulation; rows with seq_len <= 0 are not
  * written. head_dim must be 128 and num_q_heads == 6 * num_kv_heads (as the
@@ -151,6 +164,18 @@ int rl_launch_paged_attention_decode_check(void* out, int64_t out_row_stride, co
  * src/kernels/kernels.cuh:192-193 (src/kernels/silu_mul.cu:129-169). */
 int rl_launch_silu_mul(void* out, const void* gate_up, int32_t num_tokens,
                        int32_t intermediate_size, void* stream);
+
+/* out[t,:] = embed[input_ids[t],:], a bit move; the first launch of every decode step.
+ * Replaces LaunchEmbedGather, src/kernels/kernels.cuh:48-50 (src/kernels/embed_gather.cu:121-156). */
+int rl_launch_embed_gather(void* out, int64_t out_row_stride, const void* embed,
+                           const int32_t* input_ids, int32_t num_tokens, int32_t hidden_size,
+                           void* stream);
+
+/* Per-row index of the largest logit: FP32 compares, ties to the lowest index, a NaN never wins,
+ * an all-NaN row gives token 0. logits is dense [num_seqs, vocab_size]. Replaces
+ * LaunchGreedyArgmax, src/kernels/kernels.cuh:198-199 (src/kernels/argmax.cu:228-252). */
+int rl_launch_greedy_argmax(int32_t* out_tokens, const void* logits, int32_t num_seqs,
+                            int32_t vocab_size, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,123 @@
+// Greedy argmax over the vocabulary, sm_100a.
+//
+// Contract and ordering are the reference's (src/kernels/kernels.cuh:195-199,
+// src/kernels/argmax.cu:228-252): per row, the int32 index of the largest
+// logit; compares in FP32 (an exact, order-preserving widening of the stored
+// FP16); a strictly greater value wins and equal values go to the LOWEST index
+// (+0 and -0 compare equal); a NaN never displaces an incumbent, an all-NaN row
+// yields token 0; an all -inf row yields token 0 through the index tie-break.
+// The predicate is a total order over everything the reduction sees, so the
+// winner does not depend on the reduction shape.
+//
+// Mapping. A decode batch is 64 rows x 151 936 logits = 19.4 MB: one CTA per row
+// (the reference's shape) would use 64 of 148 SMs. Here every row is scanned by
+// a thread-block CLUSTER of 8 CTAs, each taking a contiguous eighth of the row
+// with 16-byte loads; warp champions meet in shared memory, the 8 CTA champions
+// meet in the leader's shared memory through distributed shared memory, and the
+// leader writes the token - one launch, no scratch in global memory, no atomics.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace rl {
+namespace {
+
+constexpr int kClusterCtas = 8;
+constexpr int kThreads = 256;
+
+struct Champion {
+  float v;
+  int i;
+};
+
+// Does candidate (v, i) beat the incumbent? Both arms are IEEE compares: false against NaN.
+__device__ __forceinline__ bool Better(float v, int i, const Champion& b) {
+  return (v > b.v) || (v == b.v && i < b.i);
+}
+__device__ __forceinline__ void Offer(Champion& b, float v, int i) {
+  if (Better(v, i, b)) {
+    b.v = v;
+    b.i = i;
+  }
+}
+
+__device__ __forceinline__ Champion WarpChampion(Champion c) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, c.v, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, c.i, off);
+    Offer(c, ov, oi);
+  }
+  return c;
+}
+
+// kVec: rows are 16-byte aligned and vocab % 8 == 0.
+template <bool kVec>
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
+ArgmaxClusterKernel(int32_t* __restrict__ out_tokens, const half* __restrict__ logits, int vocab) {
+  __shared__ Champion warp_best[kThreads / 32];
+  __shared__ Champion cta_best[kClusterCtas];  // used in the cluster leader only
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int row = blockIdx.x / kClusterCtas;
+  const half* x = logits + static_cast<int64_t>(row) * vocab;
+
+  Champion best{-INFINITY, vocab};  // the sentinel index sorts after every real column
+  if (kVec) {
+    const int chunks = vocab >> 3;
+    const int per = (chunks + kClusterCtas - 1) / kClusterCtas;
+    const int end = min(chunks, (rank + 1) * per);
+    for (int c = rank * per + threadIdx.x; c < end; c += kThreads) {
+      const uint4 w = LdgStream16(x + c * 8);
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(AsHalf2(words[j]));
+        Offer(best, f.x, c * 8 + 2 * j);
+        Offer(best, f.y, c * 8 + 2 * j + 1);
+      }
+    }
+  } else {
+    const int per = (vocab + kClusterCtas - 1) / kClusterCtas;
+    const int end = min(vocab, (rank + 1) * per);
+    for (int i = rank * per + threadIdx.x; i < end; i += kThreads) Offer(best, __half2float(x[i]), i);
+  }
+  best = WarpChampion(best);
+  if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Champion b = warp_best[0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) Offer(b, warp_best[w].v, warp_best[w].i);
+    Champion* leader = cluster.map_shared_rank(cta_best, 0);
+    leader[rank] = b;
+  }
+  cluster.sync();  // every CTA's champion is in the leader's shared memory
+  if (rank == 0 && threadIdx.x == 0) {
+    Champion b = cta_best[0];
+#pragma unroll
+    for (int r = 1; r < kClusterCtas; ++r) Offer(b, cta_best[r].v, cta_best[r].i);
+    out_tokens[row] = b.i >= vocab ? 0 : b.i;  // nothing adopted (all NaN): token 0
+  }
+}
+
+}  // namespace
+}  // namespace rl
+
+extern "C" int rl_launch_greedy_argmax(int32_t* out_tokens, const void* logits, int32_t num_seqs,
+                                       int32_t vocab_size, void* stream) {
+  using namespace rl;
+  if (num_seqs <= 0 || vocab_size <= 0) return RL_OK;
+  if (!out_tokens || !logits) return Fail(RL_E_NULL_POINTER, "greedy_argmax: null device pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const half* x = static_cast<const half*>(logits);
+  const dim3 grid(static_cast<unsigned>(num_seqs) * kClusterCtas);
+  if (vocab_size % 8 == 0 && Aligned16(logits)) {
+    ArgmaxClusterKernel<true><<<grid, kThreads, 0, s>>>(out_tokens, x, vocab_size);
+  } else {
+    ArgmaxClusterKernel<false><<<grid, kThreads, 0, s>>>(out_tokens, x, vocab_size);
+  }
+  return LaunchStatus("greedy_argmax");
+}

@@ -16,11 +16,11 @@
 // cudaGetLastError() after the step's synchronisation
 // (src/core/model_executor.cpp:711-712).
 //
-// Only the launchers on the decode hot path are provided: LaunchRmsNorm,
-// LaunchRmsNormResidual, LaunchRopeInplace, LaunchKvScatter,
-// LaunchPagedAttentionDecode (+ the test-only cross-check launcher) and
-// LaunchSiluMul. The prefill-only and embedding/argmax launchers of the
-// reference header keep their reference implementations.
+// Every launcher inside the captured decode graph is provided: LaunchEmbedGather,
+// LaunchRmsNorm, LaunchRmsNormResidual, LaunchRopeInplace, LaunchKvScatter,
+// LaunchPagedAttentionDecode (+ the test-only cross-check launcher), LaunchSiluMul
+// and LaunchGreedyArgmax. The two prefill-only launchers of the reference header
+// (LaunchKvGather, LaunchPrefillSoftmax) keep their reference implementations.
 #pragma once
 
 #include <cstdint>
@@ -45,6 +45,20 @@ inline void Check(int status, const char* launcher) {
   }
 }
 }  // namespace detail
+
+inline void LaunchEmbedGather(half* out, std::int64_t out_row_stride, const half* embed,
+                              const std::int32_t* input_ids, std::int32_t num_tokens,
+                              std::int32_t hidden_size, cudaStream_t stream) {
+  detail::Check(rl_launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidden_size,
+                                       stream),
+                "LaunchEmbedGather");
+}
+
+inline void LaunchGreedyArgmax(std::int32_t* out_tokens, const half* logits, std::int32_t num_seqs,
+                               std::int32_t vocab_size, cudaStream_t stream) {
+  detail::Check(rl_launch_greedy_argmax(out_tokens, logits, num_seqs, vocab_size, stream),
+                "LaunchGreedyArgmax");
+}
 
 inline void LaunchRmsNorm(half* out, const half* input, const half* weight, std::int32_t num_tokens,
                           std::int32_t hidden_size, float eps, cudaStream_t stream) {

@@ -126,6 +126,64 @@ RopeScalarKernel(half* q, half* k, int64_t q_row_stride, int64_t k_row_stride,
   }
 }
 
+// RoPE and KV scatter in one pass (decode shape: head_dim 128, 16-byte aligned views). One CTA per
+// token: rotate Q and K in place exactly as RopeVecKernel does, and while the rotated K chunk is in
+// registers also store it to its page slot; V chunks are copied to theirs. The qkv buffer ends up
+// bit-identical to the two-launch sequence, and so does the pool.
+__global__ void __launch_bounds__(128)
+RopeScatterKernel(half* q, half* k, const half* __restrict__ v, int64_t q_row_stride, int64_t k_row_stride,
+                  int64_t v_row_stride, half* __restrict__ pool, const int32_t* __restrict__ tables,
+                  int64_t table_row_stride, const int32_t* __restrict__ positions, int num_q_heads,
+                  int num_kv_heads, int head_dim, const __grid_constant__ InvFreq inv_freq) {
+  __shared__ __align__(16) half2 cs[kMaxPairs];
+  const int64_t row = blockIdx.x;
+  const int half_dim = head_dim >> 1;
+  const int p = positions[row];
+  const int64_t block = tables[row * table_row_stride + (p >> kKvBlockShift)];
+  const int slot = p & (kKvBlock - 1);
+  const float pos = static_cast<float>(p);
+  for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
+    float s32, c32;
+    sincosf(pos * inv_freq.f[d], &s32, &c32);
+    cs[d] = __floats2half2_rn(c32, s32);
+  }
+  __syncthreads();
+  const int chunks = half_dim >> 3;
+  const int total_heads = num_q_heads + num_kv_heads;
+  const int rope_items = total_heads * chunks;
+  const int v_items = num_kv_heads * (head_dim >> 3);
+  for (int item = threadIdx.x; item < rope_items + v_items; item += blockDim.x) {
+    if (item < rope_items) {
+      const int head = item / chunks;
+      const int d0 = (item - head * chunks) << 3;
+      half* base = HeadPtr(q, k, q_row_stride, k_row_stride, static_cast<int>(row), head, num_q_heads, head_dim);
+      uint4 lo = Ldg16(base + d0);
+      uint4 hi = Ldg16(base + d0 + half_dim);
+      uint32_t* l = &lo.x;
+      uint32_t* h = &hi.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const half2 a = cs[d0 + 2 * j], b = cs[d0 + 2 * j + 1];
+        RotateWord(l[j], h[j], __lows2half2(a, b), __highs2half2(a, b));
+      }
+      Stg16(base + d0, lo);
+      Stg16(base + d0 + half_dim, hi);
+      if (head >= num_q_heads) {
+        half* dst = pool + (((block * 2 + 0) * num_kv_heads + (head - num_q_heads)) * kKvBlock + slot) *
+                               static_cast<int64_t>(head_dim);
+        Stg16(dst + d0, lo);
+        Stg16(dst + d0 + half_dim, hi);
+      }
+    } else {
+      const int w = item - rope_items;
+      const int head = w / (head_dim >> 3);
+      const int d0 = (w - head * (head_dim >> 3)) << 3;
+      half* dst = pool + (((block * 2 + 1) * num_kv_heads + head) * kKvBlock + slot) * static_cast<int64_t>(head_dim);
+      Stg16(dst + d0, Ldg16(v + row * v_row_stride + head * head_dim + d0));
+    }
+  }
+}
+
 }  // namespace
 }  // namespace rl
 
@@ -155,4 +213,31 @@ extern "C" int rl_launch_rope_inplace(void* q, void* k, int64_t q_row_stride, in
                                                 num_q_heads, total_heads, head_dim, table);
   }
   return LaunchStatus("rope");
+}
+
+extern "C" int rl_launch_rope_kv_scatter(void* q, void* k, const void* v, int64_t q_row_stride,
+                                         int64_t k_row_stride, int64_t v_row_stride, void* kv_pool_layer,
+                                         const int32_t* block_tables, int64_t block_table_row_stride,
+                                         const int32_t* positions, int32_t num_tokens, int32_t num_q_heads,
+                                         int32_t num_kv_heads, int32_t head_dim, float rope_theta, void* stream) {
+  using namespace rl;
+  if (num_tokens <= 0 || num_q_heads + num_kv_heads <= 0) return RL_OK;
+  if (!q || !k || !v || !kv_pool_layer || !block_tables || !positions)
+    return Fail(RL_E_NULL_POINTER, "rope_kv_scatter: null device pointer");
+  const bool vec = head_dim > 0 && head_dim % 16 == 0 && head_dim / 2 <= kMaxPairs && q_row_stride % 8 == 0 &&
+                   k_row_stride % 8 == 0 && v_row_stride % 8 == 0 && Aligned16(q) && Aligned16(k) && Aligned16(v) &&
+                   Aligned16(kv_pool_layer) && num_q_heads >= 0 && num_kv_heads > 0 && rope_theta > 0.0f;
+  if (!vec) {  // odd shapes: the two separate launchers cover everything the contract admits
+    const int rc = rl_launch_rope_inplace(q, k, q_row_stride, k_row_stride, positions, num_tokens, num_q_heads,
+                                          num_kv_heads, head_dim, rope_theta, stream);
+    if (rc != RL_OK) return rc;
+    return rl_launch_kv_scatter(kv_pool_layer, k, v, k_row_stride, v_row_stride, block_tables,
+                                block_table_row_stride, positions, num_tokens, num_kv_heads, head_dim, stream);
+  }
+  const InvFreq& table = TableFor(rope_theta, head_dim);
+  RopeScatterKernel<<<num_tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<half*>(q), static_cast<half*>(k), static_cast<const half*>(v), q_row_stride, k_row_stride,
+      v_row_stride, static_cast<half*>(kv_pool_layer), block_tables, block_table_row_stride, positions,
+      num_q_heads, num_kv_heads, head_dim, table);
+  return LaunchStatus("rope_kv_scatter");
 }

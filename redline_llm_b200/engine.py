@@ -7,7 +7,8 @@ FCFS continuous-batching scheduler with the {1,2,4,8,16,32,48,64} bucket ladder
 (src/core/scheduler.cpp:11-34,145-197,248-332) and a model executor that replays one CUDA graph per
 bucket (src/core/model_executor.cpp:523-633,721-782). The decode layer sequence is the reference's
 (src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library, every
-linear layer is a library GEMM (torch.matmul -> cuBLAS, unchanged on both sides of any comparison).
+linear layer is a library GEMM (torch.matmul -> cuBLAS, unchanged on both sides of any comparison);
+the embedding gather and the greedy argmax at the two ends of the step are this library's too.
 
 One Engine drives one GPU; multi-GPU serving is one Engine per GPU with requests sharded on the
 host (`shard_requests`) - sequences and their KV pages never leave their GPU, so no collective exists.
@@ -256,13 +257,13 @@ class ModelExecutor:
         self.mlp = torch.zeros(B, cfg.hidden, dtype=f16, device=device)
         self.gateup = torch.zeros(B, 2 * cfg.inter, dtype=f16, device=device)
         self.logits = torch.zeros(B, cfg.vocab, dtype=f16, device=device)
-        self.tokens = torch.zeros(B, dtype=torch.int64, device=device)
+        self.tokens = torch.zeros(B, dtype=i32, device=device)
         # pinned mirrors (one H2D each per step, one D2H)
         self.h_ids = torch.zeros(B, dtype=i32).pin_memory()
         self.h_pos = torch.zeros(B, dtype=i32).pin_memory()
         self.h_lens = torch.zeros(B, dtype=i32).pin_memory()
         self.h_tables = torch.zeros(B, self.mbps, dtype=i32).pin_memory()
-        self.h_tokens = torch.zeros(B, dtype=torch.int64).pin_memory()
+        self.h_tokens = torch.zeros(B, dtype=i32).pin_memory()
         self._np_ids, self._np_pos = self.h_ids.numpy(), self.h_pos.numpy()
         self._np_lens, self._np_tables = self.h_lens.numpy(), self.h_tables.numpy()
         self.row_owner: List[Optional[int]] = [None] * B   # request id whose table sits in row i
@@ -272,6 +273,7 @@ class ModelExecutor:
         self.graphs: Dict[int, object] = {}
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
+        self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
         K.init(device.index if device.index is not None else -1)
 
     # ---- the decode layer sequence (src/core/model_executor.cpp:894-961)
@@ -279,18 +281,22 @@ class ModelExecutor:
         torch, K, cfg, w = self.torch, self.K, self.cfg, self.w
         x, normed, qkv, attn, mlp, gu = (self.x[:rows], self.normed[:rows], self.qkv[:rows], self.attn[:rows],
                                          self.mlp[:rows], self.gateup[:rows])
-        torch.index_select(w.embed, 0, self.ids[:rows], out=x)
+        K.launch_embed_gather(x, cfg.hidden, w.embed, self.ids, rows, cfg.hidden)
         for li, L in enumerate(w.layers):
             if li == 0:
                 K.launch_rms_norm(normed, x, L["in_norm"], rows, cfg.hidden, cfg.eps)
             else:
                 K.launch_rms_norm_residual(normed, x, mlp, L["in_norm"], rows, cfg.hidden, cfg.eps)
             torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
-            K.launch_rope_inplace(qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.positions, rows, cfg.q_heads,
-                                  cfg.kv_heads, cfg.head_dim, cfg.rope_theta, k_offset=cfg.q_width)
-            K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.tables, self.mbps,
-                                self.positions, rows, cfg.kv_heads, cfg.head_dim,
-                                k_offset=cfg.q_width, v_offset=cfg.q_width + cfg.kv_width)
+            if self.fuse_rope_scatter:
+                K.launch_rope_kv_scatter(qkv, cfg.qkv_width, self.pool[li], self.tables, self.mbps, self.positions,
+                                         rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta)
+            else:
+                K.launch_rope_inplace(qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.positions, rows, cfg.q_heads,
+                                      cfg.kv_heads, cfg.head_dim, cfg.rope_theta, k_offset=cfg.q_width)
+                K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, self.tables, self.mbps,
+                                    self.positions, rows, cfg.kv_heads, cfg.head_dim,
+                                    k_offset=cfg.q_width, v_offset=cfg.q_width + cfg.kv_width)
             if self.attention_events is not None:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -307,7 +313,7 @@ class ModelExecutor:
             torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
         K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, rows, cfg.hidden, cfg.eps)
         torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
-        torch.argmax(self.logits[:rows], dim=-1, out=self.tokens[:rows])
+        K.launch_greedy_argmax(self.tokens, self.logits, rows, cfg.vocab)
 
     def warm_and_capture(self, buckets: Sequence[int]) -> None:
         """Eager warm-up of every bucket (first launches happen outside capture), then one graph each."""

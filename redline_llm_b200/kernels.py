@@ -21,6 +21,7 @@ ABI_SYMBOLS = (
     "rl_launch_rmsnorm_residual", "rl_launch_rope_inplace", "rl_launch_kv_scatter",
     "rl_launch_paged_attention_decode", "rl_launch_paged_attention_decode_check",
     "rl_launch_silu_mul", "rl_attention_health", "rl_launch_paged_attention_decode_static",
+    "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
 )
 
 
@@ -51,6 +52,9 @@ def lib() -> C.CDLL:
         L.rl_launch_paged_attention_decode_static.argtypes = att
         L.rl_launch_silu_mul.argtypes = [vp, vp, i32, i32, vp]
         L.rl_attention_health.argtypes = [C.POINTER(C.c_int)]
+        L.rl_launch_embed_gather.argtypes = [vp, i64, vp, vp, i32, i32, vp]
+        L.rl_launch_greedy_argmax.argtypes = [vp, vp, i32, i32, vp]
+        L.rl_launch_rope_kv_scatter.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, vp]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -132,6 +136,28 @@ def launch_paged_attention_decode_static(out, out_row_stride, q, q_row_stride, k
         _ptr(out), out_row_stride, _ptr(q, q_offset), q_row_stride, _ptr(kv_pool_layer),
         block_tables.data_ptr(), seq_lens.data_ptr(), num_seqs, max_blocks_per_seq, num_q_heads,
         num_kv_heads, head_dim, scale, _stream(stream)), "LaunchPagedAttentionDecode (static scratch)")
+
+
+def launch_rope_kv_scatter(qkv, q_row_stride, kv_pool_layer, block_tables, block_table_row_stride, positions,
+                           num_tokens, num_q_heads, num_kv_heads, head_dim, rope_theta, stream=None):
+    """RoPE on the Q and K views of one fused qkv buffer (Q | K | V per row) and the scatter of the
+    rotated K and of V into the paged pool, in one launch; same results as the two separate launchers."""
+    qw, kw = num_q_heads * head_dim, num_kv_heads * head_dim
+    _check(lib().rl_launch_rope_kv_scatter(_ptr(qkv), _ptr(qkv, qw), _ptr(qkv, qw + kw), q_row_stride,
+                                           q_row_stride, q_row_stride, _ptr(kv_pool_layer),
+                                           block_tables.data_ptr(), block_table_row_stride,
+                                           positions.data_ptr(), num_tokens, num_q_heads, num_kv_heads,
+                                           head_dim, rope_theta, _stream(stream)), "rope + kv scatter")
+
+
+def launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidden_size, stream=None):
+    _check(lib().rl_launch_embed_gather(_ptr(out), out_row_stride, _ptr(embed), input_ids.data_ptr(),
+                                        num_tokens, hidden_size, _stream(stream)), "LaunchEmbedGather")
+
+
+def launch_greedy_argmax(out_tokens, logits, num_seqs, vocab_size, stream=None):
+    _check(lib().rl_launch_greedy_argmax(out_tokens.data_ptr(), _ptr(logits), num_seqs, vocab_size,
+                                         _stream(stream)), "LaunchGreedyArgmax")
 
 
 def attention_health() -> int:

@@ -365,3 +365,40 @@ def test_silu_extremes_and_config4_largest(own):
     got = host(d_gu)
     assert np.array_equal(got[:, 8960:], gu[:, 8960:])
     assert_within_one_ulp(got[:, :8960], own.silu_mul(gu, f32=True), "config 4 T=4096", min_exact=0.9995)
+
+
+# ------------------------------------------------------- RoPE + scatter fused
+
+@pytest.mark.parametrize("tokens,stride_mode", [(64, "decode"), (7, "decode"), (33, "prefill")])
+def test_fused_rope_scatter_equals_the_two_launchers_bit_for_bit(own, tokens, stride_mode):
+    c = wl.config_rope_scatter(tokens=tokens, num_blocks=1024)
+    tables = c["tables"] % 1024
+    tables[tables == 0] = 1
+    pos = c["positions"]
+    if stride_mode == "prefill":            # all tokens share one table row; positions are a run
+        pos = np.arange(100, 100 + tokens, dtype=np.int32)
+        tables = (wl.permutation(0x77, 1000)[:256] + 1).astype(np.int32).reshape(1, 256)
+        tstride = 0
+    else:
+        # distinct target slots per token
+        tables[np.arange(tokens), pos // 16] = (wl.permutation(0x78, 1000)[:tokens] + 1)
+        tstride = tables.shape[1]
+    n = 1024 * 2 * 2 * 16 * 128
+    pool0 = np.full(n, 0x7E00, np.uint16)
+    d_tab, d_pos = dev(tables), dev(pos)
+    # reference sequence: two launches
+    qkv_a, pool_a = dev(c["qkv"]), dev(pool0)
+    K.launch_rope_inplace(qkv_a, qkv_a, 2048, 2048, d_pos, tokens, 12, 2, 128, 1e6, k_offset=1536)
+    K.launch_kv_scatter(pool_a, qkv_a, qkv_a, 2048, 2048, d_tab, tstride, d_pos, tokens, 2, 128,
+                        k_offset=1536, v_offset=1792)
+    # fused
+    qkv_b, pool_b = dev(c["qkv"]), dev(pool0)
+    K.launch_rope_kv_scatter(qkv_b, 2048, pool_b, d_tab, tstride, d_pos, tokens, 12, 2, 128, 1e6)
+    assert np.array_equal(host(qkv_a), host(qkv_b))
+    assert np.array_equal(host(pool_a), host(pool_b))
+    # and the pool against the CPU mirror of the rotated K / raw V
+    rot = host(qkv_b).reshape(tokens, 2048)
+    mirror = pool0.copy()
+    own.kv_scatter(mirror, np.ascontiguousarray(rot[:, 1536:1792]).reshape(-1), np.ascontiguousarray(rot[:, 1792:]).reshape(-1),
+                   256, 256, tables, tstride, pos, 2, 128)
+    assert np.array_equal(host(pool_b), mirror)
