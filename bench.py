@@ -257,8 +257,15 @@ class DecodeStepWorkload:
         return float(np.mean(secs)), float(np.mean(nbytes))
 
 
-def cpu_decode_step(w: "DecodeStepWorkload", rows: int, use_ref: bool):
-    """One decode step of `rows` sequences of wave 0 on the host cores: the reference's CPU functions
+def sample_rows(w: "DecodeStepWorkload", n: int = 2):
+    """The n sequences of wave 0 whose contexts are closest to the job's mean context."""
+    mean = float(np.mean([c for wave in w.lens for c in wave]))
+    order = np.argsort(np.abs(np.asarray(w.lens[0], np.float64) - mean))
+    return sorted(int(i) for i in order[:n])
+
+
+def cpu_decode_step(w: "DecodeStepWorkload", rows, use_ref: bool):
+    """One decode step of the sequences `rows` (indices into wave 0) on the host cores: the reference's CPU functions
     (tests/reference, compiled into oracle/_ref) for every non-GEMM stage - or this repository's C
     restatement when those were never compiled - and BLAS FP32 GEMMs rounded to FP16. Returns
     (seconds, tokens, logits) with weight conversion and cache download kept outside the timed part."""
@@ -272,10 +279,11 @@ def cpu_decode_step(w: "DecodeStepWorkload", rows: int, use_ref: bool):
     u16 = lambda t: t.detach().cpu().numpy().view(np.uint16)
     f32 = lambda bits: np.ascontiguousarray(bits).view(np.float16).astype(np.float32)
     h16 = lambda a: a.astype(np.float16).view(np.uint16)
-    ids = ex.ids[:rows].cpu().numpy()
-    pos = ex.positions[:rows].cpu().numpy()
-    lens = ex.seq_lens[:rows].cpu().numpy()
-    tables = ex.tables[:rows].cpu().numpy()
+    sel = torch.as_tensor(rows, device=ex.ids.device)
+    ids = ex.ids.index_select(0, sel).cpu().numpy()
+    pos = ex.positions.index_select(0, sel).cpu().numpy()
+    lens = ex.seq_lens.index_select(0, sel).cpu().numpy()
+    tables = ex.tables.index_select(0, sel).cpu().numpy()
     used = np.unique(tables[tables > 0])
     remap = np.zeros(int(tables.max()) + 1, np.int32)
     remap[used] = np.arange(1, len(used) + 1, dtype=np.int32)
@@ -482,13 +490,14 @@ def run_reference_arm(args, rank, world):
     w = DecodeStepWorkload(0, 64, new_tokens=8)  # 8 sequences: one small wave is enough for the sample
     for e in w.engines:
         e.step()
-    rows = 2
+    rows = sample_rows(w, 2)
     steps = max(1, min(args.steps, 3))
     runs = [cpu_decode_step(w, rows, True) for _ in range(steps)]
     dt = float(np.mean([r[0] for r in runs]))
-    value = rows / dt
+    value = len(rows) / dt
     cpu = {"value": round(value, 4), "unit": "tok/s", "cores": runs[0][3], "kind": runs[0][4],
-           "sample": f"{rows} sequences x 1 decode step, all 28 layers, contexts {w.lens[0][:rows]}, BLAS FP32 GEMMs"}
+           "sample": f"{len(rows)} sequences x 1 decode step, all 28 layers, contexts "
+                     f"{[w.lens[0][i] for i in rows]} (closest to the job's mean), BLAS FP32 GEMMs"}
     print(json.dumps(reference_line(args, "decode tok/s", "tok/s", round(value, 4), round(1e3 * dt, 3),
                                     {"workload": DecodeStepWorkload.name, "note": "each step is a bounded sample "
                                      "(2 sequences) of the workload on the host cores"}, cpu, "f64 kernels / f32 GEMM")),
@@ -590,19 +599,22 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                      "us_per_launch": round(att_s * 1e6, 2),
                      "timed": "CUDA events around each attention launch of an eager pass over the same step"},
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
-        "gpu_launches": w.launches_per_step * args.steps,
+        "gpu_launches": w.launches_per_step * args.steps * world,
         "clocks": clocks.summary(),
         "check": {"attention_health": health},
     }
     if not args.no_cpu_baseline and world == 1:
-        dt, cpu_tok, cpu_logits, threads, kind = cpu_decode_step(w, 2, True)
+        rows = sample_rows(w, 2)
+        dt, cpu_tok, cpu_logits, threads, kind = cpu_decode_step(w, rows, True)
         e = w.engines[0]
         e.exec.enqueue_decode(DecodeStepWorkload.WAVE)   # same inputs as the CPU sample saw
         torch.cuda.synchronize()
-        gpu_logits = e.exec.logits[:2].float().cpu().numpy()
-        gpu_tok = e.exec.tokens[:2].cpu().numpy()
-        line["cpu_baseline"] = {"value": round(2 / dt, 4), "unit": "tok/s", "cores": threads, "kind": kind,
-                                "sample": "2 sequences of wave 0 x 1 decode step, all 28 layers", "seconds": round(dt, 2)}
+        gpu_logits = e.exec.logits[rows].float().cpu().numpy()
+        gpu_tok = e.exec.tokens[rows].cpu().numpy()
+        line["cpu_baseline"] = {"value": round(len(rows) / dt, 4), "unit": "tok/s", "cores": threads, "kind": kind,
+                                "sample": f"{len(rows)} sequences of wave 0 (contexts {[w.lens[0][i] for i in rows]}, "
+                                          "closest to the job's mean) x 1 decode step, all 28 layers",
+                                "seconds": round(dt, 2)}
         line["check"].update({"step_logits_max_abs_vs_cpu": float(np.abs(gpu_logits - cpu_logits).max()),
                               "step_logits_scale": float(np.abs(cpu_logits).max()),
                               "greedy_tokens_equal_cpu": bool((gpu_tok == cpu_tok).all())})
