@@ -69,14 +69,26 @@ ArgmaxClusterKernel(int32_t* __restrict__ out_tokens, const half* __restrict__ l
     const int chunks = vocab >> 3;
     const int per = (chunks + kClusterCtas - 1) / kClusterCtas;
     const int end = min(chunks, (rank + 1) * per);
-    for (int c = rank * per + threadIdx.x; c < end; c += kThreads) {
-      const uint4 w = LdgStream16(x + c * 8);
-      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    // four independent 16-byte loads in flight per thread before any compare
+    for (int c0 = rank * per + threadIdx.x; c0 < end; c0 += 4 * kThreads) {
+      uint4 w[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(AsHalf2(words[j]));
-        Offer(best, f.x, c * 8 + 2 * j);
-        Offer(best, f.y, c * 8 + 2 * j + 1);
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * kThreads;
+        if (c < end) w[k] = LdgStream16(x + c * 8);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k * kThreads;
+        if (c < end) {
+          const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(AsHalf2(words[j]));
+            Offer(best, f.x, c * 8 + 2 * j);
+            Offer(best, f.y, c * 8 + 2 * j + 1);
+          }
+        }
       }
     }
   } else {
