@@ -202,7 +202,7 @@ class DecodeStepWorkload:
     name = "decode_step_qwen2.5-1.5b_512seq_ctx1024-8192+32x32768"
     TOTAL, LONG, WAVE, NEW = 512, 32, 64, 256
 
-    def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512):
+    def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512, overlap: bool = True):
         import torch
         self.TOTAL, self.LONG = total, total // 16
         from redline_llm_b200.engine import Engine, ModelConfig, ModelWeights, blocks_for_tokens, shard_requests
@@ -221,7 +221,7 @@ class DecodeStepWorkload:
             blocks = sum(blocks_for_tokens(c + new_tokens) for c in wave) + 8
             gb = blocks * self.cfg.block_bytes() / (1 << 30)
             e = Engine(kv_pool_gb=gb, max_batch=self.WAVE, max_seq_len=max_seq, config=self.cfg, weights=self.weights,
-                       device=dev.index, graph_buckets=[64])
+                       device=dev.index, graph_buckets=[64], prologue_overlap=overlap)
             for j, c in enumerate(wave):
                 e.add_synthetic_request(c, new_tokens, seed=wl.SEED_STEP + 1000 * rank + w0 + j)
             self.engines.append(e)
@@ -539,6 +539,7 @@ def run_attention(args, rank, local_rank, world, barrier, dist):
                    "kv_tokens_per_layer": w.tokens,
                    "cold_l2": f"{args.layers} layer pools walked per step ({args.layers * 0.134:.1f} GB)",
                    "launch": "eager" if args.no_graph else "cuda_graph_replay",
+                   "prologue_overlap": not args.no_overlap,
                    "pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
@@ -563,7 +564,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     import torch
     from redline_llm_b200 import kernels as K
     need = args.warmup + args.steps + 8
-    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences)
+    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences, overlap=not args.no_overlap)
     peak, peak_kind = measured_peaks()
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
@@ -590,7 +591,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
         "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
                    "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
-                   "launch": "one CUDA-graph replay per wave", "gemm": "library (cuBLAS via torch.matmul), FP16",
+                   "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap, "gemm": "library (cuBLAS via torch.matmul), FP16",
                    "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
                    "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
@@ -640,6 +641,8 @@ def main():
     ap.add_argument("--ctx-hi", type=int, default=1280, help="attention workload: longest context")
     ap.add_argument("--sequences", type=int, default=512,
                     help="decode_step workload: sequences in the job (512 = the configuration; fewer for profiling)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="plain attention launches (no programmatic dependent launch of the prologue)")
     ap.add_argument("--kernel", default=None, help="kernels workload: only entries whose name contains this")
     args = ap.parse_args()
     if args.impl == "ours":
@@ -667,6 +670,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    from redline_llm_b200 import kernels as _K
+    _K.set_attention_prologue_overlap(not args.no_overlap)
     if args.workload == "kernels":
         peak, kind = measured_peaks()
         if rank == 0:

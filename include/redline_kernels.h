@@ -116,6 +116,19 @@ int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const vo
                                      float scale, void* stream);
 
 /*
+ * Opt-in (default 0): launch the attention kernel with programmatic stream serialisation, so its
+ * prologue - the page prefix over seq_lens and the first block-table reads - overlaps the tail of
+ * the previous kernel of the stream (this library's KV-scatter / RoPE+scatter kernels and the
+ * attention kernel itself release their dependents early). The kernel waits for that previous
+ * kernel to complete before it reads the pool or Q and before it writes anything. The one new rule
+ * for the caller: seq_lens and block_tables must not be produced by the kernel launched
+ * immediately before the attention launcher (in the reference's executor they are uploaded once
+ * per step, src/core/model_executor.cpp:876-892). Process-wide; set it before capture.
+ * No counterpart in the reference.
+ */
+int rl_attention_set_prologue_overlap(int enable);
+
+/*
  * The attention launcher for hosts that must not allocate: same arguments, same kernel and
  * bit-identical results as rl_launch_paged_attention_decode, but the split/merge scratch is a
  * ~1.6 MB device array built into the library image (held by every GPU that loads the library

@@ -21,6 +21,9 @@ KvScatterKernel(half* __restrict__ pool, const half* __restrict__ k, const half*
                 int64_t table_row_stride, const int32_t* __restrict__ positions, int num_tokens,
                 int num_kv_heads, int head_dim) {
   constexpr int kPer = sizeof(Word) / sizeof(half);
+  // the attention launch that follows may begin its table walk now (it waits for this grid to
+  // complete before it reads the pool)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= num_tokens) return;
   const int lane = threadIdx.x & 31;

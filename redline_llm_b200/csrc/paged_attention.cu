@@ -234,6 +234,10 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   const int heads = p.kv_heads;
   const int num_seqs = p.num_seqs;
   RL_STAMP(0);
+  // Let a dependent launch (the next attention call, when prologue overlap is on) start its own
+  // prologue as soon as this grid is resident; it still waits for this grid to finish before it
+  // touches anything this grid writes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
   }
@@ -299,6 +303,12 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   };
   int tiles_cur = fetch_tiles(0);
   int tiles_next = n_mine > 32 ? fetch_tiles(1) : 0;
+  // Everything above read only seq_lens and the block tables. When this grid was launched with
+  // programmatic stream serialisation it may have started while the previous kernel of the stream
+  // (the KV scatter of this layer, or the previous attention call) was still running: wait for it
+  // to complete before reading the pool or Q, or writing the output and the workspace. A no-op for
+  // an ordinary launch.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   int n_issue = 0, n_use = 0;
   auto issue_one = [&]() {
     const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, n_issue & 31);
@@ -619,6 +629,7 @@ struct DeviceState {
 constexpr int kMaxDevices = 64;
 DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
+bool g_prologue_overlap = false;  // rl_attention_set_prologue_overlap
 void* g_timeline = nullptr;  // diagnostics build only
 std::mutex g_mutex;
 
@@ -729,6 +740,11 @@ extern "C" int rl_attention_health(int* flag_out) {
   return RL_OK;
 }
 
+extern "C" int rl_attention_set_prologue_overlap(int enable) {
+  rl::attn::g_prologue_overlap = enable != 0;
+  return RL_OK;
+}
+
 extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const void* q,
                                                 int64_t q_row_stride, const void* kv_pool_layer,
                                                 const int32_t* block_tables, const int32_t* seq_lens,
@@ -773,7 +789,22 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
 #ifdef RL_ATTN_TIMELINE
     p.timeline = static_cast<unsigned long long*>(g_timeline);
 #endif
-    PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
+    if (g_prologue_overlap) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(st->ctas);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = kSmemBytes;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      const cudaError_t e = cudaLaunchKernelEx(&cfg, PagedAttentionSplitKernel, p, tile_map);
+      if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention_decode: %s", cudaGetErrorString(e));
+    } else {
+      PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
+    }
   }
   return LaunchStatus("paged_attention_decode");
 }

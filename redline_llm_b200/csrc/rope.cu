@@ -136,6 +136,9 @@ RopeScatterKernel(half* q, half* k, const half* __restrict__ v, int64_t q_row_st
                   int64_t table_row_stride, const int32_t* __restrict__ positions, int num_q_heads,
                   int num_kv_heads, int head_dim, const __grid_constant__ InvFreq inv_freq) {
   __shared__ __align__(16) half2 cs[kMaxPairs];
+  // the attention launch that follows may begin its table walk now (it waits for this grid to
+  // complete before it reads the pool or Q)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t row = blockIdx.x;
   const int half_dim = head_dim >> 1;
   const int p = positions[row];

@@ -442,7 +442,7 @@ class Engine:
                  admission_policy: str = "reserve_full", pad_eager_to_bucket: int = 0,
                  debug_dump_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
                  device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
-                 graph_buckets: Optional[Sequence[int]] = None):
+                 graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True):
         import torch
         if admission_policy != "reserve_full":
             raise ValueError("only the reserve_full admission policy is provided")
@@ -458,6 +458,10 @@ class Engine:
         num_blocks = max(2, int(kv_pool_gb * (1 << 30)) // self.cfg.block_bytes())
         self.allocator = BlockAllocator(num_blocks)
         self.scheduler = Scheduler(self.allocator, max_batch, max_seq_len, prefill_chunk, self.cfg.eos_token_id)
+        from . import kernels as K
+        # attention's table walk may overlap the RoPE+scatter kernel before it: seq_lens and the block
+        # tables are uploaded at the start of a step, never written by that kernel
+        K.set_attention_prologue_overlap(prologue_overlap)
         self.weights = weights or ModelWeights(self.cfg, self.device, seed)
         self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
         self.max_seq_len, self.max_batch = max_seq_len, max_batch

@@ -22,6 +22,7 @@ ABI_SYMBOLS = (
     "rl_launch_paged_attention_decode", "rl_launch_paged_attention_decode_check",
     "rl_launch_silu_mul", "rl_attention_health", "rl_launch_paged_attention_decode_static",
     "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
+    "rl_attention_set_prologue_overlap",
 )
 
 
@@ -54,6 +55,7 @@ def lib() -> C.CDLL:
         L.rl_attention_health.argtypes = [C.POINTER(C.c_int)]
         L.rl_launch_embed_gather.argtypes = [vp, i64, vp, vp, i32, i32, vp]
         L.rl_launch_greedy_argmax.argtypes = [vp, vp, i32, i32, vp]
+        L.rl_attention_set_prologue_overlap.argtypes = [C.c_int]
         L.rl_launch_rope_kv_scatter.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, vp]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -158,6 +160,13 @@ def launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidde
 def launch_greedy_argmax(out_tokens, logits, num_seqs, vocab_size, stream=None):
     _check(lib().rl_launch_greedy_argmax(out_tokens.data_ptr(), _ptr(logits), num_seqs, vocab_size,
                                          _stream(stream)), "LaunchGreedyArgmax")
+
+
+def set_attention_prologue_overlap(enable: bool) -> None:
+    """Overlap the attention kernel's table walk with the previous kernel's tail (programmatic
+    dependent launch). seq_lens / block_tables must then not be written by the kernel launched
+    immediately before attention."""
+    _check(lib().rl_attention_set_prologue_overlap(1 if enable else 0), "rl_attention_set_prologue_overlap")
 
 
 def attention_health() -> int:

@@ -180,3 +180,37 @@ def test_scatter_then_attend_round_trip(own):
     K.launch_paged_attention_decode(d_out, 1536, dev(c["q"]), 1536, d_pool, dev(tables), dev((lens + 1).astype(np.int32)),
                                     3, tables.shape[1], 12, 2, 128, c["scale"])
     expect(own, c2, host(d_out), "after append")
+
+
+def test_prologue_overlap_changes_no_bit(own):
+    """With programmatic dependent launch on, the kernel's table walk runs under the previous kernel
+    (scatter, or the previous attention call); results must stay bit-identical over many back-to-back
+    scatter -> attention -> attention rounds that reuse the output, the workspace and the pool."""
+    c = case([700, 33, 1300, 0, 257, 2048, 16, 90], seed=0x0F1A, fill="normal")
+    lens = np.asarray(c["seq_lens"])
+    s = len(lens)
+    d_pool, d_tab, d_lens = dev(c["pool"]), dev(c["tables"]), dev(lens)
+    d_q = dev(c["q"])
+    kv = wl.normal_half(0x0F1B, s * 512).reshape(s, 512)
+    d_kv = dev(kv)
+    pos = dev(np.maximum(lens - 1, 0).astype(np.int32))
+    outs = {}
+    try:
+        for overlap in (False, True):
+            K.set_attention_prologue_overlap(overlap)
+            got = []
+            for it in range(20):
+                d_out = torch.zeros(s, 1536, dtype=torch.int16, device="cuda")
+                # the scatter rewrites each sequence's last token (same bytes every time), then two attention calls
+                K.launch_kv_scatter(d_pool, d_kv, d_kv, 512, 512, d_tab, c["tables"].shape[1], pos, s, 2, 128, v_offset=256)
+                K.launch_paged_attention_decode(d_out, 1536, d_q, 1536, d_pool, d_tab, d_lens, s, c["tables"].shape[1],
+                                                12, 2, 128, c["scale"])
+                K.launch_paged_attention_decode(d_out, 1536, d_q, 1536, d_pool, d_tab, d_lens, s, c["tables"].shape[1],
+                                                12, 2, 128, c["scale"])
+                got.append(host(d_out))
+            assert all(np.array_equal(g, got[0]) for g in got)
+            outs[overlap] = got[0]
+    finally:
+        K.set_attention_prologue_overlap(False)
+    live = lens > 0
+    assert np.array_equal(outs[False][live], outs[True][live])
