@@ -33,6 +33,9 @@ from redline_llm_b200 import workloads as wl  # noqa: E402
 
 LAYERS = 28
 METRIC = "decode-kernel HBM GB/s"
+# dram__bytes_read+write / algorithmic bytes of the attention kernel in the ncu capture at batch 64,
+# contexts 4096-8192 (402.6 MB / 397.3 MB); the config-3 capture gives 78.5 / 75.7 = 1.037
+ATTENTION_TRAFFIC_RATIO = 1.0134
 
 
 def measured_peaks():
@@ -265,78 +268,15 @@ def sample_rows(w: "DecodeStepWorkload", n: int = 2):
 
 
 def cpu_decode_step(w: "DecodeStepWorkload", rows, use_ref: bool):
-    """One decode step of the sequences `rows` (indices into wave 0) on the host cores: the reference's CPU functions
-    (tests/reference, compiled into oracle/_ref) for every non-GEMM stage - or this repository's C
-    restatement when those were never compiled - and BLAS FP32 GEMMs rounded to FP16. Returns
-    (seconds, tokens, logits) with weight conversion and cache download kept outside the timed part."""
-    import oracle
-    torch = w.torch
-    e, cfg = w.engines[0], w.cfg
-    ex = e.exec
-    ref = oracle.ref() if use_ref else None
-    own = oracle.own()
-    threads = ref.hardware_threads() if ref is not None else own.threads()
-    u16 = lambda t: t.detach().cpu().numpy().view(np.uint16)
-    f32 = lambda bits: np.ascontiguousarray(bits).view(np.float16).astype(np.float32)
-    h16 = lambda a: a.astype(np.float16).view(np.uint16)
-    sel = torch.as_tensor(rows, device=ex.ids.device)
-    ids = ex.ids.index_select(0, sel).cpu().numpy()
-    pos = ex.positions.index_select(0, sel).cpu().numpy()
-    lens = ex.seq_lens.index_select(0, sel).cpu().numpy()
-    tables = ex.tables.index_select(0, sel).cpu().numpy()
-    used = np.unique(tables[tables > 0])
-    remap = np.zeros(int(tables.max()) + 1, np.int32)
-    remap[used] = np.arange(1, len(used) + 1, dtype=np.int32)
-    ctab = np.ascontiguousarray(remap[tables])
-    mb = (int(lens.max()) + 15) // 16
-    ctab = np.ascontiguousarray(ctab[:, :mb])
-    idx = torch.as_tensor(np.concatenate([[0], used]), device=ex.pool.device)
-    pools = [u16(ex.pool[li].index_select(0, idx)).reshape(-1).copy() for li in range(cfg.layers)]
-    W = [{k: (f32(u16(v)) if v.dim() == 2 else u16(v).copy()) for k, v in L.items()} for L in w.weights.layers]
-    for L, T in zip(W, w.weights.layers):
-        L["qkv_bias"] = f32(u16(T["qkv_bias"]))
-    embed = u16(w.weights.embed)
-    head = f32(embed)
-    fin = u16(w.weights.final_norm).copy()
-
-    def norm(x, wt):
-        return ref.rmsnorm(x, wt, cfg.eps, threads) if ref is not None else own.rmsnorm(x, wt, cfg.eps)
-
-    def norm_res(res, x, wt):
-        o = ref.rmsnorm_residual(res, x, wt, cfg.eps, 0.0, threads) if ref is not None else own.rmsnorm_residual(res, x, wt, cfg.eps)
-        return o[0], o[1]
-
-    def rope(hb, heads):
-        return ref.rope(hb, pos, heads, cfg.head_dim, cfg.rope_theta, threads) if ref is not None else own.rope(hb, pos, heads, cfg.head_dim, cfg.rope_theta)
-
-    t0 = time.perf_counter()
-    x = np.ascontiguousarray(embed[ids])
-    mlp = None
-    for li, L in enumerate(W):
-        if li == 0:
-            normed = norm(x, L["in_norm"])
-        else:
-            normed, x = norm_res(x, mlp, L["in_norm"])
-        qkv = h16(f32(normed) @ L["qkv"].T + L["qkv_bias"])
-        q = rope(np.ascontiguousarray(qkv[:, :cfg.q_width]), cfg.q_heads)
-        k = rope(np.ascontiguousarray(qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width]), cfg.kv_heads)
-        v = np.ascontiguousarray(qkv[:, cfg.q_width + cfg.kv_width:])
-        (ref or own).kv_scatter(pools[li], k.reshape(-1), v.reshape(-1), cfg.kv_width, cfg.kv_width, ctab, mb, pos,
-                                cfg.kv_heads, cfg.head_dim)
-        if ref is not None:
-            att = ref.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim, ex.scale, threads)
-        else:
-            att = own.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim, ex.scale)
-        mlp = h16(f32(att) @ L["o"].T)
-        normed, x = norm_res(x, mlp, L["post_norm"])
-        gu = h16(f32(normed) @ L["gate_up"].T)
-        act = ref.silu_mul(gu, threads) if ref is not None else own.silu_mul(gu)
-        mlp = h16(f32(act) @ L["down"].T)
-    normed, x = norm_res(x, mlp, fin)
-    logits = f32(normed) @ head.T
-    tokens = (ref or own).argmax(h16(logits))
-    dt = time.perf_counter() - t0
-    return dt, tokens, logits, threads, ("reference" if ref is not None else "port")
+    """One decode step of the sequences `rows` (indices into wave 0) on the host cores, composed from the
+    reference's CPU functions and BLAS FP32 GEMMs (oracle/decode_step.py). Returns (seconds, tokens, logits,
+    threads, kind); weight conversion and the cache download are outside the timed part."""
+    from oracle.decode_step import CpuDecoder
+    if getattr(w, "_cpu_decoder", None) is None:
+        w._cpu_decoder = CpuDecoder(w.cfg, w.weights, use_ref)
+    dec = w._cpu_decoder
+    dt, tokens, logits = dec.step(w.engines[0].exec, rows)
+    return dt, tokens, logits, dec.threads, dec.kind
 
 
 def kernel_table(peak, only=None, eager=False):
@@ -543,7 +483,10 @@ def run_attention(args, rank, local_rank, world, barrier, dist):
                    "pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     "traffic": int(w.bytes_per_launch * (1.037 if args.ctx_hi <= 2048 else ATTENTION_TRAFFIC_RATIO)),
+                     "traffic_note": "dram read+write per launch from the ncu capture of this kernel "
+                                     "(profiles/paged_attention_split_kernel.txt), scaled by units processed",
                      "algorithmic_bytes_per_launch": w.bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 3)},
         "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
         "gpu_launches": w.launches_per_step * args.steps,
@@ -596,7 +539,10 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                    "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
                      "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
-                     "traffic": None, "algorithmic_bytes_per_launch": int(att_bytes),
+                     "traffic": int(att_bytes * ATTENTION_TRAFFIC_RATIO),
+                     "traffic_note": "dram read+write per launch scaled by units from the ncu capture at batch 64, "
+                                     "contexts 4096-8192 (profiles/paged_attention_split_kernel.txt): 1.013 x algorithmic",
+                     "algorithmic_bytes_per_launch": int(att_bytes),
                      "us_per_launch": round(att_s * 1e6, 2),
                      "timed": "CUDA events around each attention launch of an eager pass over the same step"},
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},

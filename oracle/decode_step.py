@@ -1,0 +1,111 @@
+"""One decode step of the whole model on the host cores (TEST INFRASTRUCTURE).
+
+The reference has no CPU implementation of a whole decode step; this composes one from its CPU
+functions for every non-GEMM stage (tests/reference/*.hpp compiled into oracle/_ref, or this
+repository's C restatement where those were never built) in the executor's layer order
+(src/core/model_executor.cpp:908-957), with BLAS FP32 GEMMs whose results are rounded to FP16 once
+(the FP16-in / FP32-accumulate / FP16-out contract of the library GEMMs). It is the checker of the
+engine's logits and tokens and the timed CPU baseline of the decode-step benchmark; the shipped
+path never imports it.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+
+import oracle
+
+
+def _u16(t):
+    return t.detach().cpu().numpy().view(np.uint16)
+
+
+def _f32(bits):
+    return np.ascontiguousarray(bits).view(np.float16).astype(np.float32)
+
+
+def _h16(a):
+    with np.errstate(over="ignore"):
+        return a.astype(np.float16).view(np.uint16)
+
+
+class CpuDecoder:
+    """Holds FP32 copies of the model's GEMM weights (converted once, outside any timing)."""
+
+    def __init__(self, cfg, weights, use_ref: bool = True):
+        self.cfg = cfg
+        self.ref = oracle.ref() if use_ref else None
+        self.own = oracle.own()
+        self.threads = self.ref.hardware_threads() if self.ref is not None else self.own.threads()
+        self.kind = "reference" if self.ref is not None else "port"
+        self.layers = []
+        for L in weights.layers:
+            self.layers.append({k: (_f32(_u16(v)) if k in ("qkv", "o", "gate_up", "down", "qkv_bias") else _u16(v).copy())
+                                for k, v in L.items()})
+        self.embed = _u16(weights.embed)
+        self.head = _f32(self.embed)
+        self.final_norm = _u16(weights.final_norm).copy()
+
+    # the non-GEMM stages, through the reference's CPU code when it is present
+    def _norm(self, x, w):
+        return self.ref.rmsnorm(x, w, self.cfg.eps, self.threads) if self.ref else self.own.rmsnorm(x, w, self.cfg.eps)
+
+    def _norm_res(self, res, x, w):
+        o = (self.ref.rmsnorm_residual(res, x, w, self.cfg.eps, 0.0, self.threads) if self.ref
+             else self.own.rmsnorm_residual(res, x, w, self.cfg.eps))
+        return o[0], o[1]
+
+    def _rope(self, h, pos, heads):
+        c = self.cfg
+        return (self.ref.rope(h, pos, heads, c.head_dim, c.rope_theta, self.threads) if self.ref
+                else self.own.rope(h, pos, heads, c.head_dim, c.rope_theta))
+
+    def step(self, ex, rows):
+        """The decode step the executor `ex` last uploaded, for its batch rows `rows`, recomputed on the
+        host: reads ids / positions / seq_lens / tables and those sequences' pages from the device, then
+        returns (seconds of host compute, tokens int32[len(rows)], logits float32[len(rows), vocab])."""
+        import torch
+        cfg = self.cfg
+        sel = torch.as_tensor(list(rows), device=ex.ids.device)
+        ids = ex.ids.index_select(0, sel).cpu().numpy()
+        pos = ex.positions.index_select(0, sel).cpu().numpy()
+        lens = ex.seq_lens.index_select(0, sel).cpu().numpy()
+        tables = ex.tables.index_select(0, sel).cpu().numpy()
+        used = np.unique(tables[tables > 0])
+        remap = np.zeros(int(tables.max()) + 1, np.int32)
+        remap[used] = np.arange(1, len(used) + 1, dtype=np.int32)
+        mb = (int(lens.max()) + 15) // 16
+        ctab = np.ascontiguousarray(remap[tables][:, :mb])
+        idx = torch.as_tensor(np.concatenate([[0], used]), device=ex.pool.device)
+        pools = [_u16(ex.pool[li].index_select(0, idx)).reshape(-1).copy() for li in range(cfg.layers)]
+        impl = self.ref or self.own
+
+        t0 = time.perf_counter()
+        x = np.ascontiguousarray(self.embed[ids])
+        mlp = None
+        for li, L in enumerate(self.layers):
+            if li == 0:
+                normed = self._norm(x, L["in_norm"])
+            else:
+                normed, x = self._norm_res(x, mlp, L["in_norm"])
+            qkv = _h16(_f32(normed) @ L["qkv"].T + L["qkv_bias"])
+            q = self._rope(np.ascontiguousarray(qkv[:, :cfg.q_width]), pos, cfg.q_heads)
+            k = self._rope(np.ascontiguousarray(qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width]), pos, cfg.kv_heads)
+            v = np.ascontiguousarray(qkv[:, cfg.q_width + cfg.kv_width:])
+            impl.kv_scatter(pools[li], k.reshape(-1), v.reshape(-1), cfg.kv_width, cfg.kv_width, ctab, mb, pos,
+                            cfg.kv_heads, cfg.head_dim)
+            if self.ref is not None:
+                att = self.ref.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim,
+                                               ex.scale, self.threads)
+            else:
+                att = self.own.paged_attention(q, pools[li], ctab, lens, cfg.q_heads, cfg.kv_heads, cfg.head_dim, ex.scale)
+            mlp = _h16(_f32(att) @ L["o"].T)
+            normed, x = self._norm_res(x, mlp, L["post_norm"])
+            gu = _h16(_f32(normed) @ L["gate_up"].T)
+            act = self.ref.silu_mul(gu, self.threads) if self.ref is not None else self.own.silu_mul(gu)
+            mlp = _h16(_f32(act) @ L["down"].T)
+        normed, x = self._norm_res(x, mlp, self.final_norm)
+        logits = _f32(normed) @ self.head.T
+        tokens = impl.argmax(_h16(logits))
+        return time.perf_counter() - t0, tokens, logits

@@ -167,3 +167,38 @@ def test_synthetic_requests_decode_over_long_contexts(weights):
     assert all(len(v) == 6 for v in out.values()) and len(out) == 5
     from redline_llm_b200 import kernels as K
     assert K.attention_health() == 0
+
+
+def test_full_size_model_steps_against_the_cpu_composition():
+    """The real architecture (28 layers, hidden 1536, FFN 8960, 12Q/2KV, vocab 151936, FP16 ~N(0,0.02)):
+    six teacher-forced decode steps of four cached sequences, each step's logits and greedy tokens against
+    the host composition of the reference's CPU functions + BLAS GEMMs. Token equality is required wherever
+    the host's top-1/top-2 margin exceeds the logit tolerance (coin flips are not kernel bugs)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from oracle.decode_step import CpuDecoder
+    cfg = ModelConfig()
+    w = ModelWeights(cfg, torch.device("cuda", 0), seed=0x5EED)
+    e = Engine(kv_pool_gb=0.3, max_batch=8, max_seq_len=512, config=cfg, weights=w, graph_buckets=[4])
+    rng = np.random.default_rng(11)
+    steps = 6
+    for i, ctx in enumerate((40, 100, 17, 64)):
+        rid = e.add_synthetic_request(ctx, steps, seed=300 + i)
+        e.scheduler.running[-1].forced_tokens = rng.integers(0, cfg.vocab, steps).tolist()
+    dec = CpuDecoder(cfg, w, use_ref=True)
+    worst, audited, agree = 0.0, 0, 0
+    for _ in range(steps):
+        e.step()
+        _, cpu_tok, cpu_logits = dec.step(e.exec, range(4))
+        gpu_logits = e.exec.logits[:4].float().cpu().numpy()
+        gpu_tok = e.exec.tokens[:4].cpu().numpy()
+        scale = float(np.abs(cpu_logits).max())
+        err = float(np.abs(gpu_logits - cpu_logits).max())
+        worst = max(worst, err / scale)
+        top2 = np.sort(cpu_logits, axis=1)[:, -2:]
+        for r in range(4):
+            if top2[r, 1] - top2[r, 0] > 2.5 * err:
+                audited += 1
+                agree += int(gpu_tok[r] == cpu_tok[r])
+    assert worst <= 0.02, worst
+    assert audited >= 12 and agree == audited, (agree, audited)
