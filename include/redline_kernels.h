@@ -190,6 +190,20 @@ int rl_launch_embed_gather(void* out, int64_t out_row_stride, const void* embed,
 int rl_launch_greedy_argmax(int32_t* out_tokens, const void* logits, int32_t num_seqs,
                             int32_t vocab_size, void* stream);
 
+/* Prefill-only: one sequence's cached K/V from the paged pool into dense [kv_heads, ctx_len,
+ * head_dim] staging views (position t <- block_table_row[t >> 4], slot t & 15), a bit move.
+ * Replaces LaunchKvGather, src/kernels/kernels.cuh:119-123 (src/kernels/kv_gather.cu:136-168). */
+int rl_launch_kv_gather(void* khat, void* vhat, int64_t khat_head_stride, int64_t khat_row_stride,
+                        int64_t vhat_head_stride, int64_t vhat_row_stride, const void* kv_pool_layer,
+                        const int32_t* block_table_row, int32_t ctx_len, int32_t num_kv_heads,
+                        int32_t head_dim, void* stream);
+
+/* Prefill-only: causal row softmax FP32 -> FP16 over dense [heads, chunk_len, kv_len]; row i sees
+ * keys j <= chunk_start + i; masked entries become exact +0 and are never read. Replaces
+ * LaunchPrefillSoftmax, src/kernels/kernels.cuh:185-187 (src/kernels/prefill_attention.cu:166-192). */
+int rl_launch_prefill_softmax(void* probs, const float* scores, int32_t num_q_heads, int32_t chunk_len,
+                              int32_t kv_len, int32_t chunk_start, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

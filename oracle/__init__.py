@@ -78,6 +78,9 @@ class _Own:
         _sig(L.rlo_silu_mul, None, u16p, C.c_int64, u16p, C.c_int32, C.c_int32)
         _sig(L.rlo_silu_mul_f32, None, u16p, C.c_int64, u16p, C.c_int32, C.c_int32)
         _sig(L.rlo_argmax, None, i32p, u16p, C.c_int32, C.c_int32)
+        _sig(L.rlo_kv_gather, None, u16p, u16p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, u16p, i32p,
+             C.c_int32, C.c_int32, C.c_int32)
+        _sig(L.rlo_prefill_softmax, None, u16p, f32p, C.c_int32, C.c_int32, C.c_int32, C.c_int32)
         _sig(L.rlo_omp_threads, C.c_int)
         _sig(L.rlo_set_threads, None, C.c_int)
 
@@ -208,6 +211,18 @@ class _Own:
         return out
 
 
+    def kv_gather(self, khat, vhat, head_stride, row_stride, pool, table_row, ctx_len, kv_heads, head_dim):
+        """Gathers into the flat uint16 arrays khat / vhat in place."""
+        self.L.rlo_kv_gather(khat, vhat, head_stride, row_stride, head_stride, row_stride, pool,
+                             np.ascontiguousarray(table_row, np.int32), ctx_len, kv_heads, head_dim)
+
+    def prefill_softmax(self, scores, chunk_start):
+        heads, chunk_len, kv_len = scores.shape
+        out = np.empty(scores.shape, np.uint16)
+        self.L.rlo_prefill_softmax(out, np.ascontiguousarray(scores, np.float32), heads, chunk_len, kv_len, chunk_start)
+        return out
+
+
 class _Ref:
     """The reference's own CPU code (tests/reference/*.hpp), when built."""
 
@@ -232,6 +247,9 @@ class _Ref:
              C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_double, C.c_int)
         _sig(L.rlr_silu_mul, None, u16p, u16p, C.c_int32, C.c_int32, C.c_int)
         _sig(L.rlr_argmax, None, i32p, u16p, C.c_int32, C.c_int32)
+        _sig(L.rlr_kv_gather, None, u16p, u16p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, u16p, C.c_int64, i32p,
+             C.c_int32, C.c_int32, C.c_int32)
+        _sig(L.rlr_prefill_softmax, None, u16p, f32p, C.c_int32, C.c_int32, C.c_int32, C.c_int32)
         _sig(L.rlr_hardware_threads, C.c_int)
 
     def half_to_double(self, bits):
@@ -313,6 +331,17 @@ class _Ref:
         rows, vocab = logits.shape
         out = np.empty(rows, np.int32)
         self.L.rlr_argmax(out, np.ascontiguousarray(logits), rows, vocab)
+        return out
+
+
+    def kv_gather(self, khat, vhat, head_stride, row_stride, pool, table_row, ctx_len, kv_heads, head_dim):
+        self.L.rlr_kv_gather(khat, vhat, head_stride, row_stride, head_stride, row_stride, pool, pool.size,
+                             np.ascontiguousarray(table_row, np.int32), ctx_len, kv_heads, head_dim)
+
+    def prefill_softmax(self, scores, chunk_start):
+        heads, chunk_len, kv_len = scores.shape
+        out = np.empty(scores.shape, np.uint16)
+        self.L.rlr_prefill_softmax(out, np.ascontiguousarray(scores, np.float32), heads, chunk_len, kv_len, chunk_start)
         return out
 
 

@@ -580,3 +580,48 @@ void rlo_set_threads(int n) {
   (void)n;
 #endif
 }
+
+/* ------------------------------------------------ prefill-side launchers */
+
+/*
+ * KV gather, the inverse bit move of the scatter: position t of ONE sequence comes from
+ * block_table_row[t/16], slot t%16 (tests/reference/pool_ref.hpp:68-87,
+ * src/kernels/kv_gather.cu:136-168). khat/vhat are [kv_heads, ctx_len, head_dim] views with a
+ * head stride and a row stride in elements.
+ */
+void rlo_kv_gather(uint16_t* khat, uint16_t* vhat, int64_t khat_head_stride, int64_t khat_row_stride,
+                   int64_t vhat_head_stride, int64_t vhat_row_stride, const uint16_t* pool,
+                   const int32_t* table_row, int32_t ctx_len, int32_t kv_heads, int32_t head_dim) {
+  for (int32_t t = 0; t < ctx_len; ++t) {
+    const int32_t block = table_row[t / RLO_BLOCK], slot = t % RLO_BLOCK;
+    for (int32_t h = 0; h < kv_heads; ++h) {
+      memcpy(khat + h * khat_head_stride + (int64_t)t * khat_row_stride,
+             pool + pool_index(block, 0, h, slot, 0, kv_heads, head_dim), (size_t)head_dim * 2);
+      memcpy(vhat + h * vhat_head_stride + (int64_t)t * vhat_row_stride,
+             pool + pool_index(block, 1, h, slot, 0, kv_heads, head_dim), (size_t)head_dim * 2);
+    }
+  }
+}
+
+/*
+ * Prefill causal softmax over FP32 scores [heads, chunk_len, kv_len]: query row i sits at global
+ * position chunk_start + i and sees keys j <= that position; live entries get
+ * fp16(exp(s - max) / sum) with FP64 max/sum, masked entries exact +0 and are never read
+ * (tests/reference/attention_ref.hpp:88-114, src/kernels/prefill_attention.cu:103-162).
+ */
+void rlo_prefill_softmax(uint16_t* probs, const float* scores, int32_t heads, int32_t chunk_len,
+                         int32_t kv_len, int32_t chunk_start) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int32_t h = 0; h < heads; ++h) {
+    for (int32_t i = 0; i < chunk_len; ++i) {
+      const size_t base = ((size_t)h * chunk_len + i) * (size_t)kv_len;
+      int32_t live = chunk_start + i + 1;
+      if (live > kv_len) live = kv_len;
+      double mx = -INFINITY, den = 0.0;
+      for (int32_t j = 0; j < live; ++j) if ((double)scores[base + j] > mx) mx = (double)scores[base + j];
+      for (int32_t j = 0; j < live; ++j) den += exp((double)scores[base + j] - mx);
+      for (int32_t j = 0; j < live; ++j) probs[base + j] = rlo_quantize(exp((double)scores[base + j] - mx) / den);
+      for (int32_t j = live > 0 ? live : 0; j < kv_len; ++j) probs[base + j] = 0;
+    }
+  }
+}

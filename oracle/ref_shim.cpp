@@ -167,6 +167,23 @@ void rlr_argmax(std::int32_t* out, const u16* logits, std::int32_t rows, std::in
   std::memcpy(out, r.data(), r.size() * sizeof(std::int32_t));
 }
 
+void rlr_kv_gather(u16* khat, u16* vhat, std::int64_t khat_head_stride, std::int64_t khat_row_stride,
+                   std::int64_t vhat_head_stride, std::int64_t vhat_row_stride, const u16* pool,
+                   std::int64_t pool_elems, const std::int32_t* table_row, std::int32_t ctx_len,
+                   std::int32_t kv_heads, std::int32_t head_dim) {
+  const std::vector<u16> p(pool, pool + pool_elems);
+  ref::GatherReference(khat, vhat, khat_head_stride, khat_row_stride, vhat_head_stride, vhat_row_stride, p,
+                       table_row, ctx_len, kv_heads, head_dim);
+}
+
+void rlr_prefill_softmax(u16* probs, const float* scores, std::int32_t heads, std::int32_t chunk_len,
+                         std::int32_t kv_len, std::int32_t chunk_start) {
+  const std::size_t n = std::size_t(heads) * chunk_len * kv_len;
+  const auto r = ref::PrefillSoftmaxReference(std::vector<float>(scores, scores + n), heads, chunk_len, kv_len,
+                                              chunk_start);
+  std::memcpy(probs, r.data(), n * 2);
+}
+
 int rlr_hardware_threads() { return static_cast<int>(std::thread::hardware_concurrency()); }
 
 } // extern "C"

@@ -16,11 +16,11 @@
 // cudaGetLastError() after the step's synchronisation
 // (src/core/model_executor.cpp:711-712).
 //
-// Every launcher inside the captured decode graph is provided: LaunchEmbedGather,
-// LaunchRmsNorm, LaunchRmsNormResidual, LaunchRopeInplace, LaunchKvScatter,
-// LaunchPagedAttentionDecode (+ the test-only cross-check launcher), LaunchSiluMul
-// and LaunchGreedyArgmax. The two prefill-only launchers of the reference header
-// (LaunchKvGather, LaunchPrefillSoftmax) keep their reference implementations.
+// All eleven launchers of the reference header are provided: the nine inside the
+// captured decode graph (LaunchEmbedGather, LaunchRmsNorm, LaunchRmsNormResidual,
+// LaunchRopeInplace, LaunchKvScatter, LaunchPagedAttentionDecode + the test-only
+// cross-check launcher, LaunchSiluMul, LaunchGreedyArgmax) and the two prefill-only
+// ones (LaunchKvGather, LaunchPrefillSoftmax).
 #pragma once
 
 #include <cstdint>
@@ -120,6 +120,24 @@ inline void LaunchPagedAttentionDecodeOracle(half* out, std::int64_t out_row_str
                                                        max_blocks_per_seq, num_q_heads, num_kv_heads,
                                                        head_dim, scale, stream),
                 "LaunchPagedAttentionDecodeOracle");
+}
+
+inline void LaunchKvGather(half* khat, half* vhat, std::int64_t khat_head_stride,
+                           std::int64_t khat_row_stride, std::int64_t vhat_head_stride,
+                           std::int64_t vhat_row_stride, const half* kv_pool_layer,
+                           const std::int32_t* block_table_row, std::int32_t ctx_len,
+                           std::int32_t num_kv_heads, std::int32_t head_dim, cudaStream_t stream) {
+  detail::Check(rl_launch_kv_gather(khat, vhat, khat_head_stride, khat_row_stride, vhat_head_stride,
+                                    vhat_row_stride, kv_pool_layer, block_table_row, ctx_len, num_kv_heads,
+                                    head_dim, stream),
+                "LaunchKvGather");
+}
+
+inline void LaunchPrefillSoftmax(half* probs, const float* scores, std::int32_t num_q_heads,
+                                 std::int32_t chunk_len, std::int32_t kv_len, std::int32_t chunk_start,
+                                 cudaStream_t stream) {
+  detail::Check(rl_launch_prefill_softmax(probs, scores, num_q_heads, chunk_len, kv_len, chunk_start, stream),
+                "LaunchPrefillSoftmax");
 }
 
 inline void LaunchSiluMul(half* out, const half* gate_up, std::int32_t num_tokens,

@@ -1,0 +1,124 @@
+// The two prefill-side launchers of the kernel contract, sm_100a. They are not on the decode hot
+// path (never inside the captured decode graph, src/kernels/kv_gather.cu:43-44); they are provided
+// so the drop-in header covers every launcher of src/kernels/kernels.cuh.
+//
+// LaunchKvGather (src/kernels/kernels.cuh:101-123, src/kernels/kv_gather.cu:136-168): the inverse
+// bit move of the scatter for ONE sequence - position t comes from block_table_row[t >> 4], slot
+// t & 15 - into dense [kv_heads, ctx_len, head_dim] staging views. One warp per position.
+//
+// LaunchPrefillSoftmax (src/kernels/kernels.cuh:160-187, src/kernels/prefill_attention.cu:103-162):
+// causal row softmax FP32 -> FP16 over [heads, chunk_len, kv_len]; query row i sits at position
+// chunk_start + i and sees keys j <= it; FP32 max and sum, one FP16 rounding of exp(s - max) / sum;
+// masked entries are written as exact +0 and their scores are never read. One CTA per (row, head),
+// three passes over the row (it stays in L1/L2), fixed reduction trees (run-to-run identical bits).
+#include "common.cuh"
+
+#if defined(__USE_FAST_MATH__)
+#error "the prefill softmax needs the precise expf"
+#endif
+
+namespace rl {
+namespace {
+
+template <typename Word>
+__global__ void __launch_bounds__(128)
+KvGatherKernel(half* __restrict__ khat, half* __restrict__ vhat, int64_t khat_head_stride,
+               int64_t khat_row_stride, int64_t vhat_head_stride, int64_t vhat_row_stride,
+               const half* __restrict__ pool, const int32_t* __restrict__ table_row, int ctx_len,
+               int num_kv_heads, int head_dim) {
+  constexpr int kPer = sizeof(Word) / sizeof(half);
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= ctx_len) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t block = table_row[t >> kKvBlockShift];
+  const int slot = static_cast<int>(t) & (kKvBlock - 1);
+  const int words_per_head = head_dim / kPer;
+  const int words_per_side = num_kv_heads * words_per_head;
+  for (int w = lane; w < 2 * words_per_side; w += 32) {
+    const int kv = w >= words_per_side;
+    const int r = w - kv * words_per_side;
+    const int h = r / words_per_head;
+    const int dw = r - h * words_per_head;
+    const int64_t src = (((block * 2 + kv) * num_kv_heads + h) * kKvBlock + slot) * static_cast<int64_t>(head_dim);
+    half* dst = kv ? vhat + h * vhat_head_stride + t * vhat_row_stride
+                   : khat + h * khat_head_stride + t * khat_row_stride;
+    reinterpret_cast<Word*>(dst)[dw] = reinterpret_cast<const Word*>(pool + src)[dw];
+  }
+}
+
+constexpr int kSoftmaxThreads = 256;
+
+__device__ __forceinline__ float BlockReduce(float v, bool is_max, float* scratch) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = is_max ? fmaxf(v, o) : v + o;
+  }
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = scratch[0];
+#pragma unroll
+  for (int w = 1; w < kSoftmaxThreads / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  __syncthreads();  // scratch is reused by the next reduction
+  return r;
+}
+
+__global__ void __launch_bounds__(kSoftmaxThreads)
+PrefillSoftmaxKernel(half* __restrict__ probs, const float* __restrict__ scores, int chunk_len, int kv_len,
+                     int chunk_start) {
+  __shared__ float scratch[kSoftmaxThreads / 32];
+  const int row = blockIdx.x, head = blockIdx.y;
+  const size_t base = (static_cast<size_t>(head) * chunk_len + row) * static_cast<size_t>(kv_len);
+  const float* s = scores + base;
+  half* p = probs + base;
+  const int live = min(chunk_start + row + 1, kv_len);
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < live; j += kSoftmaxThreads) mx = fmaxf(mx, s[j]);
+  mx = BlockReduce(mx, true, scratch);
+  float sum = 0.0f;
+  for (int j = threadIdx.x; j < live; j += kSoftmaxThreads) sum += expf(s[j] - mx);
+  sum = BlockReduce(sum, false, scratch);
+  for (int j = threadIdx.x; j < kv_len; j += kSoftmaxThreads)
+    p[j] = j < live ? __float2half_rn(expf(s[j] - mx) / sum) : __ushort_as_half(0);
+}
+
+}  // namespace
+}  // namespace rl
+
+extern "C" int rl_launch_kv_gather(void* khat, void* vhat, int64_t khat_head_stride, int64_t khat_row_stride,
+                                   int64_t vhat_head_stride, int64_t vhat_row_stride, const void* kv_pool_layer,
+                                   const int32_t* block_table_row, int32_t ctx_len, int32_t num_kv_heads,
+                                   int32_t head_dim, void* stream) {
+  using namespace rl;
+  if (ctx_len <= 0 || num_kv_heads <= 0 || head_dim <= 0) return RL_OK;
+  if (!khat || !vhat || !kv_pool_layer || !block_table_row)
+    return Fail(RL_E_NULL_POINTER, "kv_gather: null device pointer");
+  const dim3 grid((ctx_len + 3) / 4), block(128);
+  half* k = static_cast<half*>(khat);
+  half* v = static_cast<half*>(vhat);
+  const half* pool = static_cast<const half*>(kv_pool_layer);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = head_dim % 8 == 0 && khat_head_stride % 8 == 0 && khat_row_stride % 8 == 0 &&
+                   vhat_head_stride % 8 == 0 && vhat_row_stride % 8 == 0 && Aligned16(khat) && Aligned16(vhat) &&
+                   Aligned16(kv_pool_layer);
+  if (vec) {
+    KvGatherKernel<uint4><<<grid, block, 0, s>>>(k, v, khat_head_stride, khat_row_stride, vhat_head_stride,
+                                                 vhat_row_stride, pool, block_table_row, ctx_len, num_kv_heads, head_dim);
+  } else {
+    KvGatherKernel<half><<<grid, block, 0, s>>>(k, v, khat_head_stride, khat_row_stride, vhat_head_stride,
+                                                vhat_row_stride, pool, block_table_row, ctx_len, num_kv_heads, head_dim);
+  }
+  return LaunchStatus("kv_gather");
+}
+
+extern "C" int rl_launch_prefill_softmax(void* probs, const float* scores, int32_t num_q_heads, int32_t chunk_len,
+                                         int32_t kv_len, int32_t chunk_start, void* stream) {
+  using namespace rl;
+  if (num_q_heads <= 0 || chunk_len <= 0 || kv_len <= 0) return RL_OK;
+  if (!probs || !scores) return Fail(RL_E_NULL_POINTER, "prefill_softmax: null device pointer");
+  if (chunk_start < 0) return Fail(RL_E_BAD_SHAPE, "prefill_softmax: negative chunk_start");
+  if (num_q_heads > 65535) return Fail(RL_E_TOO_LARGE, "prefill_softmax: more than 65535 heads");
+  PrefillSoftmaxKernel<<<dim3(chunk_len, num_q_heads), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<half*>(probs), scores, chunk_len, kv_len, chunk_start);
+  return LaunchStatus("prefill_softmax");
+}

@@ -411,24 +411,26 @@ class ModelExecutor:
         self.torch.cuda.current_stream().synchronize()
         return self.h_tokens[:rows].tolist()
 
-    # ---- prompt ingestion (not on the hot path): chunked, eager, library attention
+    # ---- prompt ingestion (not on the hot path): chunked, eager, the reference's gather/GEMM/softmax/GEMM composite
     def prefill_chunk(self, r: Request, start: int, end: int) -> Optional[int]:
         torch, K, cfg, w = self.torch, self.K, self.cfg, self.w
-        import torch.nn.functional as F
         n = end - start
         dev = self.device
         ids = torch.tensor(r.prompt[start:end], dtype=torch.int32, device=dev)
         pos = torch.arange(start, end, dtype=torch.int32, device=dev)
         row = torch.zeros(1, self.mbps, dtype=torch.int32, device=dev)
         row[0, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32, device=dev)
-        x = w.embed.index_select(0, ids)
+        x = torch.empty(n, cfg.hidden, dtype=torch.float16, device=dev)
+        K.launch_embed_gather(x, cfg.hidden, w.embed, ids, n, cfg.hidden)
         normed, mlp = torch.empty_like(x), torch.empty_like(x)
         qkv = torch.empty(n, cfg.qkv_width, dtype=torch.float16, device=dev)
         gu = torch.empty(n, 2 * cfg.inter, dtype=torch.float16, device=dev)
-        slots = torch.arange(end, device=dev)
-        blk = row[0, (slots // KV_BLOCK).long()].long()
-        slot = (slots % KV_BLOCK).long()
-        mask = (torch.arange(end, device=dev)[None, :] <= pos[:, None].long())
+        # staging for the prefill attention composite (src/core/model_executor.cpp:1219-1290):
+        # kv_gather -> scores GEMMs -> causal softmax -> PV GEMMs, the GEMMs being library calls
+        khat = torch.empty(cfg.kv_heads, end, cfg.head_dim, dtype=torch.float16, device=dev)
+        vhat = torch.empty_like(khat)
+        group = cfg.q_heads // cfg.kv_heads
+        probs = torch.empty(cfg.q_heads, n, end, dtype=torch.float16, device=dev)
         for li, L in enumerate(w.layers):
             if li == 0:
                 K.launch_rms_norm(normed, x, L["in_norm"], n, cfg.hidden, cfg.eps)
@@ -440,11 +442,13 @@ class ModelExecutor:
             K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, row, 0, pos, n,
                                 cfg.kv_heads, cfg.head_dim, k_offset=cfg.q_width,
                                 v_offset=cfg.q_width + cfg.kv_width)
-            kc = self.pool[li][blk, 0, :, slot, :].permute(1, 0, 2)   # [kv_heads, end, d]
-            vc = self.pool[li][blk, 1, :, slot, :].permute(1, 0, 2)
-            q = qkv[:, :cfg.q_width].view(n, cfg.q_heads, cfg.head_dim).permute(1, 0, 2)
-            o = F.scaled_dot_product_attention(q[None], kc[None], vc[None], attn_mask=mask[None, None],
-                                               enable_gqa=True)[0]
+            K.launch_kv_gather(khat, vhat, end * cfg.head_dim, cfg.head_dim, end * cfg.head_dim, cfg.head_dim,
+                               self.pool[li], row, end, cfg.kv_heads, cfg.head_dim)
+            q = qkv[:, :cfg.q_width].view(n, cfg.q_heads, cfg.head_dim).permute(1, 0, 2)      # [q_heads, n, d]
+            kx = khat.repeat_interleave(group, dim=0)                                          # [q_heads, end, d]
+            scores = torch.bmm(q.float(), kx.float().transpose(1, 2)) * self.scale             # FP32, scaled
+            K.launch_prefill_softmax(probs, scores.contiguous(), cfg.q_heads, n, end, start)
+            o = torch.bmm(probs, vhat.repeat_interleave(group, dim=0))                         # [q_heads, n, d]
             attn = o.permute(1, 0, 2).reshape(n, cfg.q_width).contiguous()
             torch.matmul(attn, L["o"].t(), out=mlp)
             K.launch_rms_norm_residual(normed, x, mlp, L["post_norm"], n, cfg.hidden, cfg.eps)
@@ -456,7 +460,9 @@ class ModelExecutor:
             return None
         K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, n, cfg.hidden, cfg.eps)
         logits = torch.matmul(normed[-1:], w.lm_head.t())
-        return int(torch.argmax(logits, dim=-1).item())
+        tok = torch.zeros(1, dtype=torch.int32, device=dev)
+        K.launch_greedy_argmax(tok, logits, 1, cfg.vocab)
+        return int(tok.item())
 
 
 class Engine:

@@ -22,7 +22,7 @@ ABI_SYMBOLS = (
     "rl_launch_paged_attention_decode", "rl_launch_paged_attention_decode_check",
     "rl_launch_silu_mul", "rl_attention_health", "rl_launch_paged_attention_decode_static",
     "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
-    "rl_attention_set_prologue_overlap",
+    "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
 )
 
 
@@ -56,6 +56,8 @@ def lib() -> C.CDLL:
         L.rl_launch_embed_gather.argtypes = [vp, i64, vp, vp, i32, i32, vp]
         L.rl_launch_greedy_argmax.argtypes = [vp, vp, i32, i32, vp]
         L.rl_attention_set_prologue_overlap.argtypes = [C.c_int]
+        L.rl_launch_kv_gather.argtypes = [vp, vp, i64, i64, i64, i64, vp, vp, i32, i32, i32, vp]
+        L.rl_launch_prefill_softmax.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.rl_launch_rope_kv_scatter.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, vp]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -150,6 +152,18 @@ def launch_rope_kv_scatter(qkv, q_row_stride, kv_pool_layer, block_tables, block
                                            block_tables.data_ptr(), block_table_row_stride,
                                            positions.data_ptr(), num_tokens, num_q_heads, num_kv_heads,
                                            head_dim, rope_theta, _stream(stream)), "rope + kv scatter")
+
+
+def launch_kv_gather(khat, vhat, khat_head_stride, khat_row_stride, vhat_head_stride, vhat_row_stride,
+                     kv_pool_layer, block_table_row, ctx_len, num_kv_heads, head_dim, stream=None):
+    _check(lib().rl_launch_kv_gather(_ptr(khat), _ptr(vhat), khat_head_stride, khat_row_stride, vhat_head_stride,
+                                     vhat_row_stride, _ptr(kv_pool_layer), block_table_row.data_ptr(), ctx_len,
+                                     num_kv_heads, head_dim, _stream(stream)), "LaunchKvGather")
+
+
+def launch_prefill_softmax(probs, scores, num_q_heads, chunk_len, kv_len, chunk_start, stream=None):
+    _check(lib().rl_launch_prefill_softmax(_ptr(probs), scores.data_ptr(), num_q_heads, chunk_len, kv_len,
+                                           chunk_start, _stream(stream)), "LaunchPrefillSoftmax")
 
 
 def launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidden_size, stream=None):

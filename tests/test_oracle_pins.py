@@ -160,3 +160,23 @@ def test_live_scatter_and_attention_config_shapes(own, ref):
     o1 = own.paged_attention(a["q"], a["pool"], a["tables"], a["seq_lens"], 12, 2, 128, a["scale"])
     o2 = ref.paged_attention(a["q"], a["pool"], a["tables"], a["seq_lens"], 12, 2, 128, a["scale"], threads=4)
     assert np.array_equal(o1, o2)
+
+
+def test_live_gather_and_prefill_softmax(own, ref):
+    a = wl.config_attention(lens=[257], num_blocks=40, seed=0x6A7, fill="uniform")
+    ctx = 257
+    for head_stride, row_stride in ((ctx * 128, 128), (300 * 133, 133)):
+        sent = own.uniform_half(0x6A8, 2 * head_stride, -1.0, 1.0)
+        k1, v1, k2, v2 = sent.copy(), sent.copy(), sent.copy(), sent.copy()
+        own.kv_gather(k1, v1, head_stride, row_stride, a["pool"], a["tables"][0], ctx, 2, 128)
+        ref.kv_gather(k2, v2, head_stride, row_stride, a["pool"], a["tables"][0], ctx, 2, 128)
+        assert np.array_equal(k1, k2) and np.array_equal(v1, v2)
+        assert not np.array_equal(k1, sent)
+    rng = np.random.default_rng(9)
+    for (h, c, kv, start) in ((2, 5, 5, 0), (3, 7, 40, 33), (1, 1, 1, 0), (2, 16, 257, 241)):
+        sc = rng.normal(0, 3, (h, c, kv)).astype(np.float32)
+        for i in range(c):
+            sc[:, i, start + i + 1:] = np.nan  # masked scores are never read
+        p1, p2 = own.prefill_softmax(sc, start), ref.prefill_softmax(sc, start)
+        assert np.array_equal(p1, p2)
+        assert not ((p1 & 0x7FFF) > 0x7C00).any() and (p1[:, 0, start + 1:] == 0).all()
