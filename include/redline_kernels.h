@@ -102,8 +102,8 @@ int rl_launch_rope_kv_scatter(void* q, void* k, const void* v, int64_t q_row_str
  * written. head_dim must be 128 and num_q_heads == 6 * num_kv_heads (as the
  * reference, src/kernels/paged_attention.cu:459-484,519-520). The KV axis is
  * split across the whole grid in balanced page ranges and merged in a fixed
- * order (the reference has no split variant; docs/DESIGN.md:884 names it as
- * future work), so long and ragged contexts need no other entry point.
+ * order (the reference has no split variant: one CTA walks a whole (sequence, head) serially,
+ * src/kernels/paged_attention.cu:176,214), so long and ragged contexts need no other entry point.
  * Uses the per-device workspace (see rl_kernels_init).
  * Replaces LaunchPagedAttentionDecode, src/kernels/kernels.cuh:141-146
  * (src/kernels/paged_attention.cu:507-532).

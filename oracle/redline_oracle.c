@@ -382,7 +382,7 @@ void rlo_rope_inv_freq_f32(float* table, int32_t head_dim, float theta) {
 
 /*
  * Element index in one layer's pool slice [num_blocks, 2, kv_heads, 16,
- * head_dim]: tests/reference/pool_ref.hpp:21-34, docs/DESIGN.md:150-155.
+ * head_dim]: tests/reference/pool_ref.hpp:21-34, src/kernels/kv_scatter.cu:82-88.
  */
 static inline int64_t pool_index(int32_t block, int32_t kv, int32_t head, int32_t slot, int32_t d,
                                  int32_t kv_heads, int32_t head_dim) {

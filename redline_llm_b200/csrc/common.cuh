@@ -31,6 +31,35 @@ struct DeviceFacts {
 const DeviceFacts& CurrentDeviceFacts();
 int CurrentDeviceIndex();
 
+// Process-wide opt-in (rl_attention_set_prologue_overlap): launch the decode-sized kernels with
+// programmatic stream serialisation. Kernels launched this way start with griddepcontrol.wait (the
+// attention kernel after its table walk), so they never read or write before the previous kernel of
+// the stream has completed; what overlaps is the launch itself and, for attention, the walk.
+extern bool g_launch_overlap;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t LaunchOverlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_launch_overlap ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// First statement of a kernel that may be launched by LaunchOverlapped: let the next such launch
+// be set up now, then wait for the previous kernel of the stream (a no-op for ordinary launches).
+__device__ __forceinline__ void DependentLaunchGate() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 inline bool Aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
 
 // 16-byte global access. .nc loads are for data this kernel never writes.

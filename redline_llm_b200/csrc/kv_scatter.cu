@@ -2,7 +2,7 @@
 // for sm_100a. A pure bit move (NaN payloads survive): for token t,
 //   p = positions[t]; block = block_tables[t*row_stride + (p >> 4)]; slot = p & 15
 //   pool[block][0][h][slot][:] = k[t][h][:],  pool[block][1][h][slot][:] = v[t][h][:]
-// (src/kernels/kv_scatter.cu:98-137; pool index formula docs/DESIGN.md:150-155).
+// (src/kernels/kv_scatter.cu:98-137; pool index formula src/kernels/kv_scatter.cu:82-88).
 // row_stride == 0 shares one table row among all tokens (prefill).
 //
 // Mapping: one warp per token; a token's K and V rows are 2*H*D/8 16-byte

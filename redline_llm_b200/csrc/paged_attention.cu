@@ -13,7 +13,7 @@
 //    equal contiguous share per CTA (one persistent CTA per SM). A batch of 64
 //    short sequences and a batch holding a few 32k-token sequences both load
 //    every SM equally; the reference walks one (sequence, head) per CTA serially
-//    and names the split as future work (docs/DESIGN.md:884). The launch shape
+//    (src/kernels/paged_attention.cu:176,214) and has no split variant. The launch shape
 //    depends only on the SM count, never on device-side seq_lens, so it can be
 //    frozen in a CUDA graph.
 //  * A CTA writes an item it covers completely straight to `out`. An item cut
@@ -629,7 +629,6 @@ struct DeviceState {
 constexpr int kMaxDevices = 64;
 DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
-bool g_prologue_overlap = false;  // rl_attention_set_prologue_overlap
 void* g_timeline = nullptr;  // diagnostics build only
 std::mutex g_mutex;
 
@@ -741,7 +740,7 @@ extern "C" int rl_attention_health(int* flag_out) {
 }
 
 extern "C" int rl_attention_set_prologue_overlap(int enable) {
-  rl::attn::g_prologue_overlap = enable != 0;
+  rl::g_launch_overlap = enable != 0;
   return RL_OK;
 }
 
@@ -789,22 +788,9 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
 #ifdef RL_ATTN_TIMELINE
     p.timeline = static_cast<unsigned long long*>(g_timeline);
 #endif
-    if (g_prologue_overlap) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(st->ctas);
-      cfg.blockDim = dim3(kThreads);
-      cfg.dynamicSmemBytes = kSmemBytes;
-      cfg.stream = s;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      const cudaError_t e = cudaLaunchKernelEx(&cfg, PagedAttentionSplitKernel, p, tile_map);
-      if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention_decode: %s", cudaGetErrorString(e));
-    } else {
-      PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
-    }
+    const cudaError_t e = LaunchOverlapped(PagedAttentionSplitKernel, dim3(st->ctas), dim3(kThreads), kSmemBytes, s,
+                                           p, tile_map);
+    if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention_decode: %s", cudaGetErrorString(e));
   }
   return LaunchStatus("paged_attention_decode");
 }

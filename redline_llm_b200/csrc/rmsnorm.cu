@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(32 * CPL)
 RmsNormBlockKernel(half* __restrict__ out, half* __restrict__ residual, const half* __restrict__ input,
                    const half* __restrict__ weight, int hidden, float eps) {
   __shared__ float group_sum[CPL];
+  DependentLaunchGate();
   const int c = threadIdx.x;
   const int chunks = hidden >> 3;
   const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
@@ -194,8 +195,8 @@ int Launch(half* out, half* residual, const half* input, const half* weight, int
 #define RL_NORM_CASE(N)                                                                             \
   case N:                                                                                           \
     if (few_rows)                                                                                   \
-      RmsNormBlockKernel<N, kResidual><<<num_tokens, 32 * N, 0, stream>>>(out, residual, input,     \
-                                                                          weight, hidden, eps);     \
+      LaunchOverlapped(RmsNormBlockKernel<N, kResidual>, dim3(num_tokens), dim3(32 * N), 0, stream, \
+                       out, residual, input, weight, hidden, eps);                                  \
     else                                                                                            \
       RmsNormWarpKernel<N, kResidual><<<grid, block, 0, stream>>>(out, residual, input, weight,     \
                                                                   num_tokens, hidden, eps);         \

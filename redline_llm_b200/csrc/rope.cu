@@ -137,8 +137,8 @@ RopeScatterKernel(half* q, half* k, const half* __restrict__ v, int64_t q_row_st
                   int num_kv_heads, int head_dim, const __grid_constant__ InvFreq inv_freq) {
   __shared__ __align__(16) half2 cs[kMaxPairs];
   // the attention launch that follows may begin its table walk now (it waits for this grid to
-  // complete before it reads the pool or Q)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // complete before it reads the pool or Q); this grid itself waits for the QKV GEMM before it
+  DependentLaunchGate();
   const int64_t row = blockIdx.x;
   const int half_dim = head_dim >> 1;
   const int p = positions[row];
@@ -238,9 +238,9 @@ extern "C" int rl_launch_rope_kv_scatter(void* q, void* k, const void* v, int64_
                                 block_table_row_stride, positions, num_tokens, num_kv_heads, head_dim, stream);
   }
   const InvFreq& table = TableFor(rope_theta, head_dim);
-  RopeScatterKernel<<<num_tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<half*>(q), static_cast<half*>(k), static_cast<const half*>(v), q_row_stride, k_row_stride,
-      v_row_stride, static_cast<half*>(kv_pool_layer), block_tables, block_table_row_stride, positions,
-      num_q_heads, num_kv_heads, head_dim, table);
+  LaunchOverlapped(RopeScatterKernel, dim3(num_tokens), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                   static_cast<half*>(q), static_cast<half*>(k), static_cast<const half*>(v), q_row_stride,
+                   k_row_stride, v_row_stride, static_cast<half*>(kv_pool_layer), block_tables,
+                   block_table_row_stride, positions, num_q_heads, num_kv_heads, head_dim, table);
   return LaunchStatus("rope_kv_scatter");
 }

@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 namespace rl {
+bool g_launch_overlap = false;
 namespace {
 thread_local char g_error[512] = "";
 constexpr int kMaxDevices = 64;

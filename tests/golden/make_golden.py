@@ -1,7 +1,7 @@
 """Generates the committed golden vectors under tests/golden/.
 
-Run in a container where the reference tree is mounted (default
-/root/reference):  python tests/golden/make_golden.py
+Run where the reference tree is mounted (its location comes from the
+REDLINE_REFERENCE environment variable):  python tests/golden/make_golden.py
 
 Sources of truth, none of them this repository's code:
   * the reference's committed RoPE capture tests/data/rope_fixture.json
