@@ -48,9 +48,19 @@ namespace attn {
 
 constexpr int kHeadDim = 128;
 constexpr int kGroup = 6;               // query heads per KV head
-constexpr int kWarps = 8;
+#ifndef RL_ATTN_WARPS
+#define RL_ATTN_WARPS 8
+#endif
+#ifndef RL_ATTN_STAGES
+#define RL_ATTN_STAGES 3
+#endif
+constexpr int kWarps = RL_ATTN_WARPS;   // 4, 8 or 12: the merge maps 128 threads to one head's 128 columns
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 3;              // pages in flight per warp
+constexpr int kStages = RL_ATTN_STAGES; // pages in flight per warp
+constexpr int kMergeGroups = kThreads / 128;          // heads merged side by side
+constexpr int kHeadsPerGroup = 6 / kMergeGroups;      // heads each 128-thread group walks
+static_assert(kThreads % 128 == 0 && 6 % kMergeGroups == 0, "warps per CTA must be 4, 8 or 12");
+constexpr int kSeqsPerThread = (1024 + kThreads - 1) / kThreads;
 constexpr int kPageBytes = kKvBlock * kHeadDim * 2;  // 4096: one (block, kv, head) tile
 constexpr int kStageBytes = 2 * kPageBytes;          // K tile + V tile
 constexpr int kMaxSeqsPerLaunch = 1024;
@@ -245,10 +255,10 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   // ---- page prefix over sequences (every CTA computes the same table) ----
   {
     __shared__ int warp_tot[kWarps];
-    int n[4], sum = 0;
+    int n[kSeqsPerThread], sum = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int s = tid * 4 + i;
+    for (int i = 0; i < kSeqsPerThread; ++i) {
+      const int s = tid * kSeqsPerThread + i;
       int len = s < num_seqs ? p.seq_lens[s] : 0;
       len = min(len, p.max_blocks * kKvBlock);
       n[i] = len > 0 ? (len + kKvBlock - 1) >> kKvBlockShift : 0;
@@ -266,13 +276,13 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     for (int w = 0; w < warp; ++w) base += warp_tot[w];
     int run = base + incl - sum;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int s = tid * 4 + i;
+    for (int i = 0; i < kSeqsPerThread; ++i) {
+      const int s = tid * kSeqsPerThread + i;
       if (s <= num_seqs) prefix[s] = run;
       run += n[i];
     }
-    if (tid == kThreads - 1 && num_seqs == kMaxSeqsPerLaunch) prefix[num_seqs] = run;
-    if (tid < kStages * kWarps) MbarInit(bars + tid * 8, 1);
+    if (tid == kThreads - 1 && num_seqs >= kThreads * kSeqsPerThread) prefix[num_seqs] = run;
+    for (int b = tid; b < kStages * kWarps; b += kThreads) MbarInit(bars + b * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
@@ -490,8 +500,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       float* rec = p.partials +
                    (static_cast<size_t>(blockIdx.x) * 2 + (item_begin < share_begin ? 0 : 1)) * kPartialFloats;
 #pragma unroll
-      for (int qi = 0; qi < 3; ++qi) {
-        const int qh = (tid >> 7) + 2 * qi;
+      for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+        const int qh = (tid >> 7) + kMergeGroups * qi;
         float mx = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mbuf[w * 8 + qh]);
@@ -534,33 +544,37 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
           __threadfence();
           // Two passes over the contributors' records (L2 reads, independent per contributor):
           // running max per head, then the rescaled sums, always in CTA order.
-          const int q0 = tid >> 7;  // this thread's heads: q0, q0 + 2, q0 + 4
-          float mx[3] = {-INFINITY, -INFINITY, -INFINITY};
+          const int q0 = tid >> 7;  // this thread's heads: q0, q0 + kMergeGroups, ...
+          float mx[kHeadsPerGroup];
+#pragma unroll
+          for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = -INFINITY;
 #pragma unroll 4
           for (int c = c_first; c <= c_last; ++c) {
             if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
             const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats +
                              kGroup * kHeadDim + q0;
 #pragma unroll
-            for (int qi = 0; qi < 3; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + 2 * qi));
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + kMergeGroups * qi));
           }
-          float acc[3] = {0.0f, 0.0f, 0.0f}, den[3] = {0.0f, 0.0f, 0.0f};
+          float acc[kHeadsPerGroup], den[kHeadsPerGroup];
+#pragma unroll
+          for (int qi = 0; qi < kHeadsPerGroup; ++qi) acc[qi] = den[qi] = 0.0f;
 #pragma unroll 2
           for (int c = c_first; c <= c_last; ++c) {
             if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
             const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
 #pragma unroll
-            for (int qi = 0; qi < 3; ++qi) {
-              const int qh = q0 + 2 * qi;
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+              const int qh = q0 + kMergeGroups * qi;
               const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx[qi]);
               acc[qi] = fmaf(f, __ldcg(r + qh * kHeadDim + d), acc[qi]);
               den[qi] = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), den[qi]);
             }
           }
 #pragma unroll
-          for (int qi = 0; qi < 3; ++qi) {
+          for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
             p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
-                  (static_cast<int64_t>(sc.head) * kGroup + q0 + 2 * qi) * kHeadDim + d] =
+                  (static_cast<int64_t>(sc.head) * kGroup + q0 + kMergeGroups * qi) * kHeadDim + d] =
                 __float2half_rn(acc[qi] / den[qi]);
           }
         }

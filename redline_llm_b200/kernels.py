@@ -13,7 +13,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libredline_b200.so")
+# REDLINE_B200_LIB points at another build of the same library (e.g. one compiled with other tuning macros)
+_LIB_PATH = os.environ.get("REDLINE_B200_LIB") or os.path.join(_HERE, "libredline_b200.so")
 _lib = None
 
 ABI_SYMBOLS = (
