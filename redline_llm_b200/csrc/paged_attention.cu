@@ -17,11 +17,16 @@
 //    depends only on the SM count, never on device-side seq_lens, so it can be
 //    frozen in a CUDA graph.
 //  * A CTA writes an item it covers completely straight to `out`. An item cut
-//    by a CTA boundary leaves (o, m, l) partials in a small per-device
-//    workspace (at most two per CTA); each contributor takes a ticket from an
-//    atomic counter and the LAST one to arrive merges all partials of the item
-//    in CTA order. Nobody waits for anybody, and the merge order is fixed, so
-//    results are bit-reproducible run to run whoever arrives last.
+//    by a CTA boundary is finished by whichever contributor comes LAST, and
+//    nobody ever waits: a contributor first looks (load-acquire) whether all
+//    the others have already published - usual at the tail of a share, whose
+//    neighbour met the same item at the very start of its own share - and then
+//    simply reads their (o, m, l) records, under its own fold, and writes the
+//    item; otherwise it publishes its record in a small per-device workspace
+//    (at most two per CTA) and takes a ticket from an atomic counter, and the
+//    holder of the last ticket merges. Either way the records are combined in
+//    CTA order with the same arithmetic, so results are bit-reproducible run to
+//    run whoever ends up doing it.
 //  * K/V pages are fetched by TMA - one cp.async.bulk.tensor per page brings the
 //    K tile and the V tile of a head (8 KiB, 128-byte swizzle, so the ldmatrix
 //    reads are bank-conflict free) - into a private 3-deep ring per warp, with
@@ -61,6 +66,7 @@ constexpr int kMergeGroups = kThreads / 128;          // heads merged side by si
 constexpr int kHeadsPerGroup = 6 / kMergeGroups;      // heads each 128-thread group walks
 static_assert(kThreads % 128 == 0 && 6 % kMergeGroups == 0, "warps per CTA must be 4, 8 or 12");
 constexpr int kSeqsPerThread = (1024 + kThreads - 1) / kThreads;
+constexpr int kInlineContributors = 3;  // items over at most this many CTAs are merged from registers
 constexpr int kPageBytes = kKvBlock * kHeadDim * 2;  // 4096: one (block, kv, head) tile
 constexpr int kStageBytes = 2 * kPageBytes;          // K tile + V tile
 constexpr int kMaxSeqsPerLaunch = 1024;
@@ -140,12 +146,30 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, int parity) {
 }
 // One page of one KV head - its K tile and its V tile, 8 KiB - in a single tensor copy into this CTA's
 // shared memory, 128-byte swizzled; completion is counted in bytes on `bar`. No cluster multicast.
-__device__ __forceinline__ void TmaLoadPage(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar) {
+// KV pages are read once per launch: they are marked evict-first in L2 so that the stream does not
+// push out the small data every launch re-reads (seq_lens, block tables - loaded evict-last below).
+__device__ __forceinline__ void TmaLoadPage(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar,
+                                            uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %2, %2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(0), "r"(tile), "r"(bar)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %2, %2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(map), "r"(0), "r"(tile), "r"(bar), "l"(policy)
       : "memory");
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictFirst() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictLast() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ int LdgKeepInL2(const int32_t* ptr, uint64_t policy) {
+  int v;
+  asm volatile("ld.global.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(ptr), "l"(policy));
+  return v;
 }
 #ifdef RL_ATTN_TIMELINE
 __device__ __forceinline__ unsigned long long GlobalTimerNs() {
@@ -238,7 +262,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   const uint32_t bars = SmemAddr(smem + kBarOff);
   int* prefix = reinterpret_cast<int*>(smem + kPrefixOff);
 
-  __shared__ bool merge_here;
+  __shared__ bool merge_here, others_done;
+  __shared__ float fold_scale[kWarps * 8], fold_max[8], fold_den[8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tig = lane & 3;
   const int heads = p.kv_heads;
@@ -252,6 +277,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
   }
 
+  const uint64_t keep_policy = L2PolicyEvictLast(), stream_policy = L2PolicyEvictFirst();
   // ---- page prefix over sequences (every CTA computes the same table) ----
   {
     __shared__ int warp_tot[kWarps];
@@ -259,7 +285,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
 #pragma unroll
     for (int i = 0; i < kSeqsPerThread; ++i) {
       const int s = tid * kSeqsPerThread + i;
-      int len = s < num_seqs ? p.seq_lens[s] : 0;
+      int len = s < num_seqs ? LdgKeepInL2(p.seq_lens + s, keep_policy) : 0;
       len = min(len, p.max_blocks * kKvBlock);
       n[i] = len > 0 ? (len + kKvBlock - 1) >> kKvBlockShift : 0;
       sum += n[i];
@@ -308,7 +334,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     const int k = 32 * batch + lane;
     if (k >= n_mine) return 0;
     const Cursor c = Locate(share_begin + warp + kWarps * k, prefix, num_seqs, heads);
-    const int block = __ldg(p.tables + static_cast<int64_t>(c.seq) * p.max_blocks + c.page);
+    const int block = LdgKeepInL2(p.tables + static_cast<int64_t>(c.seq) * p.max_blocks + c.page, keep_policy);
     return block * 2 * heads + c.head;
   };
   int tiles_cur = fetch_tiles(0);
@@ -327,7 +353,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       const uint32_t dst = my_ring + stage * kStageBytes;
       const uint32_t bar = my_bars + stage * 8;
       MbarExpectTx(bar, kStageBytes);
-      TmaLoadPage(dst, &tile_map, tile_k, bar);
+      TmaLoadPage(dst, &tile_map, tile_k, bar, stream_policy);
     }
     ++n_issue;
     if ((n_issue & 31) == 0) {
@@ -469,7 +495,26 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     }
 
     RL_STAMP(3);
-    // ---- merge the 8 warps' partial (o, m, l) of this segment ----
+    // ---- the segment is done: fold the warps' (o, m, l); then write the item, or hand it on ----
+    const bool whole = seg_begin == item_begin && seg_end == item_end;
+    const int ctas = gridDim.x;
+    int c_first = blockIdx.x, c_last = blockIdx.x, contributors = 1;
+    bool sparse = false;
+    if (!whole) {  // uniform over the CTA
+      c_first = item_begin < share_begin ? ShareOf(item_begin, total, ctas) : blockIdx.x;
+      c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
+      sparse = total < ctas;  // then every non-empty share is exactly one page
+      contributors = sparse ? sc.pages : c_last - c_first + 1;
+      if (tid == 0) {
+        // Have all the other contributors of this item published already? (Usual for the tail of a
+        // share: the next CTA met the same item at the very start of its own share.) Then this CTA is
+        // the last one, reads their records now - under the fold below - and neither publishes its own
+        // nor takes a ticket.
+        int seen;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.meta + kTicketOff + c_first) : "memory");
+        others_done = !sparse && contributors <= kInlineContributors && seen == contributors - 1;
+      }
+    }
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
       l0 += __shfl_xor_sync(0xffffffffu, l0, off);
@@ -494,42 +539,115 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     __syncthreads();
     RL_STAMP(5);
     {
-      const bool whole = seg_begin == item_begin && seg_end == item_end;
       const int d = tid & 127;
-      // slot 0: the item started in an earlier CTA; slot 1: it starts here and runs on
-      float* rec = p.partials +
-                   (static_cast<size_t>(blockIdx.x) * 2 + (item_begin < share_begin ? 0 : 1)) * kPartialFloats;
+      const int q0 = tid >> 7;  // this thread's heads: q0, q0 + kMergeGroups, ...
+      // Records of the OTHER contributors (at most two when read inline), in CTA order.
+      float om[kInlineContributors - 1][kHeadsPerGroup], ol[kInlineContributors - 1][kHeadsPerGroup],
+          oo[kInlineContributors - 1][kHeadsPerGroup];
+      auto load_others = [&]() {
+        int k = 0;
+        for (int c = c_first; c <= c_last; ++c) {
+          if (c == static_cast<int>(blockIdx.x)) continue;
+          const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
 #pragma unroll
-      for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
-        const int qh = (tid >> 7) + kMergeGroups * qi;
+          for (int j = 0; j < kInlineContributors - 1; ++j) {
+            if (j == k) {
+#pragma unroll
+              for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+                const int qh = q0 + kMergeGroups * qi;
+                om[j][qi] = __ldcg(r + kGroup * kHeadDim + qh);
+                ol[j][qi] = __ldcg(r + kGroup * kHeadDim + 8 + qh);
+                oo[j][qi] = __ldcg(r + qh * kHeadDim + d);
+              }
+            }
+          }
+          ++k;
+        }
+      };
+      const bool fast = !whole && others_done;
+      if (fast) load_others();
+
+      // Scale factors exp2(m_w - max) per (warp, head): six threads, once, instead of every thread.
+      if (tid < kGroup) {
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mbuf[w * 8 + qh]);
-        float acc = 0.0f, den = 0.0f;
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mbuf[w * 8 + tid]);
+        float den = 0.0f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-          const float f = Exp2(mbuf[w * 8 + qh] - mx);  // 0 for a warp that saw no page
-          acc = fmaf(f, obuf[(w * kGroup + qh) * kORowPad + d], acc);
-          den = fmaf(f, lbuf[w * 8 + qh], den);
+          const float f = Exp2(mbuf[w * 8 + tid] - mx);  // 0 for a warp that saw no page
+          fold_scale[w * 8 + tid] = f;
+          den = fmaf(f, lbuf[w * 8 + tid], den);
         }
-        if (whole) {
-          p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
-                (static_cast<int64_t>(sc.head) * kGroup + qh) * kHeadDim + d] = __float2half_rn(acc / den);
-        } else {
-          rec[qh * kHeadDim + d] = acc;
+        fold_max[tid] = mx;
+        fold_den[tid] = den;
+      }
+      __syncthreads();
+      float acc[kHeadsPerGroup], mxo[kHeadsPerGroup], deno[kHeadsPerGroup];
+#pragma unroll
+      for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+        const int qh = q0 + kMergeGroups * qi;
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) a = fmaf(fold_scale[w * 8 + qh], obuf[(w * kGroup + qh) * kORowPad + d], a);
+        acc[qi] = a;
+        mxo[qi] = fold_max[qh];
+        deno[qi] = fold_den[qh];
+      }
+      half* out_row = p.out + static_cast<int64_t>(sc.seq) * p.out_stride +
+                      static_cast<int64_t>(sc.head) * kGroup * kHeadDim + d;
+      // The item from this CTA's fold and the other contributors' records, always combined in CTA
+      // order with the same arithmetic, whichever CTA happens to do it.
+      auto combine_inline = [&]() {
+#pragma unroll
+        for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+          float mx = mxo[qi];
+#pragma unroll
+          for (int j = 0; j < kInlineContributors - 1; ++j)
+            if (j < contributors - 1) mx = fmaxf(mx, om[j][qi]);
+          float a = 0.0f, dn = 0.0f;
+          int k = 0;
+          for (int c = c_first; c <= c_last; ++c) {
+            if (c == static_cast<int>(blockIdx.x)) {
+              const float f = Exp2(mxo[qi] - mx);
+              a = fmaf(f, acc[qi], a);
+              dn = fmaf(f, deno[qi], dn);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kInlineContributors - 1; ++j) {
+                if (j == k) {
+                  const float f = Exp2(om[j][qi] - mx);
+                  a = fmaf(f, oo[j][qi], a);
+                  dn = fmaf(f, ol[j][qi], dn);
+                }
+              }
+              ++k;
+            }
+          }
+          out_row[(q0 + kMergeGroups * qi) * kHeadDim] = __float2half_rn(a / dn);
+        }
+      };
+      if (whole) {
+#pragma unroll
+        for (int qi = 0; qi < kHeadsPerGroup; ++qi)
+          out_row[(q0 + kMergeGroups * qi) * kHeadDim] = __float2half_rn(acc[qi] / deno[qi]);
+      } else if (fast) {
+        combine_inline();
+        if (tid == 0) p.meta[kTicketOff + c_first] = 0;  // everyone had arrived: re-arm for the next launch
+      } else {
+        // Publish this CTA's record, take a ticket; the last contributor of the item merges.
+        // slot 0: the item started in an earlier CTA; slot 1: it starts here and runs on
+        float* rec = p.partials +
+                     (static_cast<size_t>(blockIdx.x) * 2 + (item_begin < share_begin ? 0 : 1)) * kPartialFloats;
+#pragma unroll
+        for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+          const int qh = q0 + kMergeGroups * qi;
+          rec[qh * kHeadDim + d] = acc[qi];
           if (d == 0) {
-            rec[kGroup * kHeadDim + qh] = mx;
-            rec[kGroup * kHeadDim + 8 + qh] = den;
+            rec[kGroup * kHeadDim + qh] = mxo[qi];
+            rec[kGroup * kHeadDim + 8 + qh] = deno[qi];
           }
         }
-      }
-      if (!whole) {  // uniform over the CTA
-        // Publish the record, take a ticket; the last contributor of the item merges.
-        const int ctas = gridDim.x;
-        const int c_first = item_begin < share_begin ? ShareOf(item_begin, total, ctas) : blockIdx.x;
-        const int c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
-        const bool sparse = total < ctas;  // then every non-empty share is exactly one page
-        const int contributors = sparse ? sc.pages : c_last - c_first + 1;
         RL_STAMP(6);
         __syncthreads();  // the whole record is written (CTA scope) ...
         if (tid == 0) {
@@ -542,40 +660,41 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
         RL_STAMP(7);
         if (merge_here) {
           __threadfence();
-          // Two passes over the contributors' records (L2 reads, independent per contributor):
-          // running max per head, then the rescaled sums, always in CTA order.
-          const int q0 = tid >> 7;  // this thread's heads: q0, q0 + kMergeGroups, ...
-          float mx[kHeadsPerGroup];
+          if (!sparse && contributors <= kInlineContributors) {
+            load_others();
+            combine_inline();
+          } else {
+            // Many contributors (a long sequence over many CTAs): two passes over the records (L2 reads,
+            // independent per contributor) - running max per head, then the rescaled sums, in CTA order.
+            float mx[kHeadsPerGroup];
 #pragma unroll
-          for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = -INFINITY;
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = -INFINITY;
 #pragma unroll 4
-          for (int c = c_first; c <= c_last; ++c) {
-            if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-            const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats +
-                             kGroup * kHeadDim + q0;
+            for (int c = c_first; c <= c_last; ++c) {
+              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats +
+                               kGroup * kHeadDim + q0;
 #pragma unroll
-            for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + kMergeGroups * qi));
-          }
-          float acc[kHeadsPerGroup], den[kHeadsPerGroup];
-#pragma unroll
-          for (int qi = 0; qi < kHeadsPerGroup; ++qi) acc[qi] = den[qi] = 0.0f;
-#pragma unroll 2
-          for (int c = c_first; c <= c_last; ++c) {
-            if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-            const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
-#pragma unroll
-            for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
-              const int qh = q0 + kMergeGroups * qi;
-              const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx[qi]);
-              acc[qi] = fmaf(f, __ldcg(r + qh * kHeadDim + d), acc[qi]);
-              den[qi] = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), den[qi]);
+              for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + kMergeGroups * qi));
             }
-          }
+            float a[kHeadsPerGroup], dn[kHeadsPerGroup];
 #pragma unroll
-          for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
-            p.out[static_cast<int64_t>(sc.seq) * p.out_stride +
-                  (static_cast<int64_t>(sc.head) * kGroup + q0 + kMergeGroups * qi) * kHeadDim + d] =
-                __float2half_rn(acc[qi] / den[qi]);
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi) a[qi] = dn[qi] = 0.0f;
+#pragma unroll 2
+            for (int c = c_first; c <= c_last; ++c) {
+              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
+              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+#pragma unroll
+              for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+                const int qh = q0 + kMergeGroups * qi;
+                const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx[qi]);
+                a[qi] = fmaf(f, __ldcg(r + qh * kHeadDim + d), a[qi]);
+                dn[qi] = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), dn[qi]);
+              }
+            }
+#pragma unroll
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi)
+              out_row[(q0 + kMergeGroups * qi) * kHeadDim] = __float2half_rn(a[qi] / dn[qi]);
           }
         }
       }

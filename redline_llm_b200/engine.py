@@ -246,9 +246,9 @@ class ModelExecutor:
         f16, i32 = torch.float16, torch.int32
         self.pool = torch.zeros(cfg.layers, num_blocks, 2, cfg.kv_heads, KV_BLOCK, cfg.head_dim, dtype=f16, device=device)
         B = BUCKETS[-1]
-        self.ids = torch.zeros(B, dtype=i32, device=device)
-        self.positions = torch.zeros(B, dtype=i32, device=device)
-        self.seq_lens = torch.zeros(B, dtype=i32, device=device)
+        # token ids | positions | seq_lens in one buffer: one H2D copy per step instead of three
+        self.step_inputs = torch.zeros(3, B, dtype=i32, device=device)
+        self.ids, self.positions, self.seq_lens = self.step_inputs[0], self.step_inputs[1], self.step_inputs[2]
         self.tables = torch.zeros(B, self.mbps, dtype=i32, device=device)
         self.x = torch.zeros(B, cfg.hidden, dtype=f16, device=device)          # residual stream
         self.normed = torch.zeros(B, cfg.hidden, dtype=f16, device=device)
@@ -259,9 +259,8 @@ class ModelExecutor:
         self.logits = torch.zeros(B, cfg.vocab, dtype=f16, device=device)
         self.tokens = torch.zeros(B, dtype=i32, device=device)
         # pinned mirrors (one H2D each per step, one D2H)
-        self.h_ids = torch.zeros(B, dtype=i32).pin_memory()
-        self.h_pos = torch.zeros(B, dtype=i32).pin_memory()
-        self.h_lens = torch.zeros(B, dtype=i32).pin_memory()
+        self.h_step_inputs = torch.zeros(3, B, dtype=i32).pin_memory()
+        self.h_ids, self.h_pos, self.h_lens = self.h_step_inputs[0], self.h_step_inputs[1], self.h_step_inputs[2]
         self.h_tables = torch.zeros(B, self.mbps, dtype=i32).pin_memory()
         self.h_tokens = torch.zeros(B, dtype=i32).pin_memory()
         self._np_ids, self._np_pos = self.h_ids.numpy(), self.h_pos.numpy()
@@ -389,15 +388,13 @@ class ModelExecutor:
                 self.dirty_rows.append(i)
 
     def upload(self, rows: int) -> None:
-        self.ids[:rows].copy_(self.h_ids[:rows], non_blocking=True)
-        self.positions[:rows].copy_(self.h_pos[:rows], non_blocking=True)
-        self.seq_lens[:rows].copy_(self.h_lens[:rows], non_blocking=True)
+        self.step_inputs.copy_(self.h_step_inputs, non_blocking=True)
         if len(self.dirty_rows) > rows // 2:
             self.tables[:rows].copy_(self.h_tables[:rows], non_blocking=True)
         else:
             for i in self.dirty_rows:
                 self.tables[i].copy_(self.h_tables[i], non_blocking=True)
-        self.h2d_bytes = 12 * rows + 4 * self.mbps * (rows if len(self.dirty_rows) > rows // 2 else len(self.dirty_rows))
+        self.h2d_bytes = self.h_step_inputs.numel() * 4 + 4 * self.mbps * (rows if len(self.dirty_rows) > rows // 2 else len(self.dirty_rows))
 
     def run(self, rows: int) -> None:
         g = self.graphs.get(rows)
