@@ -34,8 +34,8 @@ from redline_llm_b200 import workloads as wl  # noqa: E402
 LAYERS = 28
 METRIC = "decode-kernel HBM GB/s"
 # dram__bytes_read+write / algorithmic bytes of the attention kernel in the ncu capture at batch 64,
-# contexts 4096-8192 (402.6 MB / 397.3 MB); the config-3 capture gives 78.5 / 75.7 = 1.037
-ATTENTION_TRAFFIC_RATIO = 1.0134
+# contexts 4096-8192 (400.5 MB / 397.3 MB); the config-3 capture gives 78.4 / 75.7 = 1.036
+ATTENTION_TRAFFIC_RATIO = 1.008
 
 
 def measured_peaks():
@@ -492,7 +492,7 @@ def run_attention(args, rank, local_rank, world, barrier, dist):
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel",
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "peak_kind": f"of {peak_kind}",
-                     "traffic": int(w.bytes_per_launch * (1.037 if args.ctx_hi <= 2048 else ATTENTION_TRAFFIC_RATIO)),
+                     "traffic": int(w.bytes_per_launch * (1.036 if args.ctx_hi <= 2048 else ATTENTION_TRAFFIC_RATIO)),
                      "traffic_note": "dram read+write per launch from the ncu capture of this kernel "
                                      "(profiles/paged_attention_split_kernel.txt), scaled by units processed",
                      "algorithmic_bytes_per_launch": w.bytes_per_launch, "us_per_launch": round(per_launch_s * 1e6, 3)},
@@ -549,7 +549,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                      "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                      "traffic": int(att_bytes * ATTENTION_TRAFFIC_RATIO),
                      "traffic_note": "dram read+write per launch scaled by units from the ncu capture at batch 64, "
-                                     "contexts 4096-8192 (profiles/paged_attention_split_kernel.txt): 1.013 x algorithmic",
+                                     "contexts 4096-8192 (profiles/paged_attention_split_kernel.txt): 1.008 x algorithmic",
                      "algorithmic_bytes_per_launch": int(att_bytes),
                      "us_per_launch": round(att_s * 1e6, 2),
                      "timed": "CUDA events over graph replays of the step's 28 attention launches per wave "
