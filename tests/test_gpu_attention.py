@@ -214,3 +214,50 @@ def test_prologue_overlap_changes_no_bit(own):
         K.set_attention_prologue_overlap(False)
     live = lens > 0
     assert np.array_equal(outs[False][live], outs[True][live])
+
+
+@pytest.mark.parametrize("kv_heads", [1, 3, 4, 8])
+def test_other_kv_head_counts(own, kv_heads):
+    """The tile stride of the tensor copy follows num_kv_heads (1..8); 6 query heads per KV head throughout."""
+    c = case([300, 17, 0, 1025, 64], seed=0x4E0 + kv_heads, q_heads=6 * kv_heads, kv_heads=kv_heads)
+    s = len(c["seq_lens"])
+    width = 6 * kv_heads * 128
+    d_out = torch.zeros(s, width, dtype=torch.int16, device="cuda")
+    K.launch_paged_attention_decode(d_out, width, dev(c["q"]), width, dev(c["pool"]), dev(c["tables"]),
+                                    dev(c["seq_lens"]), s, c["tables"].shape[1], 6 * kv_heads, kv_heads, 128, c["scale"])
+    expect(own, c, host(d_out), f"{kv_heads} kv heads")
+
+
+def test_seq_len_beyond_the_table_is_clamped_to_it(own):
+    """seq_len larger than max_blocks_per_seq * 16 is clamped, as the reference kernel does
+    (src/kernels/paged_attention.cu:153): no table entry past the row is ever read."""
+    c = case([160, 48], seed=0xC1A, fill="normal")
+    lens = np.array([100000, 48], np.int32)  # row 0 claims far more than its 10-entry table row holds
+    d_out = torch.zeros(2, 1536, dtype=torch.int16, device="cuda")
+    K.launch_paged_attention_decode(d_out, 1536, dev(c["q"]), 1536, dev(c["pool"]), dev(c["tables"]), dev(lens), 2,
+                                    c["tables"].shape[1], 12, 2, 128, c["scale"])
+    expect(own, c, host(d_out), "clamped row")
+
+
+def test_second_device_keeps_its_own_state(own):
+    """Per-device workspace and attributes: the same case on device 1 after device 0 (needs two GPUs)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU")
+    c = case([700, 33, 1300], seed=0xD2, fill="normal")
+    outs = []
+    for d in (0, 1, 0):
+        with torch.cuda.device(d):
+            K.init(d)
+            to = lambda a: dev(a).to(f"cuda:{d}")
+            d_out = torch.zeros(3, 1536, dtype=torch.int16, device=f"cuda:{d}")
+            K.launch_paged_attention_decode(d_out, 1536, to(c["q"]), 1536, to(c["pool"]), to(c["tables"]),
+                                            to(c["seq_lens"]), 3, c["tables"].shape[1], 12, 2, 128, c["scale"])
+            qkv = to(wl.normal_half(0xD3, 3 * 2048).reshape(3, 2048))
+            K.launch_rope_inplace(qkv, qkv, 2048, 2048, to(np.array([5, 700, 4000], np.int32)), 3, 12, 2, 128, 1e6,
+                                  k_offset=1536)
+            torch.cuda.synchronize(d)
+            outs.append((host(d_out), host(qkv)))
+            assert K.attention_health() == 0
+    expect(own, c, outs[1][0], "device 1")
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][0], outs[2][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
