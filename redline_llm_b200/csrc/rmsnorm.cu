@@ -67,6 +67,11 @@ __device__ __forceinline__ uint4 NormChunk(const uint4& h, const uint4& w, float
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Output and the rewritten residual are not read again by this kernel: stream them past L1.
+__device__ __forceinline__ void StgStream16(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 template <int CPL, bool kResidual>
 __global__ void __launch_bounds__(256)
 RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const half* __restrict__ input,
@@ -88,7 +93,7 @@ RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const hal
       uint4 x = LdgStream16(input + base + c * 8);
       if (kResidual) {
         x = AddChunk(Ldg16(residual + base + c * 8), x);
-        Stg16(residual + base + c * 8, x);
+        StgStream16(residual + base + c * 8, x);
       }
       hv[i] = x;
       part[i] = ChunkSumSq(x);
@@ -101,7 +106,7 @@ RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const hal
 #pragma unroll
   for (int i = 0; i < CPL; ++i) {
     const int c = i * 32 + lane;
-    if (c < chunks) Stg16(out + base + c * 8, NormChunk(hv[i], Ldg16(weight + c * 8), inv));
+    if (c < chunks) StgStream16(out + base + c * 8, NormChunk(hv[i], Ldg16(weight + c * 8), inv));
   }
 }
 
