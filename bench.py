@@ -230,6 +230,10 @@ class DecodeStepWorkload:
             self.engines.append(e)
             self.lens.append(wave)
         self.tokens_per_step = len(mine)
+        wts = self.weights
+        self.weight_bytes = sum(t.numel() * 2 for L in wts.layers for t in L.values()) + wts.final_norm.numel() * 2 \
+            + wts.lm_head.numel() * 2  # streamed once per wave per step (the embedding rows gathered are negligible)
+        self.kv_bytes_per_token = self.cfg.layers * 2 * self.cfg.kv_heads * self.cfg.head_dim * 2
         self.launches_per_step = len(self.engines) * (self.cfg.layers * 6 + 3)  # 6 own kernels per layer + embed, final norm, argmax
         self.h2d = self.d2h = 0
 
@@ -533,6 +537,11 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     if rank != 0:
         return
     tokens = w.TOTAL
+    # HBM bytes one step must move on this rank: the weights once per wave, every cached token's K/V once
+    # (at the contexts the timed replays saw), the new tokens' K/V written
+    ctx_now = sum(int(e.exec.seq_lens[:DecodeStepWorkload.WAVE].sum().item()) for e in w.engines)
+    step_bytes = len(w.engines) * w.weight_bytes + (ctx_now + w.tokens_per_step) * w.kv_bytes_per_token
+    step_gbs = step_bytes / (ms * 1e-3 / args.steps) / 1e9
     value = tokens * args.steps / (ms * 1e-3)
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
     achieved = att_bytes / att_s / 1e9
@@ -544,7 +553,10 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                    "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
                    "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap, "gemm": "library (cuBLAS via torch.matmul), FP16",
                    "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
-                   "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2)},
+                   "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2),
+                   "step_hbm_bytes_per_gpu": int(step_bytes), "step_GBps_per_gpu": round(step_gbs, 1),
+                   "step_frac_of_measured_hbm": round(step_gbs / peak, 4),
+                   "step_pct_of_8TBps": round(100 * step_gbs / 8000.0, 2)},
         "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
                      "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                      "traffic": int(att_bytes * ATTENTION_TRAFFIC_RATIO),
