@@ -205,9 +205,11 @@ class DecodeStepWorkload:
     name = "decode_step_qwen2.5-1.5b_512seq_ctx1024-8192+32x32768"
     TOTAL, LONG, WAVE, NEW = 512, 32, 64, 256
 
-    def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512, overlap: bool = True):
+    def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512, overlap: bool = True,
+                 linear: str = "tcgen05"):
         import torch
         self.TOTAL, self.LONG = total, total // 16
+        self.linear = linear
         from redline_llm_b200.engine import Engine, ModelConfig, ModelWeights, blocks_for_tokens, shard_requests
         self.torch = torch
         ctx = np.concatenate([wl.randint(wl.SEED_STEP, self.TOTAL - self.LONG, 1024, 8192),
@@ -224,7 +226,7 @@ class DecodeStepWorkload:
             blocks = sum(blocks_for_tokens(c + new_tokens) for c in wave) + 8
             gb = blocks * self.cfg.block_bytes() / (1 << 30)
             e = Engine(kv_pool_gb=gb, max_batch=self.WAVE, max_seq_len=max_seq, config=self.cfg, weights=self.weights,
-                       device=dev.index, graph_buckets=[64], prologue_overlap=overlap)
+                       device=dev.index, graph_buckets=[64], prologue_overlap=overlap, decode_linear=linear)
             for j, c in enumerate(wave):
                 e.add_synthetic_request(c, new_tokens, seed=wl.SEED_STEP + 1000 * rank + w0 + j)
             self.engines.append(e)
@@ -234,7 +236,9 @@ class DecodeStepWorkload:
         self.weight_bytes = sum(t.numel() * 2 for L in wts.layers for t in L.values()) + wts.final_norm.numel() * 2 \
             + wts.lm_head.numel() * 2  # streamed once per wave per step (the embedding rows gathered are negligible)
         self.kv_bytes_per_token = self.cfg.layers * 2 * self.cfg.kv_heads * self.cfg.head_dim * 2
-        self.launches_per_step = len(self.engines) * (self.cfg.layers * 6 + 3)  # 6 own kernels per layer + embed, final norm, argmax
+        # own kernels per layer: 2 norms, RoPE+scatter, attention, and either SiLU (library GEMMs) or the
+        # four linear layers (SiLU fused into the gate/up product); + embed, final norm, argmax
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * (8 if linear == "tcgen05" else 5) + 3)
         self.h2d = self.d2h = 0
 
     def step(self):  # inputs already resident: graph replays only
@@ -519,7 +523,8 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     import torch
     from redline_llm_b200 import kernels as K
     need = args.warmup + args.steps + 8
-    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences, overlap=not args.no_overlap)
+    w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences, overlap=not args.no_overlap,
+                           linear=args.linear)
     peak, peak_kind = measured_peaks()
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
@@ -551,7 +556,10 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
         "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
                    "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
-                   "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap, "gemm": "library (cuBLAS via torch.matmul), FP16",
+                   "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
+                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (SiLU fused), "
+                            "library GEMM for the vocabulary projection, FP16" if args.linear == "tcgen05"
+                            else "library (cuBLAS via torch.matmul), FP16"),
                    "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
                    "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2),
                    "step_hbm_bytes_per_gpu": int(step_bytes), "step_GBps_per_gpu": round(step_gbs, 1),
@@ -608,6 +616,8 @@ def main():
     ap.add_argument("--ctx-hi", type=int, default=1280, help="attention workload: longest context")
     ap.add_argument("--sequences", type=int, default=512,
                     help="decode_step workload: sequences in the job (512 = the configuration; fewer for profiling)")
+    ap.add_argument("--linear", choices=["tcgen05", "library"], default="tcgen05",
+                    help="decode_step: linear layers by this library's tcgen05 kernel (default) or by the library GEMM")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain attention launches (no programmatic dependent launch of the prologue)")
     ap.add_argument("--kernel", default=None, help="kernels workload: only entries whose name contains this")

@@ -204,6 +204,43 @@ int rl_launch_kv_gather(void* khat, void* vhat, int64_t khat_head_stride, int64_
 int rl_launch_prefill_softmax(void* probs, const float* scores, int32_t num_q_heads, int32_t chunk_len,
                               int32_t kv_len, int32_t chunk_start, void* stream);
 
+/*
+ * Linear layer of the decode step for at most 64 token rows:
+ *   out[t, n] = fp16( sum_k x[t, k] * weight[n, k]  (+ bias[n]) ),  FP16 in, FP32 accumulate, one rounding.
+ * Replaces the cuBLASLt call behind CublasLtGemm::Run for the decode shapes
+ * (src/gemm/cublaslt_gemm.cpp:569-598; call sites src/core/model_executor.cpp:916-951): with so few
+ * rows the product is a stream over the weights, and this kernel (TMA + tcgen05, split along K where
+ * the shape has few row tiles) is built to run it at HBM speed. Row strides are in elements; x and
+ * weight rows must be 16-byte aligned and in_features a multiple of 8. More than 64 token rows
+ * returns RL_E_TOO_LARGE: prefill-sized products stay with the library.
+ *   epilogue 0: bias (may be NULL) added in FP32 before the rounding; out is [num_tokens, out_features].
+ *   epilogue 1: the gated-MLP input. weight has 2*out_features rows, `gate` rows first, then `up` rows;
+ *               out[t, c] = fp16( silu(fp16(gate_acc)) * fp16(up_acc) ), i.e. exactly rl_launch_silu_mul
+ *               applied to the rounded GEMM output, without storing the [num_tokens, 2*out_features]
+ *               intermediate. bias must be NULL.
+ * Results do not depend on arrival order or on the ring depth (fixed summation order).
+ * First call per device must happen outside stream capture (it opts in to large shared memory and
+ * allocates a 256-byte error flag).
+ */
+int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, int64_t x_row_stride,
+                            const void* weight, int64_t weight_row_stride, const void* bias,
+                            int32_t num_tokens, int32_t out_features, int32_t in_features,
+                            int32_t epilogue, void* stream);
+
+/* Synchronises the device and reports (then clears) the error flag of rl_launch_decode_linear:
+ * 0 = every bounded wait inside the kernel completed; 1..3 name the wait that gave up. */
+int rl_decode_linear_health(int* flag_out);
+
+/* Tuning: depth of the kernel's shared-memory ring, 2..8 stages of 24 KB (default 4, which lets the
+ * CTAs of two consecutive launches share an SM). Process-wide; affects later launches. */
+int rl_decode_linear_set_stages(int stages);
+
+/* Tuning: the largest number of CTAs a row tile may be split into along K (1, 2, 4 or 8; default 8).
+ * The split count is a function of the shape and of this cap only, and the partial sums are added in a
+ * fixed order, so a given (shape, cap) always gives the same bits; different caps may differ in the
+ * last FP32 bit of the accumulated sum. Process-wide; affects later launches. */
+int rl_decode_linear_set_max_splits(int max_splits);
+
 #ifdef __cplusplus
 }
 #endif

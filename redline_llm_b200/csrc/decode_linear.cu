@@ -1,0 +1,688 @@
+// Decode-sized linear layer for sm_100a (B200): out[T, N] = x[T, K] . W[N, K]^T (+ bias), T <= 64.
+//
+// In the reference every linear layer of the decode step is a cuBLASLt call whose algorithm is the
+// first heuristic result (src/gemm/cublaslt_gemm.cpp:569-598, called from
+// src/core/model_executor.cpp:916-951). With at most 64 token rows these products are weight
+// streams: every weight is read once and used 64 times, so the bound is HBM, and the library
+// kernels reach 15-70 % of it at the reference model's shapes. This kernel is built for exactly that case.
+//
+//  * The weight matrix is the M operand. A CTA owns 128 weight rows and a contiguous range of
+//    64-wide k-blocks; tcgen05.mma (M=128, N=tokens padded to 16, K=16, FP16 in, FP32 accumulate)
+//    reads both operands from shared memory and keeps the 128 x T accumulator in tensor memory.
+//    One thread issues the MMAs; one thread issues the TMA loads; a ring of (128 x 64 weights,
+//    T x 64 activations) tiles, 128-byte swizzled, keeps 16 KB of weights per stage in flight.
+//    Every CTA loads its own tiles; no peer GPU memory is ever touched.
+//  * Weights do not depend on the previous kernel of the stream: under programmatic dependent
+//    launch the first stages of weights are requested BEFORE griddepcontrol.wait, the activations
+//    after it, so the stream of weights starts while the previous kernel drains.
+//  * Shapes with few row tiles are split along K so that tiles x splits fills the GPU. The S splits
+//    of a tile (2, 4 or 8) form one thread-block cluster. Token t of the tile is finished by CTA
+//    t mod S: every CTA stores the FP32 partial sums of that token straight into the owner's shared
+//    memory (distributed shared memory; remote stores do not stall the sender), the cluster meets
+//    once at the hardware cluster barrier, and each owner adds the S slices it received in split
+//    order 0..S-1 from its own shared memory. No global workspace, no atomics, no spinning; results
+//    do not depend on arrival order.
+//  * Epilogue 0 adds the bias in FP32 and rounds once to FP16. Epilogue 1 is the gated MLP input:
+//    W holds `gate` rows then `up` rows; a CTA takes 64 of each, rounds both accumulators to FP16
+//    (what a separate GEMM would have stored) and writes fp16(silu(gate) * up) - bit-identical to
+//    running the SiLU kernel on the GEMM's output (src/kernels/silu_mul.cu:67-83), without the
+//    [T, 2I] round trip.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "silu_math.cuh"
+
+namespace rl {
+namespace lin {
+
+constexpr int kTileRows = 128;   // weight rows per CTA = MMA M
+constexpr int kHalfRows = 64;    // rows per weight TMA box (two boxes per stage)
+constexpr int kBlockK = 64;      // halves per k-block: one 128-byte swizzle row
+constexpr int kMaxTokens = 64;   // MMA N
+constexpr int kThreads = 256;    // two warps per tensor-memory lane quadrant in the epilogue
+constexpr int kMaxStages = 8;
+constexpr int kMaxSplits = 8;    // portable cluster size
+constexpr int kWTileBytes = kTileRows * 128;    // 16384
+constexpr int kXTileBytes = kMaxTokens * 128;   // 8192 (T x 128 B used)
+constexpr int kStageBytes = kWTileBytes + kXTileBytes;
+// Shared memory, from a 1024-byte aligned base: barriers and small slots, the receive area of a
+// split launch, then the ring. Without splits the idle ring stages the FP16 tile for the output pass.
+constexpr int kBarOff = 0;     // full[kMaxStages], empty[kMaxStages], accum, tmem slot
+constexpr int kRecvOff = 1024;                      // split K only: partial sums received from the cluster
+constexpr int kRecvBytes = kMaxTokens * kTileRows * 4;   // S slices x (64 / S) tokens x 128 rows, FP32
+__host__ __device__ constexpr int RingOff(int splits) { return splits > 1 ? kRecvOff + kRecvBytes : 1024; }
+__host__ __device__ constexpr int SmemBytes(int stages, int splits) { return RingOff(splits) + stages * kStageBytes + 1024; }  // + slack to align the base
+static_assert(SmemBytes(kMaxStages, 1) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
+static_assert(SmemBytes(kMaxStages - 1, 8) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
+static_assert(2 * kStageBytes >= kMaxTokens * kTileRows * 2, "the FP16 output tile is staged in the idle ring");
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: a wait that never completes sets the error flag
+
+enum Epilogue { kEpilogueBias = 0, kEpilogueSiluMul = 1 };
+enum ErrorCode { kErrProducerWait = 1, kErrMmaWait = 2, kErrAccumWait = 3 };
+
+struct Params {
+  half* out;
+  int64_t out_stride;
+  const half* bias;      // may be null
+  int tokens;            // T
+  int tokens_padded;     // MMA N: T rounded up to 16
+  int out_cols;          // columns of `out`
+  int up_row_offset;     // epilogue 1: first `up` row of W; unused otherwise
+  int k_blocks;          // ceil(K / 64)
+  int splits;            // CTAs per row tile along K = cluster size: 1, 2, 4 or 8
+  int split_shift;       // log2(splits)
+  int stages;            // ring depth
+  int epilogue;
+  int tmem_cols;         // 32 or 64
+  int out_vec;           // out rows are 16-byte aligned: vector stores allowed
+  int* error_flag;
+  unsigned long long* timeline;  // diagnostics build only
+};
+
+// ------------------------------------------------------------------ PTX
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void MbarInit(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, int parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the phase never completed within kWaitCycles.
+__device__ __forceinline__ bool MbarWait(uint32_t bar, int parity) {
+  if (MbarTryWait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!MbarTryWait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictFirst() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t L2PolicyEvictLast() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+// One box of a 2-D tensor map (x = k element, y = row) into this CTA's shared memory, completion
+// counted in bytes on `bar`. x is always a multiple of 64 halves, so the copy starts 128-byte aligned.
+__device__ __forceinline__ void TmaLoad2D(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                          uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 halves), written
+// by TMA with the 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte offset), leading
+// byte offset unused for swizzled K-major tiles (encoded 1), descriptor version 1, layout type 2
+// (128-byte swizzle). Fields are in 16-byte units. The tile base is 1024-byte aligned; advancing
+// the start address by 32 bytes steps one K=16 slice inside the swizzle row.
+__device__ __forceinline__ uint64_t TileDesc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Instruction descriptor: FP32 accumulate (bits 4-5 = 1), A and B FP16 (0), both K-major (0),
+// N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t InstrDesc(int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
+}
+__device__ __forceinline__ void Umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void UmmaCommit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// 16 consecutive accumulator columns of this thread's tensor-memory lane. The load is asynchronous:
+// the values may be used only after TmemWaitLoads, which takes the registers as read-write operands
+// so that no use can be scheduled ahead of it.
+__device__ __forceinline__ void TmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void TmemWaitLoads(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Thread-block cluster: barrier over all threads of all CTAs (split into arrive and wait), the
+// address of a peer CTA's shared memory, and a store to it.
+__device__ __forceinline__ void ClusterArriveRelaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void ClusterArriveRelease() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void ClusterWait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t PeerSmemAddr(uint32_t local_addr, int cta_rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(cta_rank));
+  return a;
+}
+__device__ __forceinline__ void StPeerF32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+#ifdef RL_LIN_TIMELINE
+__device__ __forceinline__ unsigned long long GlobalTimerNs() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define RL_LSTAMP(slot) \
+  if (p.timeline) p.timeline[blockIdx.x * 16 + (slot)] = GlobalTimerNs()
+#else
+#define RL_LSTAMP(slot)
+#endif
+
+// ------------------------------------------------------------------ kernel
+
+__global__ void __launch_bounds__(kThreads)
+DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
+                   const __grid_constant__ CUtensorMap x_map) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int ring_off = RingOff(p.splits);
+  const uint32_t ring = SmemAddr(smem + ring_off);
+  const uint32_t bars = SmemAddr(smem + kBarOff);
+  // Split launches: tell the cluster this CTA is running (its shared memory may be written from now
+  // on); the matching wait comes just before the first remote store.
+  if (p.splits > 1) ClusterArriveRelaxed();
+  const uint32_t full0 = bars, empty0 = bars + kMaxStages * 8, accum_bar = bars + 2 * kMaxStages * 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + (2 * kMaxStages + 1) * 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;  // split = rank in the cluster
+  const int kb0 = static_cast<int>(static_cast<long long>(split) * p.k_blocks / p.splits);
+  const int kb1 = static_cast<int>(static_cast<long long>(split + 1) * p.k_blocks / p.splits);
+  const int nkb = kb1 - kb0;
+  const int T = p.tokens, TP = p.tokens_padded, stages = p.stages;
+  const int first_row0 = (p.epilogue == kEpilogueSiluMul) ? tile * kHalfRows : tile * kTileRows;
+  const int second_row0 = (p.epilogue == kEpilogueSiluMul) ? p.up_row_offset + tile * kHalfRows
+                                                            : tile * kTileRows + kHalfRows;
+  const int stage_tx = kWTileBytes + TP * 128;
+  const int pre = nkb < stages ? nkb : stages;
+
+  if (tid == 0) {
+    RL_LSTAMP(0);
+    for (int s = 0; s < stages; ++s) {
+      MbarInit(full0 + s * 8, 1);
+      MbarInit(empty0 + s * 8, 1);
+    }
+    MbarInit(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // The first ring of weight tiles is requested at once: weights never depend on the previous
+    // kernel of the stream, so this runs ahead of the dependency gate and of the TMEM set-up.
+    const uint64_t stream_policy = L2PolicyEvictFirst();
+    for (int i = 0; i < pre; ++i) {
+      const uint32_t dst = ring + i * kStageBytes, bar = full0 + i * 8;
+      MbarExpectTx(bar, stage_tx);
+      TmaLoad2D(dst, &w_map, (kb0 + i) * kBlockK, first_row0, bar, stream_policy);
+      TmaLoad2D(dst + kHalfRows * 128, &w_map, (kb0 + i) * kBlockK, second_row0, bar, stream_policy);
+    }
+    RL_LSTAMP(2);
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     SmemAddr(const_cast<uint32_t*>(tmem_slot))),
+                 "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0) { RL_LSTAMP(1); }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: activations once the previous kernel has completed, then the steady state
+      const uint64_t stream_policy = L2PolicyEvictFirst(), keep_policy = L2PolicyEvictLast();
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      RL_LSTAMP(9);
+      for (int i = 0; i < pre; ++i)
+        TmaLoad2D(ring + i * kStageBytes + kWTileBytes, &x_map, (kb0 + i) * kBlockK, 0, full0 + i * 8, keep_policy);
+      int s = 0, parity = 0;  // stage and the phase of empty[s] that frees it
+      for (int i = pre; i < nkb; ++i) {
+        if (!MbarWait(empty0 + s * 8, parity)) {
+          atomicExch(p.error_flag, kErrProducerWait);
+          break;
+        }
+        const uint32_t dst = ring + s * kStageBytes, bar = full0 + s * 8;
+        MbarExpectTx(bar, stage_tx);
+        TmaLoad2D(dst, &w_map, (kb0 + i) * kBlockK, first_row0, bar, stream_policy);
+        TmaLoad2D(dst + kHalfRows * 128, &w_map, (kb0 + i) * kBlockK, second_row0, bar, stream_policy);
+        TmaLoad2D(dst + kWTileBytes, &x_map, (kb0 + i) * kBlockK, 0, bar, keep_policy);
+        if (++s == stages) {
+          s = 0;
+          parity ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issue: four K=16 slices per k-block, accumulator stays in tensor memory
+      const uint32_t idesc = InstrDesc(TP);
+      bool ok = true;
+      int s = 0, parity = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (!MbarWait(full0 + s * 8, parity)) {
+          atomicExch(p.error_flag, kErrMmaWait);
+          ok = false;
+          break;
+        }
+        TcFenceAfter();
+        if (i == 0) { RL_LSTAMP(3); }
+        const uint64_t a_desc = TileDesc(ring + s * kStageBytes);
+        const uint64_t b_desc = TileDesc(ring + s * kStageBytes + kWTileBytes);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k)
+          Umma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        UmmaCommit(empty0 + s * 8);
+        if (++s == stages) {
+          s = 0;
+          parity ^= 1;
+        }
+      }
+      RL_LSTAMP(4);
+      if (ok) UmmaCommit(accum_bar);
+    }
+    __syncwarp();
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- accumulator to registers. Warp w reads tensor-memory lanes 32*(w%4)..+31 (accumulator rows);
+  // warps 0-3 take the even 16-token column chunks, warps 4-7 the odd ones.
+  const int row = (warp & 3) * 32 + lane;
+  const int chunk0 = warp >> 2;
+  bool good = MbarWait(accum_bar, 0);
+  good = __all_sync(0xffffffffu, good);
+  if (tid == 0) { RL_LSTAMP(5); }
+  if (!good && lane == 0) atomicExch(p.error_flag, kErrAccumWait);
+  TcFenceAfter();
+  uint32_t raw[2][16];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[j][i] = 0u;
+  if (good) {
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if ((chunk0 + 2 * j) * 16 < TP) TmemLoad16(taddr + (chunk0 + 2 * j) * 16, raw[j]);
+    TmemWaitLoads(raw[0]);
+    TmemWaitLoads(raw[1]);
+  }
+  float v[2][16];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[j][i] = __uint_as_float(raw[j][i]);
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                 : "memory");
+  }
+  if (tid == 0) { RL_LSTAMP(6); }
+  // From here on every thread of every CTA runs the same barriers whatever `good` says: a CTA whose
+  // wait gave up has raised the error flag and contributes zeros.
+  // Every MMA has completed, so the ring is idle: it stages the tile, token-major, for the
+  // cooperative output pass of an unsplit launch ([token][128 rows], FP16).
+
+  if (p.splits == 1) {
+    half* stage = reinterpret_cast<half*>(smem + ring_off);
+    const bool silu = p.epilogue == kEpilogueSiluMul;
+    const int col = tile * kTileRows + row;
+    const float b = (!silu && p.bias && col < p.out_cols) ? __half2float(p.bias[col]) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = (chunk0 + 2 * j) * 16 + i;
+        if (t < T) stage[t * kTileRows + row] = __float2half_rn(v[j][i] + b);
+      }
+    }
+    __syncthreads();
+    if (!silu) {
+      // 16 chunks of 8 columns per token
+      const int col_base = tile * kTileRows;
+      for (int u = tid; u < T * 16; u += kThreads) {
+        const int t = u >> 4, c0 = (u & 15) * 8;
+        const half* src = stage + t * kTileRows + c0;
+        half* dst = p.out + t * p.out_stride + col_base + c0;
+        if (p.out_vec && col_base + c0 + 8 <= p.out_cols) {
+          Stg16(dst, *reinterpret_cast<const uint4*>(src));
+        } else {
+          for (int e = 0; e < 8; ++e)
+            if (col_base + c0 + e < p.out_cols) dst[e] = src[e];
+        }
+      }
+    } else {
+      // rows 0-63 hold `gate`, rows 64-127 `up`, both already rounded to FP16: 8 chunks of 8 columns per token
+      const int col_base = tile * kHalfRows;
+      for (int u = tid; u < T * 8; u += kThreads) {
+        const int t = u >> 3, c0 = (u & 7) * 8;
+        const uint4 g = *reinterpret_cast<const uint4*>(stage + t * kTileRows + c0);
+        const uint4 up = *reinterpret_cast<const uint4*>(stage + t * kTileRows + kHalfRows + c0);
+        const uint4 r = SiluMulChunk(g, up);
+        half* dst = p.out + t * p.out_stride + col_base + c0;
+        if (p.out_vec && col_base + c0 + 8 <= p.out_cols) {
+          Stg16(dst, r);
+        } else {
+          const half* rh = reinterpret_cast<const half*>(&r);
+          for (int e = 0; e < 8; ++e)
+            if (col_base + c0 + e < p.out_cols) dst[e] = rh[e];
+        }
+      }
+    }
+    if (tid == 0) { RL_LSTAMP(8); }
+    return;
+  }
+
+  // ---- split K: token t belongs to CTA t mod S of the cluster. Every CTA stores its partial sums
+  // of token t into slice [its split][t / S] of the owner's receive area; after the cluster barrier
+  // the owner adds the S slices of each of its tokens in split order and writes the row.
+  const int S = p.splits, shift = p.split_shift;
+  const int slots = (T + S - 1) >> shift;   // tokens per owner, at most
+  float* recv = reinterpret_cast<float*>(smem + kRecvOff);
+  const uint32_t recv_mine = SmemAddr(recv) + static_cast<uint32_t>((split * slots) * kTileRows + row) * 4;
+  ClusterWait();  // every CTA of the cluster has started
+  uint32_t peer[kMaxSplits];
+#pragma unroll
+  for (int d = 0; d < kMaxSplits; ++d) peer[d] = PeerSmemAddr(recv_mine, d < S ? d : 0);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int t = (chunk0 + 2 * j) * 16 + i;
+      if (t < T) {
+        const int d = t & (S - 1), k = t >> shift;
+        uint32_t dst = peer[0];
+#pragma unroll
+        for (int e = 1; e < kMaxSplits; ++e) dst = d == e ? peer[e] : dst;
+        StPeerF32(dst + static_cast<uint32_t>(k * kTileRows) * 4, v[j][i]);
+      }
+    }
+  }
+  ClusterArriveRelease();
+  ClusterWait();
+  if (tid == 0) { RL_LSTAMP(7); }
+  {
+    const int my_tokens = T > split ? (T - split + S - 1) >> shift : 0;
+    const int col_base = tile * kTileRows;
+    for (int u = tid; u < my_tokens * 32; u += kThreads) {
+      const int k = u >> 5, c0 = (u & 31) * 4;
+      const int t = (k << shift) + split;
+      const float* src = recv + k * kTileRows + c0;
+      float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+        if (s2 < S) {
+          const float4 part = *reinterpret_cast<const float4*>(src + s2 * slots * kTileRows);
+          sum.x += part.x;
+          sum.y += part.y;
+          sum.z += part.z;
+          sum.w += part.w;
+        }
+      }
+      const int col = col_base + c0;
+      float bias4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (p.bias) {
+        for (int e = 0; e < 4; ++e)
+          if (col + e < p.out_cols) bias4[e] = __half2float(p.bias[col + e]);
+      }
+      const half2 lo = __floats2half2_rn(sum.x + bias4[0], sum.y + bias4[1]);
+      const half2 hi = __floats2half2_rn(sum.z + bias4[2], sum.w + bias4[3]);
+      half* dst = p.out + t * p.out_stride + col;
+      if (p.out_vec && col + 4 <= p.out_cols) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(AsU32(lo), AsU32(hi));
+      } else {
+        const half r[4] = {__low2half(lo), __high2half(lo), __low2half(hi), __high2half(hi)};
+        for (int e = 0; e < 4; ++e)
+          if (col + e < p.out_cols) dst[e] = r[e];
+      }
+    }
+  }
+  if (tid == 0) { RL_LSTAMP(8); }
+}
+
+// ------------------------------------------------------------------ host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  void* workspace = nullptr;  // error flag
+  int sm_count = 0;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_state[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mutex;
+void* g_timeline = nullptr;  // diagnostics build only
+int g_max_splits = kMaxSplits;
+int g_stages = 4;  // two CTAs of consecutive launches fit on one SM: the next one's weights stream in early
+
+int EnsureReady(DeviceState** out_state) {
+  const int dev = CurrentDeviceIndex();
+  DeviceState& st = g_state[dev];
+  *out_state = &st;
+  if (st.ready) return RL_OK;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (st.ready) return RL_OK;
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+      return Fail(e != cudaSuccess ? static_cast<int>(e) : RL_E_WORKSPACE,
+                  "decode_linear: cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const DeviceFacts& facts = CurrentDeviceFacts();
+  constexpr int kMostSmem = SmemBytes(kMaxStages, 1) > SmemBytes(kMaxStages - 1, 8) ? SmemBytes(kMaxStages, 1)
+                                                                                    : SmemBytes(kMaxStages - 1, 8);
+  if (facts.max_smem_optin < kMostSmem)
+    return Fail(RL_E_WORKSPACE, "decode_linear: device offers %d B of shared memory per block, %d needed",
+                facts.max_smem_optin, kMostSmem);
+  cudaError_t e = cudaFuncSetAttribute(DecodeLinearKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMostSmem);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "decode_linear: shared-memory opt-in: %s", cudaGetErrorString(e));
+  e = cudaMalloc(&st.workspace, 256);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "decode_linear: workspace: %s", cudaGetErrorString(e));
+  e = cudaMemset(st.workspace, 0, 256);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "decode_linear: workspace clear: %s", cudaGetErrorString(e));
+  st.sm_count = facts.sm_count;
+  st.ready = true;
+  return RL_OK;
+}
+
+// A row-major [rows, cols] FP16 matrix with `row_stride` elements between rows, boxes of 64 columns
+// (128 bytes, the swizzle span) by `box_rows` rows. Rows and columns past the extents read as zero.
+int EncodeMatrixMap(const void* base, int64_t rows, int64_t cols, int64_t row_stride, int box_rows,
+                    CUtensorMap* map) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "decode_linear: tensor map encode failed (CUresult %d)", static_cast<int>(r));
+  return RL_OK;
+}
+
+// CTAs per row tile along K (= cluster size: 1, 2, 4 or 8): the largest that keeps tiles x splits
+// within the SM count, unless a smaller one already gives every split a single k-block.
+int ChooseSplits(int tiles, int k_blocks, int sm_count) {
+  int best = 1;
+  for (int s = 2; s <= g_max_splits; s *= 2) {
+    if (tiles * s > sm_count || s > k_blocks) break;
+    best = s;
+  }
+  return best;
+}
+
+}  // namespace lin
+}  // namespace rl
+
+extern "C" int rl_decode_linear_health(int* flag_out) {
+  using namespace rl;
+  using namespace rl::lin;
+  if (!flag_out) return Fail(RL_E_NULL_POINTER, "rl_decode_linear_health: null pointer");
+  *flag_out = 0;
+  DeviceState& st = g_state[CurrentDeviceIndex()];
+  if (!st.ready) return RL_OK;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(flag_out, st.workspace, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && *flag_out != 0) e = cudaMemset(st.workspace, 0, sizeof(int));
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "rl_decode_linear_health: %s", cudaGetErrorString(e));
+  return RL_OK;
+}
+
+#ifdef RL_LIN_TIMELINE
+// Diagnostics build (-DRL_LIN_TIMELINE): per-CTA %globaltimer stamps of the last launch, 16 slots per CTA.
+extern "C" int rl_debug_linear_timeline(unsigned long long* host_out, int max_entries) {
+  cudaDeviceSynchronize();
+  const int n = 2048 * 16;
+  return cudaMemcpy(host_out, rl::lin::g_timeline, sizeof(unsigned long long) * (n < max_entries ? n : max_entries),
+                    cudaMemcpyDeviceToHost);
+}
+extern "C" int rl_debug_linear_timeline_init(void) {
+  const size_t bytes = sizeof(unsigned long long) * 2048 * 16;
+  if (!rl::lin::g_timeline) cudaMalloc(&rl::lin::g_timeline, bytes);
+  return cudaMemset(rl::lin::g_timeline, 0, bytes);
+}
+#endif
+
+extern "C" int rl_decode_linear_set_stages(int stages) {
+  using namespace rl;
+  if (stages < 2 || stages > lin::kMaxStages)
+    return Fail(RL_E_BAD_SHAPE, "rl_decode_linear_set_stages: 2..%d stages, got %d", lin::kMaxStages, stages);
+  lin::g_stages = stages;
+  return RL_OK;
+}
+
+extern "C" int rl_decode_linear_set_max_splits(int max_splits) {
+  using namespace rl;
+  if (max_splits != 1 && max_splits != 2 && max_splits != 4 && max_splits != 8)
+    return Fail(RL_E_BAD_SHAPE, "rl_decode_linear_set_max_splits: 1, 2, 4 or 8, got %d", max_splits);
+  lin::g_max_splits = max_splits;
+  return RL_OK;
+}
+
+extern "C" int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, int64_t x_row_stride,
+                                       const void* weight, int64_t weight_row_stride, const void* bias,
+                                       int32_t num_tokens, int32_t out_features, int32_t in_features,
+                                       int32_t epilogue, void* stream) {
+  using namespace rl;
+  using namespace rl::lin;
+  if (num_tokens <= 0 || out_features <= 0) return RL_OK;
+  if (!out || !x || !weight) return Fail(RL_E_NULL_POINTER, "decode_linear: null device pointer");
+  if (num_tokens > kMaxTokens)
+    return Fail(RL_E_TOO_LARGE, "decode_linear: at most %d token rows per call, got %d", kMaxTokens, num_tokens);
+  if (epilogue != kEpilogueBias && epilogue != kEpilogueSiluMul)
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: epilogue must be 0 (bias) or 1 (silu-mul)");
+  if (epilogue == kEpilogueSiluMul && bias)
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: the silu-mul epilogue takes no bias");
+  if (in_features < 8 || (in_features & 7) || (x_row_stride & 7) || (weight_row_stride & 7) || !Aligned16(x) ||
+      !Aligned16(weight))
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: x and weight rows must be 16-byte aligned, in_features a multiple of 8");
+  if (x_row_stride < in_features || weight_row_stride < in_features || out_row_stride < out_features)
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: row stride smaller than the row");
+  DeviceState* st;
+  int rc;
+  if ((rc = EnsureReady(&st)) != RL_OK) return rc;
+
+  const int weight_rows = epilogue == kEpilogueSiluMul ? 2 * out_features : out_features;
+  const int rows_per_tile = epilogue == kEpilogueSiluMul ? kHalfRows : kTileRows;
+  const int tiles = (out_features + rows_per_tile - 1) / rows_per_tile;
+  Params p;
+  p.out = static_cast<half*>(out);
+  p.out_stride = out_row_stride;
+  p.bias = static_cast<const half*>(bias);
+  p.tokens = num_tokens;
+  p.tokens_padded = (num_tokens + 15) & ~15;
+  p.out_cols = out_features;
+  p.up_row_offset = out_features;
+  p.k_blocks = (in_features + kBlockK - 1) / kBlockK;
+  p.splits = epilogue == kEpilogueSiluMul ? 1 : ChooseSplits(tiles, p.k_blocks, st->sm_count);
+  const int longest_split = (p.k_blocks + p.splits - 1) / p.splits;
+  p.stages = longest_split < g_stages ? (longest_split < 2 ? 2 : longest_split) : g_stages;
+  if (p.splits > 1 && p.stages > kMaxStages - 1) p.stages = kMaxStages - 1;  // room for the receive area
+  p.split_shift = p.splits == 8 ? 3 : p.splits == 4 ? 2 : p.splits == 2 ? 1 : 0;
+  p.epilogue = epilogue;
+  p.tmem_cols = p.tokens_padded <= 32 ? 32 : 64;
+  p.out_vec = (Aligned16(out) && (out_row_stride & 7) == 0) ? 1 : 0;
+  p.error_flag = static_cast<int*>(st->workspace);
+  p.timeline = nullptr;
+#ifdef RL_LIN_TIMELINE
+  p.timeline = static_cast<unsigned long long*>(g_timeline);
+#endif
+  CUtensorMap w_map, x_map;
+  if ((rc = EncodeMatrixMap(weight, weight_rows, in_features, weight_row_stride, kHalfRows, &w_map)) != RL_OK) return rc;
+  if ((rc = EncodeMatrixMap(x, num_tokens, in_features, x_row_stride, p.tokens_padded, &x_map)) != RL_OK) return rc;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * p.splits);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = SmemBytes(p.stages, p.splits);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_launch_overlap ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = p.splits;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, DecodeLinearKernel, p, w_map, x_map);
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "decode_linear: %s", cudaGetErrorString(e));
+  return LaunchStatus("decode_linear");
+}

@@ -276,6 +276,11 @@ class ModelExecutor:
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
+        # Linear layers of the decode step: "tcgen05" = this library's weight-streaming kernel (with the
+        # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
+        # The vocabulary projection always stays with the library.
+        self.decode_linear = "tcgen05"
+        self.act = torch.zeros(B, cfg.inter, dtype=f16, device=device)         # silu(gate) * up
         K.init(device.index if device.index is not None else -1)
 
     # ---- the decode layer sequence (src/core/model_executor.cpp:894-961)
@@ -289,7 +294,11 @@ class ModelExecutor:
                 K.launch_rms_norm(normed, x, L["in_norm"], rows, cfg.hidden, cfg.eps)
             else:
                 K.launch_rms_norm_residual(normed, x, mlp, L["in_norm"], rows, cfg.hidden, cfg.eps)
-            torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
+            own = self.decode_linear == "tcgen05"
+            if own:
+                K.launch_decode_linear(qkv, normed, L["qkv"], L["qkv_bias"], num_tokens=rows)
+            else:
+                torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
             if self.fuse_rope_scatter:
                 K.launch_rope_kv_scatter(qkv, cfg.qkv_width, self.pool[li], self.tables, self.mbps, self.positions,
                                          rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta)
@@ -308,11 +317,19 @@ class ModelExecutor:
             if self.attention_events is not None:
                 e1.record()
                 self.attention_events.append((e0, e1))
-            torch.matmul(attn, L["o"].t(), out=mlp)
+            if own:
+                K.launch_decode_linear(mlp, attn, L["o"], num_tokens=rows)
+            else:
+                torch.matmul(attn, L["o"].t(), out=mlp)
             K.launch_rms_norm_residual(normed, x, mlp, L["post_norm"], rows, cfg.hidden, cfg.eps)
-            torch.matmul(normed, L["gate_up"].t(), out=gu)
-            K.launch_silu_mul(gu, gu, rows, cfg.inter)
-            torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
+            if own:
+                act = self.act[:rows]
+                K.launch_decode_linear(act, normed, L["gate_up"], num_tokens=rows, epilogue=K.EPILOGUE_SILU_MUL)
+                K.launch_decode_linear(mlp, act, L["down"], num_tokens=rows)
+            else:
+                torch.matmul(normed, L["gate_up"].t(), out=gu)
+                K.launch_silu_mul(gu, gu, rows, cfg.inter)
+                torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
         K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, rows, cfg.hidden, cfg.eps)
         torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
         K.launch_greedy_argmax(self.tokens, self.logits, rows, cfg.vocab)
@@ -470,7 +487,8 @@ class Engine:
                  admission_policy: str = "reserve_full", pad_eager_to_bucket: int = 0,
                  debug_dump_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
                  device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
-                 graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True):
+                 graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True,
+                 decode_linear: str = "tcgen05"):
         import torch
         if admission_policy != "reserve_full":
             raise ValueError("only the reserve_full admission policy is provided")
@@ -491,7 +509,10 @@ class Engine:
         # tables are uploaded at the start of a step, never written by that kernel
         K.set_attention_prologue_overlap(prologue_overlap)
         self.weights = weights or ModelWeights(self.cfg, self.device, seed)
+        if decode_linear not in ("tcgen05", "library"):
+            raise ValueError("decode_linear must be 'tcgen05' or 'library'")
         self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
+        self.exec.decode_linear = decode_linear
         self.max_seq_len, self.max_batch = max_seq_len, max_batch
         self.pad_eager_to_bucket = pad_eager_to_bucket
         buckets = [b for b in BUCKETS if b <= select_bucket(max_batch)]

@@ -24,6 +24,8 @@ ABI_SYMBOLS = (
     "rl_launch_silu_mul", "rl_attention_health", "rl_launch_paged_attention_decode_static",
     "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
+    "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
+    "rl_decode_linear_set_max_splits",
 )
 
 
@@ -60,6 +62,10 @@ def lib() -> C.CDLL:
         L.rl_launch_kv_gather.argtypes = [vp, vp, i64, i64, i64, i64, vp, vp, i32, i32, i32, vp]
         L.rl_launch_prefill_softmax.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.rl_launch_rope_kv_scatter.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, vp]
+        L.rl_launch_decode_linear.argtypes = [vp, i64, vp, i64, vp, i64, vp, i32, i32, i32, i32, vp]
+        L.rl_decode_linear_health.argtypes = [C.POINTER(C.c_int)]
+        L.rl_decode_linear_set_stages.argtypes = [C.c_int]
+        L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
         _lib = L
@@ -188,6 +194,35 @@ def attention_health() -> int:
     """0 if every page load of the attention kernel arrived since the last query (synchronises)."""
     flag = C.c_int(0)
     _check(lib().rl_attention_health(C.byref(flag)), "rl_attention_health")
+    return flag.value
+
+
+EPILOGUE_BIAS, EPILOGUE_SILU_MUL = 0, 1
+
+
+def launch_decode_linear(out, x, weight, bias=None, num_tokens=None, epilogue=EPILOGUE_BIAS, stream=None):
+    """out[T, N] = x[T, K] . weight[N, K]^T (+ bias) for T <= 64 token rows (row views of 2-D tensors;
+    strides are taken from the tensors). With EPILOGUE_SILU_MUL weight is [2N, K] (gate rows, then up rows)
+    and out[T, N] = silu(gate) * up."""
+    T = x.shape[0] if num_tokens is None else num_tokens
+    N = out.shape[1]
+    _check(lib().rl_launch_decode_linear(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(weight),
+                                         weight.stride(0), _ptr(bias), T, N, x.shape[1], epilogue,
+                                         _stream(stream)), "decode linear")
+
+
+def set_decode_linear_stages(stages: int) -> None:
+    _check(lib().rl_decode_linear_set_stages(stages), "rl_decode_linear_set_stages")
+
+
+def set_decode_linear_max_splits(max_splits: int) -> None:
+    _check(lib().rl_decode_linear_set_max_splits(max_splits), "rl_decode_linear_set_max_splits")
+
+
+def decode_linear_health() -> int:
+    """0 if every bounded wait of the decode linear kernel completed since the last query (synchronises)."""
+    flag = C.c_int(0)
+    _check(lib().rl_decode_linear_health(C.byref(flag)), "rl_decode_linear_health")
     return flag.value
 
 
