@@ -246,11 +246,15 @@ class DecodeStepWorkload:
             e.exec.run(self.WAVE)
 
     def step_e2e(self):  # the public API: host mirrors -> H2D -> replay -> D2H of the sampled tokens
+        # every wave's step is begun (mirrors filled, H2D, graph replay and D2H enqueued) before the first
+        # one is ended, so the host work of wave i+1 overlaps the device work of wave i
         self.h2d = self.d2h = 0
         for e in self.engines:
-            e.step()
+            e.step_begin()
             self.h2d += e.exec.h2d_bytes
             self.d2h += 4 * self.WAVE
+        for e in self.engines:
+            e.step_end()
 
     def profile_attention(self, replays: int = 3):
         """The attention kernel's own duration inside this step: for every wave, the step's 28 attention
@@ -618,6 +622,8 @@ def main():
                     help="decode_step workload: sequences in the job (512 = the configuration; fewer for profiling)")
     ap.add_argument("--linear", choices=["tcgen05", "library"], default="tcgen05",
                     help="decode_step: linear layers by this library's tcgen05 kernel (default) or by the library GEMM")
+    ap.add_argument("--linear-stages", type=int, default=None, help="ring depth of the tcgen05 linear kernel (2..8)")
+    ap.add_argument("--linear-splits", type=int, default=None, help="largest K split of the tcgen05 linear kernel (1,2,4,8)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain attention launches (no programmatic dependent launch of the prologue)")
     ap.add_argument("--kernel", default=None, help="kernels workload: only entries whose name contains this")
@@ -649,6 +655,10 @@ def main():
 
     from redline_llm_b200 import kernels as _K
     _K.set_attention_prologue_overlap(not args.no_overlap)
+    if args.linear_stages is not None:
+        _K.set_decode_linear_stages(args.linear_stages)
+    if args.linear_splits is not None:
+        _K.set_decode_linear_max_splits(args.linear_splits)
     if args.workload == "kernels":
         peak, kind = measured_peaks()
         if rank == 0:

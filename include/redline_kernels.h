@@ -231,8 +231,8 @@ int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, in
  * 0 = every bounded wait inside the kernel completed; 1..3 name the wait that gave up. */
 int rl_decode_linear_health(int* flag_out);
 
-/* Tuning: depth of the kernel's shared-memory ring, 2..8 stages of 24 KB (default 4, which lets the
- * CTAs of two consecutive launches share an SM). Process-wide; affects later launches. */
+/* Tuning: depth of the kernel's shared-memory ring, 2..8 stages of 24 KB (default 6; a launch never uses
+ * more stages than its longest K split has k-blocks). Process-wide; affects later launches. */
 int rl_decode_linear_set_stages(int stages);
 
 /* Tuning: the largest number of CTAs a row tile may be split into along K (1, 2, 4 or 8; default 8).

@@ -273,6 +273,7 @@ class ModelExecutor:
         self._last_rows = 0
         self._last_tokens = None                            # tokens appended by the previous step (numpy)
         self.graphs: Dict[int, object] = {}
+        self.tokens_ready = torch.cuda.Event()   # recorded behind the D2H copy of the sampled tokens
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
@@ -421,8 +422,15 @@ class ModelExecutor:
             self.enqueue_decode(rows)
 
     def download(self, rows: int):
+        self.download_begin(rows)
+        return self.download_end(rows)
+
+    def download_begin(self, rows: int) -> None:
         self.h_tokens[:rows].copy_(self.tokens[:rows], non_blocking=True)
-        self.torch.cuda.current_stream().synchronize()
+        self.tokens_ready.record()
+
+    def download_end(self, rows: int):
+        self.tokens_ready.synchronize()
         return self.h_tokens[:rows].tolist()
 
     # ---- prompt ingestion (not on the hot path): chunked, eager, the reference's gather/GEMM/softmax/GEMM composite
@@ -520,6 +528,7 @@ class Engine:
             buckets = [b for b in buckets if b in set(graph_buckets)]
         self.exec.warm_and_capture(buckets)
         self._next_id = 0
+        self._pending = None   # a step begun and not yet ended
         self._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
         self._hist = {b: 0 for b in BUCKETS}
 
@@ -542,35 +551,59 @@ class Engine:
         return len(self.scheduler.running) + len(self.scheduler.waiting) < self.max_batch
 
     def step(self) -> List[Tuple[int, int, bool, str]]:
+        self.step_begin()
+        return self.step_end()
+
+    # A step in two halves, for a driver that runs several engines (replicas on different GPUs, or admission
+    # waves on one): step_begin() plans the step and, for a decode step, uploads the inputs and launches the
+    # forward pass without waiting for it; step_end() waits for the sampled tokens and returns what step()
+    # returns. Between the two the host is free to begin the steps of other engines. step() is the pair.
+    def step_begin(self) -> None:
+        if self._pending is not None:
+            raise RuntimeError("step_begin: the previous step has not been ended")
         plan = self.scheduler.plan_step()
         self._stats["steps"] += 1
         if plan[0] == "idle":
-            return []
+            self._pending = ("done", [])
+            return
         if plan[0] == "flush":
             out = []
             for r in plan[1]:
                 self.scheduler.release(r)
                 out.append((r.req_id, -1, True, r.reason))
-            return out
+            self._pending = ("done", out)
+            return
         if plan[0] == "prefill":
             _, r, start, end = plan
             tok = self.exec.prefill_chunk(r, start, end)
             self._stats["prefill_tokens"] += end - start
             if tok is None:
-                return []
+                self._pending = ("done", [])
+                return
             r.cached = len(r.prompt)
-            return [self.scheduler.complete(r, tok)]
+            self._pending = ("done", [self.scheduler.complete(r, tok)])
+            return
         batch = plan[1]
         rows = select_bucket(max(len(batch), self.pad_eager_to_bucket))
         self.exec.fill_mirrors(batch, rows)
         self.exec.upload(rows)
         self.exec.run(rows)
-        toks = self.exec.download(rows)
+        self.exec.download_begin(rows)
+        self._pending = ("decode", list(batch), rows)
+
+    def step_end(self) -> List[Tuple[int, int, bool, str]]:
+        if self._pending is None:
+            raise RuntimeError("step_end without step_begin")
+        pending, self._pending = self._pending, None
+        if pending[0] == "done":
+            return pending[1]
+        _, batch, rows = pending
+        toks = self.exec.download_end(rows)
         self._stats["graph_replays" if rows in self.exec.graphs else "eager_decodes"] += 1
         self._stats["decode_tokens"] += len(batch)
         self._hist[rows] += 1
         out = []
-        for r, t in zip(list(batch), toks):
+        for r, t in zip(batch, toks):
             r.cached += 1
             out.append(self.scheduler.complete(r, t))
         # what the next step feeds back (forced tokens included); any finished request changes the batch

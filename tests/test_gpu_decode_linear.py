@@ -27,7 +27,7 @@ def _need_gpu():
         pytest.skip("no CUDA device")
     K.init()
     yield
-    K.set_decode_linear_stages(4)
+    K.set_decode_linear_stages(6)
     assert K.decode_linear_health() == 0
 
 
@@ -157,7 +157,7 @@ def test_ring_depth_and_overlap_change_no_bit():
                         base = got
                     assert np.array_equal(got, base), f"stages={stages} overlap={overlap} changed the result"
     finally:
-        K.set_decode_linear_stages(4)
+        K.set_decode_linear_stages(6)
         K.set_attention_prologue_overlap(False)
 
 

@@ -78,13 +78,15 @@ def run_to_completion(e, limit=2000):
     return out
 
 
-def test_teacher_forced_decode_matches_fp32_forward(weights):
+@pytest.mark.parametrize("linear", ["tcgen05", "library"])
+def test_teacher_forced_decode_matches_fp32_forward(weights, linear):
     """Every decode step's logits agree with the FP32 forward; the greedy token agrees whenever the
-    reference's top-1/top-2 margin is not a coin flip."""
+    reference's top-1/top-2 margin is not a coin flip. Both choices for the linear layers: this
+    library's tcgen05 kernel (SiLU fused into the gate/up product) and the library GEMM."""
     rng = np.random.default_rng(3)
     prompt = rng.integers(0, CFG.vocab - 1, 45).tolist()
     forced = rng.integers(0, CFG.vocab - 1, 40).tolist()
-    e = make_engine(weights)
+    e = make_engine(weights, decode_linear=linear)
     rid = e.add_request(prompt, len(forced), ignore_eos=True, forced_tokens=forced)
     ref = torch_forward(weights, prompt + forced)
     scale = float(ref.abs().max())
@@ -122,6 +124,38 @@ def test_cuda_graph_replay_equals_eager_token_for_token(weights):
         s = e.stats()
         assert (s["graph_replays"] > 0) == graphs and (s["eager_decodes"] > 0) == (not graphs)
     assert outs[0] == outs[1]
+
+
+def test_steps_in_two_halves_across_engines_equal_whole_steps(weights):
+    """step_begin on every engine, then step_end on every engine (what a multi-replica driver does)
+    returns exactly what step() returns engine by engine."""
+    rng = np.random.default_rng(9)
+    prompts = [[rng.integers(0, CFG.vocab - 1, n).tolist() for n in ns] for ns in ((5, 33, 17), (64, 9), (21, 22, 23, 24))]
+
+    def fleet():
+        es = [make_engine(weights) for _ in prompts]
+        for e, ps in zip(es, prompts):
+            for p in ps:
+                e.add_request(p, 16, ignore_eos=True)
+        return es
+
+    whole, halves = fleet(), fleet()
+    busy = lambda es: any(e.stats()["running"] or e.stats()["waiting"] for e in es)
+    steps = 0
+    while busy(whole) and steps < 500:
+        want = [e.step() for e in whole]
+        for e in halves:
+            e.step_begin()
+        got = [e.step_end() for e in halves]
+        assert got == want
+        steps += 1
+    assert not busy(halves) and steps > 16
+    with pytest.raises(RuntimeError):
+        halves[0].step_end()
+    halves[0].step_begin()
+    with pytest.raises(RuntimeError):
+        halves[0].step_begin()
+    assert halves[0].step_end() == []
 
 
 def test_solo_and_batched_runs_agree_at_one_bucket_shape(weights):
