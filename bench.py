@@ -385,6 +385,25 @@ def kernel_table(peak, only=None, eager=False):
         secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pool, tab, tab.shape[1], pos, 64, 12, 2, 128, 1e6), 8)
         report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1024 + 64 * 8 + 256, "config 2 in one launch; latency-bound")
         del pool, qkv
+    # the four linear layers of a decoder block at 64 token rows: weight streams (28 distinct weights, cold L2)
+    for name, (n_out, k_in, epi, with_bias) in (("decode_linear_qkv_T64", (2048, 1536, 0, True)),
+                                                 ("decode_linear_o_T64", (1536, 1536, 0, False)),
+                                                 ("decode_linear_gate_up_silu_T64", (8960, 1536, 1, False)),
+                                                 ("decode_linear_down_T64", (1536, 8960, 0, False))):
+        if not want(name):
+            continue
+        nbuf = 28
+        rows = 2 * n_out if epi else n_out
+        ws = [dev(wl.normal_half(0x11A + i, rows * k_in, 0.0, k_in ** -0.5).reshape(rows, k_in)) for i in range(2)]
+        ws += [ws[i % 2].clone() for i in range(nbuf - 2)]
+        xs = dev(wl.normal_half(0x11B, 64 * k_in).reshape(64, k_in))
+        bias = dev(wl.normal_half(0x11C, n_out)) if with_bias else None
+        o = torch.empty(64, n_out, dtype=torch.int16, device="cuda")
+        secs = timed(lambda i: K.launch_decode_linear(o, xs, ws[i], bias, num_tokens=64, epilogue=epi), nbuf)
+        report(name, secs, rows * k_in * 2 + 64 * k_in * 2 + 64 * n_out * 2 + (n_out * 2 if with_bias else 0),
+               "tcgen05 weight stream; bytes = weights + activations in + out"
+               + ("; SiLU-mul fused, [T, 2I] never stored" if epi else ""))
+        del ws, o
     torch.cuda.empty_cache()
     return out
 

@@ -228,7 +228,7 @@ int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, in
                             int32_t epilogue, void* stream);
 
 /* Synchronises the device and reports (then clears) the error flag of rl_launch_decode_linear:
- * 0 = every bounded wait inside the kernel completed; 1..3 name the wait that gave up. */
+ * 0 = every bounded wait inside the kernel completed; 1..4 name the wait that gave up. */
 int rl_decode_linear_health(int* flag_out);
 
 /* Tuning: depth of the kernel's shared-memory ring, 2..8 stages of 24 KB (default 6; a launch never uses

@@ -49,7 +49,7 @@ constexpr int kXTileBytes = kMaxTokens * 128;   // 8192 (T x 128 B used)
 constexpr int kStageBytes = kWTileBytes + kXTileBytes;
 // Shared memory, from a 1024-byte aligned base: barriers and small slots, the receive area of a
 // split launch, then the ring. Without splits the idle ring stages the FP16 tile for the output pass.
-constexpr int kBarOff = 0;     // full[kMaxStages], empty[kMaxStages], accum, tmem slot
+constexpr int kBarOff = 0;     // full[kMaxStages], empty[kMaxStages], accum, receive, tmem slot
 constexpr int kRecvOff = 1024;                      // split K only: partial sums received from the cluster
 constexpr int kRecvBytes = kMaxTokens * kTileRows * 4;   // S slices x (64 / S) tokens x 128 rows, FP32
 __host__ __device__ constexpr int RingOff(int splits) { return splits > 1 ? kRecvOff + kRecvBytes : 1024; }
@@ -60,7 +60,7 @@ static_assert(2 * kStageBytes >= kMaxTokens * kTileRows * 2, "the FP16 output ti
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: a wait that never completes sets the error flag
 
 enum Epilogue { kEpilogueBias = 0, kEpilogueSiluMul = 1 };
-enum ErrorCode { kErrProducerWait = 1, kErrMmaWait = 2, kErrAccumWait = 3 };
+enum ErrorCode { kErrProducerWait = 1, kErrMmaWait = 2, kErrAccumWait = 3, kErrSplitWait = 4 };
 
 struct Params {
   half* out;
@@ -186,9 +186,6 @@ __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::af
 __device__ __forceinline__ void ClusterArriveRelaxed() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void ClusterArriveRelease() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void ClusterWait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -197,8 +194,11 @@ __device__ __forceinline__ uint32_t PeerSmemAddr(uint32_t local_addr, int cta_ra
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(cta_rank));
   return a;
 }
-__device__ __forceinline__ void StPeerF32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+// 16 bytes into a peer CTA's shared memory; completion is counted in bytes on the peer's mbarrier.
+__device__ __forceinline__ void StAsyncPeerF32x4(uint32_t addr, uint32_t mbar, float4 v) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(mbar)
+               : "memory");
 }
 
 #ifdef RL_LIN_TIMELINE
@@ -225,11 +225,9 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
   const int ring_off = RingOff(p.splits);
   const uint32_t ring = SmemAddr(smem + ring_off);
   const uint32_t bars = SmemAddr(smem + kBarOff);
-  // Split launches: tell the cluster this CTA is running (its shared memory may be written from now
-  // on); the matching wait comes just before the first remote store.
-  if (p.splits > 1) ClusterArriveRelaxed();
   const uint32_t full0 = bars, empty0 = bars + kMaxStages * 8, accum_bar = bars + 2 * kMaxStages * 8;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + (2 * kMaxStages + 1) * 8);
+  const uint32_t recv_bar = bars + (2 * kMaxStages + 1) * 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + (2 * kMaxStages + 2) * 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;  // split = rank in the cluster
@@ -250,6 +248,7 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
       MbarInit(empty0 + s * 8, 1);
     }
     MbarInit(accum_bar, 1);
+    MbarInit(recv_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // The first ring of weight tiles is requested at once: weights never depend on the previous
@@ -274,6 +273,11 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
   __syncthreads();
   TcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
+  // Split launches: tell the cluster this CTA is running with its barriers initialised (thread 0
+  // fenced the initialisation at cluster scope above, so a relaxed arrival is enough - a releasing one
+  // would wait here for the weight loads already in flight); the matching wait comes just before the
+  // first remote store.
+  if (p.splits > 1) ClusterArriveRelaxed();
   if (tid == 0) { RL_LSTAMP(1); }
 
   if (warp == 0) {
@@ -423,36 +427,43 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
     return;
   }
 
-  // ---- split K: token t belongs to CTA t mod S of the cluster. Every CTA stores its partial sums
-  // of token t into slice [its split][t / S] of the owner's receive area; after the cluster barrier
-  // the owner adds the S slices of each of its tokens in split order and writes the row.
+  // ---- split K: token t belongs to CTA t mod S of the cluster. Every CTA sends its partial sums of
+  // token t into slice [its split][t / S] of the owner's receive area with asynchronous stores that
+  // count bytes on the owner's mbarrier; the owner waits for all it expects (nobody waits for anything
+  // else), adds the S slices of each of its tokens in split order and writes the row.
   const int S = p.splits, shift = p.split_shift;
   const int slots = (T + S - 1) >> shift;   // tokens per owner, at most
+  const int my_tokens = T > split ? (T - split + S - 1) >> shift : 0;
   float* recv = reinterpret_cast<float*>(smem + kRecvOff);
-  const uint32_t recv_mine = SmemAddr(recv) + static_cast<uint32_t>((split * slots) * kTileRows + row) * 4;
-  ClusterWait();  // every CTA of the cluster has started
-  uint32_t peer[kMaxSplits];
-#pragma unroll
-  for (int d = 0; d < kMaxSplits; ++d) peer[d] = PeerSmemAddr(recv_mine, d < S ? d : 0);
+  // The owner expects 512 bytes per token from each of the S CTAs (its own included).
+  if (tid == 0) MbarExpectTx(recv_bar, my_tokens * S * kTileRows * 4);
+  // Transpose through the idle ring: [token][row] so that four rows of one token leave as one 16-byte store.
+  float* stage = reinterpret_cast<float*>(smem + ring_off);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int t = (chunk0 + 2 * j) * 16 + i;
-      if (t < T) {
-        const int d = t & (S - 1), k = t >> shift;
-        uint32_t dst = peer[0];
-#pragma unroll
-        for (int e = 1; e < kMaxSplits; ++e) dst = d == e ? peer[e] : dst;
-        StPeerF32(dst + static_cast<uint32_t>(k * kTileRows) * 4, v[j][i]);
-      }
+      if (t < T) stage[t * kTileRows + row] = v[j][i];
     }
   }
-  ClusterArriveRelease();
-  ClusterWait();
+  __syncthreads();
+  ClusterWait();  // every CTA of the cluster has started and armed its barrier
+  {
+    const uint32_t recv_slice = SmemAddr(recv) + static_cast<uint32_t>(split * slots * kTileRows) * 4;
+    for (int u = tid; u < T * 32; u += kThreads) {
+      const int t = u >> 5, c0 = (u & 31) * 4;
+      const int d = t & (S - 1), k = t >> shift;
+      const float4 val = *reinterpret_cast<const float4*>(stage + t * kTileRows + c0);
+      StAsyncPeerF32x4(PeerSmemAddr(recv_slice + static_cast<uint32_t>(k * kTileRows + c0) * 4, d),
+                       PeerSmemAddr(recv_bar, d), val);
+    }
+  }
+  if (!MbarWait(recv_bar, 0)) {
+    if (tid == 0) atomicExch(p.error_flag, kErrSplitWait);
+  }
   if (tid == 0) { RL_LSTAMP(7); }
   {
-    const int my_tokens = T > split ? (T - split + S - 1) >> shift : 0;
     const int col_base = tile * kTileRows;
     for (int u = tid; u < my_tokens * 32; u += kThreads) {
       const int k = u >> 5, c0 = (u & 31) * 4;
