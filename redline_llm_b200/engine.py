@@ -6,9 +6,11 @@ hot path needs to run - a reservation block allocator (src/core/block_allocator.
 FCFS continuous-batching scheduler with the {1,2,4,8,16,32,48,64} bucket ladder
 (src/core/scheduler.cpp:11-34,145-197,248-332) and a model executor that replays one CUDA graph per
 bucket (src/core/model_executor.cpp:523-633,721-782). The decode layer sequence is the reference's
-(src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library, every
-linear layer is a library GEMM (torch.matmul -> cuBLAS, unchanged on both sides of any comparison);
-the embedding gather and the greedy argmax at the two ends of the step are this library's too.
+(src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library; the four
+linear layers of a block are this library's tcgen05 weight-streaming kernel (SiLU-mul fused into the
+gate/up product) or, with decode_linear="library", library GEMMs as in the reference (torch.matmul ->
+cuBLAS); the vocabulary projection is always a library GEMM; the embedding gather and the greedy
+argmax at the two ends of the step are this library's too.
 
 One Engine drives one GPU; multi-GPU serving is one Engine per GPU with requests sharded on the
 host (`shard_requests`) - sequences and their KV pages never leave their GPU, so no collective exists.
