@@ -227,6 +227,22 @@ int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, in
                             int32_t num_tokens, int32_t out_features, int32_t in_features,
                             int32_t epilogue, void* stream);
 
+/*
+ * The QKV projection of a decode step with RoPE and the KV scatter in its epilogue: exactly
+ * rl_launch_decode_linear (epilogue 0, bias) into the fused qkv buffer (Q heads | K heads | V heads per row),
+ * followed by rl_launch_rope_inplace on the Q and K views and rl_launch_kv_scatter of K and V - same bits in
+ * the qkv buffer and in the pool, one launch instead of three (src/core/model_executor.cpp:916-930 runs the
+ * GEMM and the two kernels back to back). head_dim must be 128 (a 128-row weight tile is one head, so the CTA
+ * that finishes a token of a tile holds that token's whole head). weight is [(q_heads + 2 kv_heads) * 128,
+ * in_features]. Shapes the kernel would not split along K take the three-launch route internally.
+ */
+int rl_launch_qkv_rope_kv_scatter(void* qkv, int64_t qkv_row_stride, const void* x, int64_t x_row_stride,
+                                  const void* weight, int64_t weight_row_stride, const void* bias,
+                                  int32_t num_tokens, int32_t in_features, void* kv_pool_layer,
+                                  const int32_t* block_tables, int64_t block_table_row_stride,
+                                  const int32_t* positions, int32_t num_q_heads, int32_t num_kv_heads,
+                                  int32_t head_dim, float rope_theta, void* stream);
+
 /* Synchronises the device and reports (then clears) the error flag of rl_launch_decode_linear:
  * 0 = every bounded wait inside the kernel completed; 1..4 name the wait that gave up. */
 int rl_decode_linear_health(int* flag_out);

@@ -60,6 +60,10 @@ __device__ __forceinline__ void DependentLaunchGate() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// First-use set-up of the decode linear kernel on the current device (shared-memory opt-in, driver
+// entry point, error flag); rl_kernels_init calls it so that no launcher does set-up inside a capture.
+int DecodeLinearInit();
+
 inline bool Aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
 
 // 16-byte global access. .nc loads are for data this kernel never writes.

@@ -26,12 +26,18 @@
 //    W holds `gate` rows then `up` rows; a CTA takes 64 of each, rounds both accumulators to FP16
 //    (what a separate GEMM would have stored) and writes fp16(silu(gate) * up) - bit-identical to
 //    running the SiLU kernel on the GEMM's output (src/kernels/silu_mul.cu:67-83), without the
-//    [T, 2I] round trip.
+//    [T, 2I] round trip. Epilogue 2 is the fused QKV projection: a 128-row tile is exactly one head, so
+//    the CTA that finishes a token of a tile holds the whole head of that token; it adds the bias,
+//    rounds to FP16 (the GEMM output), rotates Q and K heads with the RoPE kernel's own arithmetic
+//    (rope_math.cuh), writes the row of the qkv buffer, and stores K and V heads to their slot of the
+//    paged pool - bit-identical to GEMM + RoPE + KV scatter (src/core/model_executor.cpp:916-930), two
+//    launches fewer.
 #include <cuda.h>
 
 #include <mutex>
 
 #include "common.cuh"
+#include "rope_math.cuh"
 #include "silu_math.cuh"
 
 namespace rl {
@@ -59,7 +65,7 @@ static_assert(SmemBytes(kMaxStages - 1, 8) <= 227 * 1024, "decode linear shared 
 static_assert(2 * kStageBytes >= kMaxTokens * kTileRows * 2, "the FP16 output tile is staged in the idle ring");
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: a wait that never completes sets the error flag
 
-enum Epilogue { kEpilogueBias = 0, kEpilogueSiluMul = 1 };
+enum Epilogue { kEpilogueBias = 0, kEpilogueSiluMul = 1, kEpilogueQkvRope = 2 };
 enum ErrorCode { kErrProducerWait = 1, kErrMmaWait = 2, kErrAccumWait = 3, kErrSplitWait = 4 };
 
 struct Params {
@@ -79,6 +85,17 @@ struct Params {
   int out_vec;           // out rows are 16-byte aligned: vector stores allowed
   int* error_flag;
   unsigned long long* timeline;  // diagnostics build only
+};
+
+// Epilogue 2 only: where the rotated K and the V of each token go, and the RoPE table.
+struct RopeArgs {
+  const int32_t* positions;
+  const int32_t* tables;
+  int64_t table_row_stride;
+  half* pool;          // one layer: [blocks][2][kv_heads][16][128]
+  int q_heads;
+  int kv_heads;
+  InvFreq inv_freq;
 };
 
 // ------------------------------------------------------------------ PTX
@@ -217,7 +234,7 @@ __device__ __forceinline__ unsigned long long GlobalTimerNs() {
 
 __global__ void __launch_bounds__(kThreads)
 DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
-                   const __grid_constant__ CUtensorMap x_map) {
+                   const __grid_constant__ CUtensorMap x_map, const __grid_constant__ RopeArgs rope) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -463,7 +480,59 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
     if (tid == 0) atomicExch(p.error_flag, kErrSplitWait);
   }
   if (tid == 0) { RL_LSTAMP(7); }
-  {
+  if (p.epilogue == kEpilogueQkvRope) {
+    // The tile is head `tile` of the fused QKV row (Q heads, then K heads, then V heads). A unit is four
+    // columns d..d+3 of the low half of the head together with their rotation partners d+64..d+67.
+    const int head = tile;
+    const bool rotate = head < rope.q_heads + rope.kv_heads;
+    for (int u = tid; u < my_tokens * 16; u += kThreads) {
+      const int k = u >> 4, c0 = (u & 15) * 4;
+      const int t = (k << shift) + split;
+      const float* src = recv + k * kTileRows + c0;
+      float4 lo4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi4 = lo4;
+#pragma unroll
+      for (int s2 = 0; s2 < kMaxSplits; ++s2) {
+        if (s2 < S) {
+          const float4 a = *reinterpret_cast<const float4*>(src + s2 * slots * kTileRows);
+          const float4 b4 = *reinterpret_cast<const float4*>(src + s2 * slots * kTileRows + 64);
+          lo4.x += a.x; lo4.y += a.y; lo4.z += a.z; lo4.w += a.w;
+          hi4.x += b4.x; hi4.y += b4.y; hi4.z += b4.z; hi4.w += b4.w;
+        }
+      }
+      const int col = head * kTileRows + c0;
+      if (p.bias) {
+        const half* bl = p.bias + col;
+        lo4.x += __half2float(bl[0]); lo4.y += __half2float(bl[1]); lo4.z += __half2float(bl[2]); lo4.w += __half2float(bl[3]);
+        hi4.x += __half2float(bl[64]); hi4.y += __half2float(bl[65]); hi4.z += __half2float(bl[66]); hi4.w += __half2float(bl[67]);
+      }
+      // the projection's FP16 output ...
+      uint32_t lo[2] = {AsU32(__floats2half2_rn(lo4.x, lo4.y)), AsU32(__floats2half2_rn(lo4.z, lo4.w))};
+      uint32_t hi[2] = {AsU32(__floats2half2_rn(hi4.x, hi4.y)), AsU32(__floats2half2_rn(hi4.z, hi4.w))};
+      const int pos = rope.positions[t];
+      if (rotate) {  // ... rotated in place for Q and K heads
+        const float fpos = static_cast<float>(pos);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const half2 a = RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j]);
+          const half2 b2 = RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j + 1]);
+          RotateWord(lo[j], hi[j], __lows2half2(a, b2), __highs2half2(a, b2));
+        }
+      }
+      half* dst = p.out + t * p.out_stride + col;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(lo[0], lo[1]);
+      *reinterpret_cast<uint2*>(dst + 64) = make_uint2(hi[0], hi[1]);
+      if (head >= rope.q_heads) {  // K (rotated) and V heads also go to this token's slot of the paged pool
+        const int kv = head >= rope.q_heads + rope.kv_heads ? 1 : 0;
+        const int kv_head = head - rope.q_heads - kv * rope.kv_heads;
+        const int64_t block = rope.tables[t * rope.table_row_stride + (pos >> kKvBlockShift)];
+        const int slot = pos & (kKvBlock - 1);
+        half* cell = rope.pool + (((block * 2 + kv) * rope.kv_heads + kv_head) * kKvBlock + slot) *
+                                     static_cast<int64_t>(kTileRows) + c0;
+        *reinterpret_cast<uint2*>(cell) = make_uint2(lo[0], lo[1]);
+        *reinterpret_cast<uint2*>(cell + 64) = make_uint2(hi[0], hi[1]);
+      }
+    }
+  } else {
     const int col_base = tile * kTileRows;
     for (int u = tid; u < my_tokens * 32; u += kThreads) {
       const int k = u >> 5, c0 = (u & 31) * 4;
@@ -580,6 +649,11 @@ int ChooseSplits(int tiles, int k_blocks, int sm_count) {
 }
 
 }  // namespace lin
+
+int DecodeLinearInit() {
+  lin::DeviceState* st;
+  return lin::EnsureReady(&st);
+}
 }  // namespace rl
 
 extern "C" int rl_decode_linear_health(int* flag_out) {
@@ -627,20 +701,16 @@ extern "C" int rl_decode_linear_set_max_splits(int max_splits) {
   return RL_OK;
 }
 
-extern "C" int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, int64_t x_row_stride,
-                                       const void* weight, int64_t weight_row_stride, const void* bias,
-                                       int32_t num_tokens, int32_t out_features, int32_t in_features,
-                                       int32_t epilogue, void* stream) {
-  using namespace rl;
-  using namespace rl::lin;
-  if (num_tokens <= 0 || out_features <= 0) return RL_OK;
+namespace rl {
+namespace lin {
+
+// Shared by the two entry points. `rope` is read by epilogue 2 only.
+int Launch(void* out, int64_t out_row_stride, const void* x, int64_t x_row_stride, const void* weight,
+           int64_t weight_row_stride, const void* bias, int num_tokens, int out_features, int in_features,
+           int epilogue, const RopeArgs& rope, void* stream, int* splits_out) {
   if (!out || !x || !weight) return Fail(RL_E_NULL_POINTER, "decode_linear: null device pointer");
   if (num_tokens > kMaxTokens)
     return Fail(RL_E_TOO_LARGE, "decode_linear: at most %d token rows per call, got %d", kMaxTokens, num_tokens);
-  if (epilogue != kEpilogueBias && epilogue != kEpilogueSiluMul)
-    return Fail(RL_E_BAD_SHAPE, "decode_linear: epilogue must be 0 (bias) or 1 (silu-mul)");
-  if (epilogue == kEpilogueSiluMul && bias)
-    return Fail(RL_E_BAD_SHAPE, "decode_linear: the silu-mul epilogue takes no bias");
   if (in_features < 8 || (in_features & 7) || (x_row_stride & 7) || (weight_row_stride & 7) || !Aligned16(x) ||
       !Aligned16(weight))
     return Fail(RL_E_BAD_SHAPE, "decode_linear: x and weight rows must be 16-byte aligned, in_features a multiple of 8");
@@ -663,6 +733,8 @@ extern "C" int rl_launch_decode_linear(void* out, int64_t out_row_stride, const 
   p.up_row_offset = out_features;
   p.k_blocks = (in_features + kBlockK - 1) / kBlockK;
   p.splits = epilogue == kEpilogueSiluMul ? 1 : ChooseSplits(tiles, p.k_blocks, st->sm_count);
+  if (splits_out) *splits_out = p.splits;
+  if (epilogue == kEpilogueQkvRope && p.splits == 1) return RL_OK;  // the caller takes the unfused route
   const int longest_split = (p.k_blocks + p.splits - 1) / p.splits;
   p.stages = longest_split < g_stages ? (longest_split < 2 ? 2 : longest_split) : g_stages;
   if (p.splits > 1 && p.stages > kMaxStages - 1) p.stages = kMaxStages - 1;  // room for the receive area
@@ -693,7 +765,67 @@ extern "C" int rl_launch_decode_linear(void* out, int64_t out_row_stride, const 
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, DecodeLinearKernel, p, w_map, x_map);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, DecodeLinearKernel, p, w_map, x_map, rope);
   if (e != cudaSuccess) return Fail(static_cast<int>(e), "decode_linear: %s", cudaGetErrorString(e));
   return LaunchStatus("decode_linear");
+}
+
+}  // namespace lin
+}  // namespace rl
+
+extern "C" int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, int64_t x_row_stride,
+                                       const void* weight, int64_t weight_row_stride, const void* bias,
+                                       int32_t num_tokens, int32_t out_features, int32_t in_features,
+                                       int32_t epilogue, void* stream) {
+  using namespace rl;
+  using namespace rl::lin;
+  if (num_tokens <= 0 || out_features <= 0) return RL_OK;
+  if (epilogue != kEpilogueBias && epilogue != kEpilogueSiluMul)
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: epilogue must be 0 (bias) or 1 (silu-mul)");
+  if (epilogue == kEpilogueSiluMul && bias)
+    return Fail(RL_E_BAD_SHAPE, "decode_linear: the silu-mul epilogue takes no bias");
+  static const RopeArgs no_rope = {};
+  return Launch(out, out_row_stride, x, x_row_stride, weight, weight_row_stride, bias, num_tokens, out_features,
+                in_features, epilogue, no_rope, stream, nullptr);
+}
+
+extern "C" int rl_launch_qkv_rope_kv_scatter(void* qkv, int64_t qkv_row_stride, const void* x, int64_t x_row_stride,
+                                             const void* weight, int64_t weight_row_stride, const void* bias,
+                                             int32_t num_tokens, int32_t in_features, void* kv_pool_layer,
+                                             const int32_t* block_tables, int64_t block_table_row_stride,
+                                             const int32_t* positions, int32_t num_q_heads, int32_t num_kv_heads,
+                                             int32_t head_dim, float rope_theta, void* stream) {
+  using namespace rl;
+  using namespace rl::lin;
+  if (num_tokens <= 0) return RL_OK;
+  if (!kv_pool_layer || !block_tables || !positions)
+    return Fail(RL_E_NULL_POINTER, "qkv_rope_kv_scatter: null device pointer");
+  if (head_dim != kTileRows || num_q_heads < 1 || num_kv_heads < 1 || !(rope_theta > 0.0f))
+    return Fail(RL_E_BAD_SHAPE, "qkv_rope_kv_scatter: head_dim must be 128, heads >= 1, theta > 0");
+  if (!Aligned16(qkv) || (qkv_row_stride & 7) || !Aligned16(kv_pool_layer))
+    return Fail(RL_E_BAD_SHAPE, "qkv_rope_kv_scatter: qkv rows and the pool slice must be 16-byte aligned");
+  const int out_features = (num_q_heads + 2 * num_kv_heads) * head_dim;
+  RopeArgs rope;
+  rope.positions = positions;
+  rope.tables = block_tables;
+  rope.table_row_stride = block_table_row_stride;
+  rope.pool = static_cast<half*>(kv_pool_layer);
+  rope.q_heads = num_q_heads;
+  rope.kv_heads = num_kv_heads;
+  rope.inv_freq = RopeTableFor(rope_theta, head_dim);
+  int splits = 0;
+  int rc = Launch(qkv, qkv_row_stride, x, x_row_stride, weight, weight_row_stride, bias, num_tokens, out_features,
+                  in_features, kEpilogueQkvRope, rope, stream, &splits);
+  if (rc != RL_OK || splits > 1) return rc;
+  // A shape this kernel does not split along K (few k-blocks, or splitting capped at 1): the same
+  // result in two launches.
+  static const RopeArgs no_rope = {};
+  rc = Launch(qkv, qkv_row_stride, x, x_row_stride, weight, weight_row_stride, bias, num_tokens, out_features,
+              in_features, kEpilogueBias, no_rope, stream, nullptr);
+  if (rc != RL_OK) return rc;
+  half* q = static_cast<half*>(qkv);
+  return rl_launch_rope_kv_scatter(q, q + num_q_heads * head_dim, q + (num_q_heads + num_kv_heads) * head_dim,
+                                   qkv_row_stride, qkv_row_stride, qkv_row_stride, kv_pool_layer, block_tables,
+                                   block_table_row_stride, positions, num_tokens, num_q_heads, num_kv_heads,
+                                   head_dim, rope_theta, stream);
 }

@@ -840,7 +840,8 @@ extern "C" int rl_kernels_init(int device) {
   }
   rl::CurrentDeviceFacts();
   rl::attn::DeviceState* st;
-  return rl::attn::EnsureReady(&st);
+  const int rc = rl::attn::EnsureReady(&st);
+  return rc != RL_OK ? rc : rl::DecodeLinearInit();
 }
 
 #ifdef RL_ATTN_TIMELINE

@@ -22,23 +22,11 @@
 #include <cmath>
 #include <mutex>
 
-#include "common.cuh"
-
-#if defined(__USE_FAST_MATH__)
-#error "rope needs the precise sincosf"
-#endif
+#include "rope_math.cuh"
 
 namespace rl {
-namespace {
 
-constexpr int kMaxPairs = 64;
-
-struct InvFreq {
-  float f[kMaxPairs];
-};
-
-// Host-side memo of the last table (pure host state; safe with any number of devices).
-const InvFreq& TableFor(float theta, int head_dim) {
+const InvFreq& RopeTableFor(float theta, int head_dim) {
   static std::mutex mu;
   static InvFreq table;
   static float cached_theta = 0.0f;
@@ -57,18 +45,12 @@ const InvFreq& TableFor(float theta, int head_dim) {
   return local;
 }
 
+namespace {
+
 __device__ __forceinline__ half* HeadPtr(half* q, half* k, int64_t qs, int64_t ks, int row, int head,
                                          int num_q_heads, int head_dim) {
   return head < num_q_heads ? q + row * qs + head * head_dim
                             : k + row * ks + (head - num_q_heads) * head_dim;
-}
-
-__device__ __forceinline__ void RotateWord(uint32_t& lo, uint32_t& hi, half2 c, half2 s) {
-  const half2 x1 = AsHalf2(lo), x2 = AsHalf2(hi);
-  const half2 a = __hadd2_rn(__hmul2_rn(x1, c), __hmul2_rn(__hneg2(x2), s));
-  const half2 b = __hadd2_rn(__hmul2_rn(x2, c), __hmul2_rn(x1, s));
-  lo = AsU32(a);
-  hi = AsU32(b);
 }
 
 // head_dim/2 a multiple of 8 and every head row 16-byte aligned.
@@ -81,9 +63,7 @@ RopeVecKernel(half* q, half* k, int64_t q_row_stride, int64_t k_row_stride,
   const int half_dim = head_dim >> 1;
   const float pos = static_cast<float>(positions[row]);
   for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
-    float s32, c32;
-    sincosf(pos * inv_freq.f[d], &s32, &c32);
-    cs[d] = __floats2half2_rn(c32, s32);
+    cs[d] = RopeCosSin(pos, inv_freq.f[d]);
   }
   __syncthreads();
   const int chunks = half_dim >> 3;
@@ -146,9 +126,7 @@ RopeScatterKernel(half* q, half* k, const half* __restrict__ v, int64_t q_row_st
   const int slot = p & (kKvBlock - 1);
   const float pos = static_cast<float>(p);
   for (int d = threadIdx.x; d < half_dim; d += blockDim.x) {
-    float s32, c32;
-    sincosf(pos * inv_freq.f[d], &s32, &c32);
-    cs[d] = __floats2half2_rn(c32, s32);
+    cs[d] = RopeCosSin(pos, inv_freq.f[d]);
   }
   __syncthreads();
   const int chunks = half_dim >> 3;
@@ -202,7 +180,7 @@ extern "C" int rl_launch_rope_inplace(void* q, void* k, int64_t q_row_stride, in
     return Fail(RL_E_BAD_SHAPE, "rope: head_dim must be even and <= 128, theta > 0");
   if ((num_q_heads > 0 && !q) || (num_kv_heads > 0 && !k) || !positions)
     return Fail(RL_E_NULL_POINTER, "rope: null device pointer");
-  const InvFreq& table = TableFor(rope_theta, head_dim);
+  const InvFreq& table = RopeTableFor(rope_theta, head_dim);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   half* qq = static_cast<half*>(q);
   half* kk = static_cast<half*>(k);
@@ -237,7 +215,7 @@ extern "C" int rl_launch_rope_kv_scatter(void* q, void* k, const void* v, int64_
     return rl_launch_kv_scatter(kv_pool_layer, k, v, k_row_stride, v_row_stride, block_tables,
                                 block_table_row_stride, positions, num_tokens, num_kv_heads, head_dim, stream);
   }
-  const InvFreq& table = TableFor(rope_theta, head_dim);
+  const InvFreq& table = RopeTableFor(rope_theta, head_dim);
   LaunchOverlapped(RopeScatterKernel, dim3(num_tokens), dim3(128), 0, static_cast<cudaStream_t>(stream),
                    static_cast<half*>(q), static_cast<half*>(k), static_cast<const half*>(v), q_row_stride,
                    k_row_stride, v_row_stride, static_cast<half*>(kv_pool_layer), block_tables,

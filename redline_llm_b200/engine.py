@@ -283,6 +283,7 @@ class ModelExecutor:
         # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
         # The vocabulary projection always stays with the library.
         self.decode_linear = "tcgen05"
+        self.fuse_qkv_rope = True      # RoPE + KV scatter in the QKV product's epilogue (tcgen05 path only)
         self.act = torch.zeros(B, cfg.inter, dtype=f16, device=device)         # silu(gate) * up
         K.init(device.index if device.index is not None else -1)
 
@@ -298,11 +299,17 @@ class ModelExecutor:
             else:
                 K.launch_rms_norm_residual(normed, x, mlp, L["in_norm"], rows, cfg.hidden, cfg.eps)
             own = self.decode_linear == "tcgen05"
-            if own:
+            fused_qkv = own and self.fuse_qkv_rope and cfg.head_dim == 128
+            if fused_qkv:
+                K.launch_qkv_rope_kv_scatter(qkv, normed, L["qkv"], L["qkv_bias"], self.pool[li], self.tables, self.mbps,
+                                             self.positions, rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta)
+            elif own:
                 K.launch_decode_linear(qkv, normed, L["qkv"], L["qkv_bias"], num_tokens=rows)
             else:
                 torch.addmm(L["qkv_bias"], normed, L["qkv"].t(), out=qkv)
-            if self.fuse_rope_scatter:
+            if fused_qkv:
+                pass
+            elif self.fuse_rope_scatter:
                 K.launch_rope_kv_scatter(qkv, cfg.qkv_width, self.pool[li], self.tables, self.mbps, self.positions,
                                          rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta)
             else:

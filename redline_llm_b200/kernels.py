@@ -25,7 +25,7 @@ ABI_SYMBOLS = (
     "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
-    "rl_decode_linear_set_max_splits",
+    "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter",
 )
 
 
@@ -64,6 +64,8 @@ def lib() -> C.CDLL:
         L.rl_launch_rope_kv_scatter.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp, i64, vp, i32, i32, i32, i32, f32, vp]
         L.rl_launch_decode_linear.argtypes = [vp, i64, vp, i64, vp, i64, vp, i32, i32, i32, i32, vp]
         L.rl_decode_linear_health.argtypes = [C.POINTER(C.c_int)]
+        L.rl_launch_qkv_rope_kv_scatter.argtypes = [vp, i64, vp, i64, vp, i64, vp, i32, i32, vp, vp, i64, vp,
+                                                    i32, i32, i32, f32, vp]
         L.rl_decode_linear_set_stages.argtypes = [C.c_int]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
@@ -209,6 +211,17 @@ def launch_decode_linear(out, x, weight, bias=None, num_tokens=None, epilogue=EP
     _check(lib().rl_launch_decode_linear(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(weight),
                                          weight.stride(0), _ptr(bias), T, N, x.shape[1], epilogue,
                                          _stream(stream)), "decode linear")
+
+
+def launch_qkv_rope_kv_scatter(qkv, x, weight, bias, kv_pool_layer, block_tables, block_table_row_stride, positions,
+                               num_tokens, num_q_heads, num_kv_heads, head_dim, rope_theta, stream=None):
+    """The QKV projection with RoPE and the KV scatter in its epilogue: one launch for
+    launch_decode_linear + launch_rope_inplace + launch_kv_scatter, same bits."""
+    _check(lib().rl_launch_qkv_rope_kv_scatter(_ptr(qkv), qkv.stride(0), _ptr(x), x.stride(0), _ptr(weight),
+                                               weight.stride(0), _ptr(bias), num_tokens, x.shape[1],
+                                               _ptr(kv_pool_layer), block_tables.data_ptr(), block_table_row_stride,
+                                               positions.data_ptr(), num_q_heads, num_kv_heads, head_dim, rope_theta,
+                                               _stream(stream)), "qkv + rope + kv scatter")
 
 
 def set_decode_linear_stages(stages: int) -> None:

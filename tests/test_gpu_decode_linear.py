@@ -141,6 +141,52 @@ def test_fused_silu_mul_is_bit_identical_to_the_two_step_path(T):
     assert np.array_equal(fused2[:T], host(out2))
 
 
+@pytest.mark.parametrize("T", [1, 7, 33, 64])
+def test_qkv_with_rope_and_scatter_in_the_epilogue_is_bit_identical_to_three_launches(T):
+    """Config-2 inputs (positions U[0,4096), permuted block tables, 8192-block pool slice) behind a QKV
+    product: the fused launch leaves the qkv buffer and the pool exactly as GEMM -> RoPE + scatter do."""
+    q_heads, kv_heads, D, H = 12, 2, 128, 1536
+    N = (q_heads + 2 * kv_heads) * D
+    c = wl.config_rope_scatter(64)
+    pos, tab = dev(c["positions"][:T].copy()), dev(c["tables"][:T].copy())
+    mbps = c["tables"].shape[1]
+    x, w = make(SEED + 71 + T, T, N, H)
+    bias = vector(SEED + 72, N)
+    xd, wd, bd = dev(x), dev(w), dev(bias)
+    pool_elems = c["num_blocks"] * 2 * kv_heads * 16 * D
+
+    def three_launches():
+        qkv = torch.full((64, N), 0x7E00, dtype=torch.int16, device="cuda")
+        pool = torch.full((pool_elems,), 0x7D01, dtype=torch.int16, device="cuda")
+        K.launch_decode_linear(qkv, xd, wd, bd, num_tokens=T)
+        K.launch_rope_kv_scatter(qkv, N, pool, tab, mbps, pos, T, q_heads, kv_heads, D, 1e6)
+        torch.cuda.synchronize()
+        return host(qkv), host(pool)
+
+    def fused():
+        qkv = torch.full((64, N), 0x7E00, dtype=torch.int16, device="cuda")
+        pool = torch.full((pool_elems,), 0x7D01, dtype=torch.int16, device="cuda")
+        K.launch_qkv_rope_kv_scatter(qkv, xd, wd, bd, pool, tab, mbps, pos, T, q_heads, kv_heads, D, 1e6)
+        torch.cuda.synchronize()
+        return host(qkv), host(pool)
+
+    want_qkv, want_pool = three_launches()
+    got_qkv, got_pool = fused()
+    assert np.array_equal(got_qkv, want_qkv), "qkv buffer differs"
+    assert np.array_equal(got_pool, want_pool), "pool differs"
+    assert (got_qkv[T:] == 0x7E00).all()
+    assert int((got_pool != 0x7D01).sum()) <= T * 2 * kv_heads * D   # only the T tokens' K and V cells
+    # with splitting capped at 1 the entry point takes the three-launch route itself
+    K.set_decode_linear_max_splits(1)
+    try:
+        ref1_qkv, ref1_pool = three_launches()
+        one_qkv, one_pool = fused()
+    finally:
+        K.set_decode_linear_max_splits(8)
+    assert np.array_equal(one_qkv, ref1_qkv) and np.array_equal(one_pool, ref1_pool)
+    assert K.decode_linear_health() == 0
+
+
 def test_ring_depth_and_overlap_change_no_bit():
     cases = [(64, 1536, 8960, False), (33, 2048, 1536, True), (64, 17920, 1536, False)]
     try:
