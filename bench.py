@@ -236,9 +236,9 @@ class DecodeStepWorkload:
         self.weight_bytes = sum(t.numel() * 2 for L in wts.layers for t in L.values()) + wts.final_norm.numel() * 2 \
             + wts.lm_head.numel() * 2  # streamed once per wave per step (the embedding rows gathered are negligible)
         self.kv_bytes_per_token = self.cfg.layers * 2 * self.cfg.kv_heads * self.cfg.head_dim * 2
-        # own kernels per layer: 2 norms, RoPE+scatter, attention, and either SiLU (library GEMMs) or the
-        # four linear layers (SiLU fused into the gate/up product); + embed, final norm, argmax
-        self.launches_per_step = len(self.engines) * (self.cfg.layers * (8 if linear == "tcgen05" else 5) + 3)
+        # own kernels per layer: 2 norms and attention, plus RoPE+scatter and SiLU beside library GEMMs, or the
+        # four linear layers (RoPE+scatter fused into the QKV product, SiLU into gate/up); + embed, final norm, argmax
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * (7 if linear == "tcgen05" else 5) + 3)
         self.h2d = self.d2h = 0
 
     def step(self):  # inputs already resident: graph replays only
@@ -580,7 +580,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
                    "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
                    "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
-                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (SiLU fused), "
+                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter fused into QKV, SiLU into gate/up), "
                             "library GEMM for the vocabulary projection, FP16" if args.linear == "tcgen05"
                             else "library (cuBLAS via torch.matmul), FP16"),
                    "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
