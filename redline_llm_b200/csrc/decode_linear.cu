@@ -17,11 +17,11 @@
 //    after it, so the stream of weights starts while the previous kernel drains.
 //  * Shapes with few row tiles are split along K so that tiles x splits fills the GPU. The S splits
 //    of a tile (2, 4 or 8) form one thread-block cluster. Token t of the tile is finished by CTA
-//    t mod S: every CTA stores the FP32 partial sums of that token straight into the owner's shared
-//    memory (distributed shared memory; remote stores do not stall the sender), the cluster meets
-//    once at the hardware cluster barrier, and each owner adds the S slices it received in split
-//    order 0..S-1 from its own shared memory. No global workspace, no atomics, no spinning; results
-//    do not depend on arrival order.
+//    t mod S: every CTA sends the FP32 partial sums of that token into the owner's shared memory
+//    with asynchronous distributed-shared-memory stores (st.async) that count bytes on the owner's
+//    mbarrier; the owner waits (bounded) until everything it expects has landed and adds the S
+//    slices in split order 0..S-1 from its own shared memory. No global workspace, no atomics;
+//    results do not depend on arrival order.
 //  * Epilogue 0 adds the bias in FP32 and rounds once to FP16. Epilogue 1 is the gated MLP input:
 //    W holds `gate` rows then `up` rows; a CTA takes 64 of each, rounds both accumulators to FP16
 //    (what a separate GEMM would have stored) and writes fp16(silu(gate) * up) - bit-identical to
@@ -62,7 +62,7 @@ __host__ __device__ constexpr int RingOff(int splits) { return splits > 1 ? kRec
 __host__ __device__ constexpr int SmemBytes(int stages, int splits) { return RingOff(splits) + stages * kStageBytes + 1024; }  // + slack to align the base
 static_assert(SmemBytes(kMaxStages, 1) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
 static_assert(SmemBytes(kMaxStages - 1, 8) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
-static_assert(2 * kStageBytes >= kMaxTokens * kTileRows * 2, "the FP16 output tile is staged in the idle ring");
+static_assert(2 * kStageBytes >= kMaxTokens * kTileRows * 4, "the tile (FP16, or FP32 before a split's exchange) is staged in two idle stages");
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s: a wait that never completes sets the error flag
 
 enum Epilogue { kEpilogueBias = 0, kEpilogueSiluMul = 1, kEpilogueQkvRope = 2 };

@@ -146,4 +146,33 @@ inline void LaunchSiluMul(half* out, const half* gate_up, std::int32_t num_token
                 "LaunchSiluMul");
 }
 
+// ---- beyond the reference header: the linear layers of the decode step (no counterpart in
+// src/kernels/; an executor opts in where it calls its GEMM wrapper, src/core/model_executor.cpp:916-951).
+
+// out[T, N] = x[T, K] . weight[N, K]^T (+ bias), T <= 64. silu_mul = true: weight is [2N, K] (gate rows, then
+// up rows), bias must be null, out[T, N] = silu(gate) * up.
+inline void LaunchDecodeLinear(half* out, std::int64_t out_row_stride, const half* x, std::int64_t x_row_stride,
+                               const half* weight, std::int64_t weight_row_stride, const half* bias,
+                               std::int32_t num_tokens, std::int32_t out_features, std::int32_t in_features,
+                               bool silu_mul, cudaStream_t stream) {
+  detail::Check(rl_launch_decode_linear(out, out_row_stride, x, x_row_stride, weight, weight_row_stride, bias,
+                                        num_tokens, out_features, in_features, silu_mul ? 1 : 0, stream),
+                "LaunchDecodeLinear");
+}
+
+// QKV projection + LaunchRopeInplace + LaunchKvScatter in one launch, same bits (head_dim 128).
+inline void LaunchQkvRopeKvScatter(half* qkv, std::int64_t qkv_row_stride, const half* x, std::int64_t x_row_stride,
+                                   const half* weight, std::int64_t weight_row_stride, const half* bias,
+                                   std::int32_t num_tokens, std::int32_t in_features, half* kv_pool_layer,
+                                   const std::int32_t* block_tables, std::int64_t block_table_row_stride,
+                                   const std::int32_t* positions, std::int32_t num_q_heads,
+                                   std::int32_t num_kv_heads, std::int32_t head_dim, float rope_theta,
+                                   cudaStream_t stream) {
+  detail::Check(rl_launch_qkv_rope_kv_scatter(qkv, qkv_row_stride, x, x_row_stride, weight, weight_row_stride, bias,
+                                              num_tokens, in_features, kv_pool_layer, block_tables,
+                                              block_table_row_stride, positions, num_q_heads, num_kv_heads,
+                                              head_dim, rope_theta, stream),
+                "LaunchQkvRopeKvScatter");
+}
+
 }  // namespace redline::kernels
