@@ -562,6 +562,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
     health = K.attention_health()
+    linear_health = K.decode_linear_health()
     if rank != 0:
         return
     tokens = w.TOTAL
@@ -600,7 +601,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
         "gpu_launches": w.launches_per_step * args.steps * world,
         "clocks": clocks.summary(),
-        "check": {"attention_health": health},
+        "check": {"attention_health": health, "linear_health": linear_health},
     }
     if not args.no_cpu_baseline and world == 1:
         rows = sample_rows(w, 2)
