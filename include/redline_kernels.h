@@ -119,11 +119,15 @@ int rl_launch_paged_attention_decode(void* out, int64_t out_row_stride, const vo
  * Opt-in (default 0): launch the attention kernel with programmatic stream serialisation, so its
  * prologue - the page prefix over seq_lens and the first block-table reads - overlaps the tail of
  * the previous kernel of the stream (this library's KV-scatter / RoPE+scatter kernels and the
- * attention kernel itself release their dependents early). The kernel waits for that previous
- * kernel to complete before it reads the pool or Q and before it writes anything. The one new rule
- * for the caller: seq_lens and block_tables must not be produced by the kernel launched
- * immediately before the attention launcher (in the reference's executor they are uploaded once
- * per step, src/core/model_executor.cpp:876-892). Process-wide; set it before capture.
+ * attention kernel itself release their dependents early), and so do the loads of its first K/V
+ * pages other than each sequence's last page. The kernel waits for that previous kernel to complete
+ * before it reads Q or any sequence's last page (the page this step's scatter writes) and before it
+ * writes anything. Two rules for the caller: seq_lens and block_tables must not be produced by a
+ * kernel still in flight when the attention launcher is called (in the reference's executor they are
+ * uploaded once per step, src/core/model_executor.cpp:876-892); and such kernels may write the pool
+ * only in each sequence's last page, as a decode step's scatter does (after a prefill that scattered
+ * whole prompts, synchronise the stream or run one launch without the option). The option also makes
+ * the norm / RoPE / scatter / linear launchers use dependent launch. Process-wide; set it before capture.
  * No counterpart in the reference.
  */
 int rl_attention_set_prologue_overlap(int enable);

@@ -73,6 +73,7 @@ constexpr int kMaxSeqsPerLaunch = 1024;
 constexpr int kORowPad = 132;           // floats per query row in the merge buffer (bank spread)
 constexpr int kPartialFloats = kGroup * kHeadDim + 16;  // o[6][128], m[6], l[6], pad
 constexpr int kMaxCtas = 256;           // workspace is sized for this many CTAs
+constexpr int kNewestPageBit = 1 << 30; // tile indices stay below 2^30: a 180 GB device holds < 2^26 tiles
 
 // Shared-memory carve (offsets from a 1024-byte aligned base).
 constexpr int kRingOff = 0;
@@ -335,7 +336,9 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     if (k >= n_mine) return 0;
     const Cursor c = Locate(share_begin + warp + kWarps * k, prefix, num_seqs, heads);
     const int block = LdgKeepInL2(p.tables + static_cast<int64_t>(c.seq) * p.max_blocks + c.page, keep_policy);
-    return block * 2 * heads + c.head;
+    // The last page of a sequence holds the token this step has just written: it is marked, so that it
+    // is never requested before the previous kernel of the stream has completed.
+    return (block * 2 * heads + c.head) | (c.page == c.pages - 1 ? kNewestPageBit : 0);
   };
   int tiles_cur = fetch_tiles(0);
   int tiles_next = n_mine > 32 ? fetch_tiles(1) : 0;
@@ -344,10 +347,40 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   // (the KV scatter of this layer, or the previous attention call) was still running: wait for it
   // to complete before reading the pool or Q, or writing the output and the workspace. A no-op for
   // an ordinary launch.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  //
+  // The first ring of pages is requested BEFORE that wait, except pages that hold a sequence's newest
+  // token: every other page was written by an earlier step, so its load can run under the tail of the
+  // previous kernel and its DRAM latency is off the critical path. (Contract of the overlap option:
+  // kernels still in flight when this one starts may write only each sequence's last page.)
   int n_issue = 0, n_use = 0;
+  int deferred = 0;  // bit i: page i of the first ring waits for the dependency gate
+  {
+    const int first = n_mine < kStages ? n_mine : kStages;
+#pragma unroll 1
+    for (int i = 0; i < first; ++i) {
+      const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, i);
+      if (tile_k & kNewestPageBit) {
+        deferred |= 1 << i;
+      } else if (lane == 0) {
+        MbarExpectTx(my_bars + i * 8, kStageBytes);
+        TmaLoadPage(my_ring + i * kStageBytes, &tile_map, tile_k, my_bars + i * 8, stream_policy);
+      }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll 1
+    for (int i = 0; i < first; ++i) {
+      if ((deferred >> i) & 1) {
+        const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, i) & ~kNewestPageBit;
+        if (lane == 0) {
+          MbarExpectTx(my_bars + i * 8, kStageBytes);
+          TmaLoadPage(my_ring + i * kStageBytes, &tile_map, tile_k, my_bars + i * 8, stream_policy);
+        }
+      }
+    }
+    n_issue = first;
+  }
   auto issue_one = [&]() {
-    const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, n_issue & 31);
+    const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, n_issue & 31) & ~kNewestPageBit;
     if (lane == 0) {
       const int stage = n_issue % kStages;
       const uint32_t dst = my_ring + stage * kStageBytes;
@@ -361,9 +394,6 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       tiles_next = fetch_tiles((n_issue >> 5) + 1);
     }
   };
-#pragma unroll 1
-  for (int i = 0; i < kStages && n_issue < n_mine; ++i) issue_one();
-
   // ldmatrix byte offsets inside a stage, fixed per lane. K tile: k-steps j and j+4 are 2048
   // apart (the two 64-dim boxes); V tile likewise for dim tiles j and j+4.
   uint32_t koff[4], voff[4];
