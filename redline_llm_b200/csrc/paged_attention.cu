@@ -65,14 +65,21 @@ constexpr int kStages = RL_ATTN_STAGES; // pages in flight per warp
 constexpr int kMergeGroups = kThreads / 128;          // heads merged side by side
 constexpr int kHeadsPerGroup = 6 / kMergeGroups;      // heads each 128-thread group walks
 static_assert(kThreads % 128 == 0 && 6 % kMergeGroups == 0, "warps per CTA must be 4, 8 or 12");
-constexpr int kSeqsPerThread = (1024 + kThreads - 1) / kThreads;
+#ifndef RL_ATTN_CTAS_PER_SM
+#define RL_ATTN_CTAS_PER_SM 1
+#endif
+#ifndef RL_ATTN_MAX_SEQS
+#define RL_ATTN_MAX_SEQS 1024
+#endif
+constexpr int kCtasPerSm = RL_ATTN_CTAS_PER_SM;
+constexpr int kSeqsPerThread = (RL_ATTN_MAX_SEQS + kThreads - 1) / kThreads;
 constexpr int kInlineContributors = 3;  // items over at most this many CTAs are merged from registers
 constexpr int kPageBytes = kKvBlock * kHeadDim * 2;  // 4096: one (block, kv, head) tile
 constexpr int kStageBytes = 2 * kPageBytes;          // K tile + V tile
-constexpr int kMaxSeqsPerLaunch = 1024;
+constexpr int kMaxSeqsPerLaunch = RL_ATTN_MAX_SEQS;
 constexpr int kORowPad = 132;           // floats per query row in the merge buffer (bank spread)
 constexpr int kPartialFloats = kGroup * kHeadDim + 16;  // o[6][128], m[6], l[6], pad
-constexpr int kMaxCtas = 256;           // workspace is sized for this many CTAs
+constexpr int kMaxCtas = 256 * kCtasPerSm;  // workspace is sized for this many CTAs
 constexpr int kNewestPageBit = 1 << 30; // tile indices stay below 2^30: a 180 GB device holds < 2^26 tiles
 
 // Shared-memory carve (offsets from a 1024-byte aligned base).
@@ -88,6 +95,7 @@ constexpr int kPrefixOff = kBarOff + kBarBytes;
 constexpr int kPrefixBytes = (kMaxSeqsPerLaunch + 8) * 4;
 constexpr int kSmemBytes = kPrefixOff + kPrefixBytes + 1024;  // + slack to align the base
 static_assert(kSmemBytes <= 227 * 1024, "attention shared memory exceeds the 227 KB per-CTA limit");
+static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 228 * 1024, "that many CTAs do not fit one SM's shared memory");
 
 // Workspace (one per device): meta ints, then kMaxCtas * 2 partial records.
 constexpr int kTicketOff = 16;                     // meta[0] = error flag, meta[16 + c] = tickets of
@@ -251,7 +259,7 @@ __device__ __forceinline__ Cursor Locate(long long t, const int* prefix, int num
 
 // --------------------------------------------------------------- kernel
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap tile_map) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -823,7 +831,7 @@ int EnsureReady(DeviceState** out_state) {
   if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention: workspace: %s", cudaGetErrorString(e));
   e = cudaMemset(st.workspace, 0, kWorkspaceBytes);
   if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_attention: workspace clear: %s", cudaGetErrorString(e));
-  st.ctas = facts.sm_count < kMaxCtas ? facts.sm_count : kMaxCtas;
+  st.ctas = facts.sm_count * kCtasPerSm < kMaxCtas ? facts.sm_count * kCtasPerSm : kMaxCtas;
   st.ready = true;
   return RL_OK;
 }
