@@ -59,7 +59,13 @@ constexpr int kStageBytes = kWTileBytes + kXTileBytes;
 constexpr int kBarOff = 0;     // full[kMaxStages], empty[kMaxStages], accum, receive, tmem slot
 constexpr int kRecvOff = 1024;                      // split K only: partial sums received from the cluster
 constexpr int kRecvBytes = kMaxTokens * kTileRows * 4;   // S slices x (64 / S) tokens x 128 rows, FP32
-__host__ __device__ constexpr int RingOff(int splits) { return splits > 1 ? kRecvOff + kRecvBytes : 1024; }
+// Epilogue 2 only: {cos, sin} of this CTA's tokens (FP16 pairs) and each token's position and page block,
+// prepared by the idle epilogue warps while the weights stream.
+constexpr int kRopeSlots = 16;                              // tokens per owner covered by the table (T / S <= 16 for S >= 4)
+constexpr int kRopeOff = kRecvOff + kRecvBytes;
+constexpr int kRopeBytes = kRopeSlots * (kMaxPairs * 4 + 8) + 512;   // 4 KB of pairs + (pos, block) per token, rounded to 5 KB
+static_assert((kRopeOff + 5120) % 1024 == 0 && kRopeBytes <= 5120, "rope table carve");
+__host__ __device__ constexpr int RingOff(int splits) { return splits > 1 ? kRopeOff + 5120 : 1024; }
 __host__ __device__ constexpr int SmemBytes(int stages, int splits) { return RingOff(splits) + stages * kStageBytes + 1024; }  // + slack to align the base
 static_assert(SmemBytes(kMaxStages, 1) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
 static_assert(SmemBytes(kMaxStages - 1, 8) <= 227 * 1024, "decode linear shared memory exceeds the 227 KB per-CTA limit");
@@ -178,6 +184,29 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
   // first remote store.
   if (p.splits > 1) ClusterArriveRelaxed();
   if (tid == 0) { RL_LSTAMP(1); }
+
+  // Epilogue 2: positions and block tables were uploaded at the start of the step, so warps 2-7 - idle until the
+  // accumulator is ready - prepare what the RoPE + scatter epilogue needs for the tokens this CTA will finish
+  // (t = split, split + S, ...): position, page block, and the FP16 {cos, sin} of all 64 rotation pairs.
+  half2* rope_cs = reinterpret_cast<half2*>(smem + kRopeOff);
+  int* rope_pos = reinterpret_cast<int*>(smem + kRopeOff + kRopeSlots * kMaxPairs * 4);
+  int* rope_block = rope_pos + kRopeSlots;
+  const bool rope_table = p.epilogue == kEpilogueQkvRope && p.splits > 1 &&
+                          ((T + p.splits - 1) >> p.split_shift) <= kRopeSlots;
+  if (rope_table && warp >= 2) {
+    const int mine = T > split ? (T - split + p.splits - 1) >> p.split_shift : 0;
+    const bool rotate = tile < rope.q_heads + rope.kv_heads;
+    for (int u = tid - 64; u < mine * kMaxPairs; u += kThreads - 64) {
+      const int k = u >> 6, d = u & (kMaxPairs - 1);
+      const int t = (k << p.split_shift) + split;
+      const int pos = rope.positions[t];
+      if (d == 0) {
+        rope_pos[k] = pos;
+        rope_block[k] = tile >= rope.q_heads ? rope.tables[t * rope.table_row_stride + (pos >> kKvBlockShift)] : 0;
+      }
+      if (rotate) rope_cs[k * kMaxPairs + d] = RopeCosSin(static_cast<float>(pos), rope.inv_freq.f[d]);
+    }
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -390,13 +419,14 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
       // the projection's FP16 output ...
       uint32_t lo[2] = {AsU32(__floats2half2_rn(lo4.x, lo4.y)), AsU32(__floats2half2_rn(lo4.z, lo4.w))};
       uint32_t hi[2] = {AsU32(__floats2half2_rn(hi4.x, hi4.y)), AsU32(__floats2half2_rn(hi4.z, hi4.w))};
-      const int pos = rope.positions[t];
+      const int pos = rope_table ? rope_pos[k] : rope.positions[t];
       if (rotate) {  // ... rotated in place for Q and K heads
         const float fpos = static_cast<float>(pos);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const half2 a = RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j]);
-          const half2 b2 = RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j + 1]);
+          const half2 a = rope_table ? rope_cs[k * kMaxPairs + c0 + 2 * j] : RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j]);
+          const half2 b2 = rope_table ? rope_cs[k * kMaxPairs + c0 + 2 * j + 1]
+                                      : RopeCosSin(fpos, rope.inv_freq.f[c0 + 2 * j + 1]);
           RotateWord(lo[j], hi[j], __lows2half2(a, b2), __highs2half2(a, b2));
         }
       }
@@ -406,7 +436,7 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
       if (head >= rope.q_heads) {  // K (rotated) and V heads also go to this token's slot of the paged pool
         const int kv = head >= rope.q_heads + rope.kv_heads ? 1 : 0;
         const int kv_head = head - rope.q_heads - kv * rope.kv_heads;
-        const int64_t block = rope.tables[t * rope.table_row_stride + (pos >> kKvBlockShift)];
+        const int64_t block = rope_table ? rope_block[k] : rope.tables[t * rope.table_row_stride + (pos >> kKvBlockShift)];
         const int slot = pos & (kKvBlock - 1);
         half* cell = rope.pool + (((block * 2 + kv) * rope.kv_heads + kv_head) * kKvBlock + slot) *
                                      static_cast<int64_t>(kTileRows) + c0;
