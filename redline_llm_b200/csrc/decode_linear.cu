@@ -208,6 +208,18 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
     }
   }
 
+  // The bias of the columns this thread will finish in a split epilogue-2 launch (column group fixed per thread),
+  // fetched now rather than after the exchange.
+  float bias_lo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bias_hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (p.epilogue == kEpilogueQkvRope && p.bias) {
+    const half* bl = p.bias + tile * kTileRows + (tid & 15) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      bias_lo[e] = __half2float(bl[e]);
+      bias_hi[e] = __half2float(bl[64 + e]);
+    }
+  }
+
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: activations once the previous kernel has completed, then the steady state
@@ -411,11 +423,8 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
         }
       }
       const int col = head * kTileRows + c0;
-      if (p.bias) {
-        const half* bl = p.bias + col;
-        lo4.x += __half2float(bl[0]); lo4.y += __half2float(bl[1]); lo4.z += __half2float(bl[2]); lo4.w += __half2float(bl[3]);
-        hi4.x += __half2float(bl[64]); hi4.y += __half2float(bl[65]); hi4.z += __half2float(bl[66]); hi4.w += __half2float(bl[67]);
-      }
+      lo4.x += bias_lo[0]; lo4.y += bias_lo[1]; lo4.z += bias_lo[2]; lo4.w += bias_lo[3];   // zeros without a bias
+      hi4.x += bias_hi[0]; hi4.y += bias_hi[1]; hi4.z += bias_hi[2]; hi4.w += bias_hi[3];
       // the projection's FP16 output ...
       uint32_t lo[2] = {AsU32(__floats2half2_rn(lo4.x, lo4.y)), AsU32(__floats2half2_rn(lo4.z, lo4.w))};
       uint32_t hi[2] = {AsU32(__floats2half2_rn(hi4.x, hi4.y)), AsU32(__floats2half2_rn(hi4.z, hi4.w))};
