@@ -186,6 +186,37 @@ int main() {
     Require(ok, "LaunchRmsNormResidual writes back fp16(residual + input) exactly");
     Require(worst <= 4e-3, "LaunchRmsNormResidual output within FP16 rounding of the FP64 result");
   }
+  // ---- decode-sized linear layer (beyond the reference header): product against a host double sum, and the
+  // gated epilogue against the product followed by LaunchSiluMul
+  {
+    constexpr int kLinT = 9, kLinK = 256, kLinI = 192;
+    std::vector<half> lx = RandomHalves(static_cast<size_t>(kLinT) * kLinK, -1.0, 1.0);
+    std::vector<half> lw = RandomHalves(static_cast<size_t>(2 * kLinI) * kLinK, -0.0625, 0.0625);
+    half *d_lx = Upload(lx), *d_lw = Upload(lw);
+    half *d_prod = nullptr, *d_act = nullptr, *d_two = nullptr;
+    cudaMalloc(&d_prod, sizeof(half) * kLinT * 2 * kLinI);
+    cudaMalloc(&d_act, sizeof(half) * kLinT * kLinI);
+    cudaMalloc(&d_two, sizeof(half) * kLinT * kLinI);
+    rl_decode_linear_set_max_splits(1);  // the gated product is never split along K: compare like with like
+    rk::LaunchDecodeLinear(d_prod, 2 * kLinI, d_lx, kLinK, d_lw, kLinK, nullptr, kLinT, 2 * kLinI, kLinK, false, stream);
+    rl_decode_linear_set_max_splits(8);
+    rk::LaunchDecodeLinear(d_act, kLinI, d_lx, kLinK, d_lw, kLinK, nullptr, kLinT, kLinI, kLinK, true, stream);
+    rk::LaunchSiluMul(d_two, d_prod, kLinT, kLinI, stream);
+    cudaStreamSynchronize(stream);
+    const auto prod = Download(d_prod, static_cast<size_t>(kLinT) * 2 * kLinI);
+    const auto act = Download(d_act, static_cast<size_t>(kLinT) * kLinI), two = Download(d_two, static_cast<size_t>(kLinT) * kLinI);
+    double worst = 0.0;
+    for (int t = 0; t < kLinT; ++t)
+      for (int n = 0; n < 2 * kLinI; ++n) {
+        double sum = 0.0;
+        for (int k = 0; k < kLinK; ++k) sum += static_cast<double>(__half2float(lx[(size_t)t * kLinK + k])) * __half2float(lw[(size_t)n * kLinK + k]);
+        worst = std::fmax(worst, std::fabs(sum - __half2float(prod[(size_t)t * 2 * kLinI + n])));
+      }
+    bool same = true;
+    for (size_t i = 0; i < act.size(); ++i) same = same && Bits(act[i]) == Bits(two[i]);
+    Require(worst <= 1.5e-3, "LaunchDecodeLinear within FP16 rounding of the host double product");
+    Require(same, "LaunchDecodeLinear with the gated epilogue equals product + LaunchSiluMul bit for bit");
+  }
   Require(cudaGetLastError() == cudaSuccess, "no CUDA error left behind");
   std::printf("all checks passed\n");
   return 0;
