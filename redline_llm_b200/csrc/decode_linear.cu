@@ -595,12 +595,12 @@ extern "C" int rl_decode_linear_health(int* flag_out) {
 // Diagnostics build (-DRL_LIN_TIMELINE): per-CTA %globaltimer stamps of the last launch, 16 slots per CTA.
 extern "C" int rl_debug_linear_timeline(unsigned long long* host_out, int max_entries) {
   cudaDeviceSynchronize();
-  const int n = 2048 * 16;
+  const int n = 128 * 2048 * 16;
   return cudaMemcpy(host_out, rl::lin::g_timeline, sizeof(unsigned long long) * (n < max_entries ? n : max_entries),
                     cudaMemcpyDeviceToHost);
 }
 extern "C" int rl_debug_linear_timeline_init(void) {
-  const size_t bytes = sizeof(unsigned long long) * 2048 * 16;
+  const size_t bytes = sizeof(unsigned long long) * 128 * 2048 * 16;
   if (!rl::lin::g_timeline) cudaMalloc(&rl::lin::g_timeline, bytes);
   return cudaMemset(rl::lin::g_timeline, 0, bytes);
 }
@@ -666,7 +666,11 @@ int Launch(void* out, int64_t out_row_stride, const void* x, int64_t x_row_strid
   p.error_flag = static_cast<int*>(st->workspace);
   p.timeline = nullptr;
 #ifdef RL_LIN_TIMELINE
-  p.timeline = static_cast<unsigned long long*>(g_timeline);
+  {  // one 2048 x 16 region per launch, 128 regions in rotation
+    static int launch_seq = 0;
+    p.timeline = g_timeline ? static_cast<unsigned long long*>(g_timeline) + static_cast<size_t>(launch_seq++ % 128) * 2048 * 16
+                            : nullptr;
+  }
 #endif
   CUtensorMap w_map, x_map;
   if ((rc = EncodeMatrixMap(weight, weight_rows, in_features, weight_row_stride, kHalfRows, &w_map)) != RL_OK) return rc;

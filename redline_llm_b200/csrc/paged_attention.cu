@@ -74,6 +74,7 @@ static_assert(kThreads % 128 == 0 && 6 % kMergeGroups == 0, "warps per CTA must 
 constexpr int kCtasPerSm = RL_ATTN_CTAS_PER_SM;
 constexpr int kSeqsPerThread = (RL_ATTN_MAX_SEQS + kThreads - 1) / kThreads;
 constexpr int kInlineContributors = 3;  // items over at most this many CTAs are merged from registers
+constexpr int kMergeBatch = 8;          // longer items: records fetched this many contributors at a time
 constexpr int kPageBytes = kKvBlock * kHeadDim * 2;  // 4096: one (block, kv, head) tile
 constexpr int kStageBytes = 2 * kPageBytes;          // K tile + V tile
 constexpr int kMaxSeqsPerLaunch = RL_ATTN_MAX_SEQS;
@@ -702,32 +703,47 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
             load_others();
             combine_inline();
           } else {
-            // Many contributors (a long sequence over many CTAs): two passes over the records (L2 reads,
-            // independent per contributor) - running max per head, then the rescaled sums, in CTA order.
-            float mx[kHeadsPerGroup];
+            // Many contributors (a long sequence over many CTAs). This CTA is the last to arrive, so the whole
+            // grid waits for it: the records are fetched kMergeBatch contributors at a time, every load of a
+            // batch in flight before the first use (one L2 round trip per batch instead of one per
+            // contributor), and folded in CTA order with a running maximum, as an online softmax does.
+            float mx[kHeadsPerGroup], a[kHeadsPerGroup], dn[kHeadsPerGroup];
 #pragma unroll
-            for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = -INFINITY;
-#pragma unroll 4
-            for (int c = c_first; c <= c_last; ++c) {
-              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats +
-                               kGroup * kHeadDim + q0;
-#pragma unroll
-              for (int qi = 0; qi < kHeadsPerGroup; ++qi) mx[qi] = fmaxf(mx[qi], __ldcg(r + kMergeGroups * qi));
+            for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+              mx[qi] = -INFINITY;
+              a[qi] = dn[qi] = 0.0f;
             }
-            float a[kHeadsPerGroup], dn[kHeadsPerGroup];
+#pragma unroll 1
+            for (int c0 = c_first; c0 <= c_last; c0 += kMergeBatch) {
+              float mv[kMergeBatch][kHeadsPerGroup], ov[kMergeBatch][kHeadsPerGroup], lv[kMergeBatch][kHeadsPerGroup];
+              bool live[kMergeBatch];
 #pragma unroll
-            for (int qi = 0; qi < kHeadsPerGroup; ++qi) a[qi] = dn[qi] = 0.0f;
-#pragma unroll 2
-            for (int c = c_first; c <= c_last; ++c) {
-              if (sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas)) continue;
-              const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+              for (int j = 0; j < kMergeBatch; ++j) {
+                const int c = c0 + j;
+                live[j] = c <= c_last && !(sparse && ShareBegin(c, total, ctas) == ShareBegin(c + 1, total, ctas));
+                if (live[j]) {
+                  const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
 #pragma unroll
-              for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
-                const int qh = q0 + kMergeGroups * qi;
-                const float f = Exp2(__ldcg(r + kGroup * kHeadDim + qh) - mx[qi]);
-                a[qi] = fmaf(f, __ldcg(r + qh * kHeadDim + d), a[qi]);
-                dn[qi] = fmaf(f, __ldcg(r + kGroup * kHeadDim + 8 + qh), dn[qi]);
+                  for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+                    const int qh = q0 + kMergeGroups * qi;
+                    mv[j][qi] = __ldcg(r + kGroup * kHeadDim + qh);
+                    ov[j][qi] = __ldcg(r + qh * kHeadDim + d);
+                    lv[j][qi] = __ldcg(r + kGroup * kHeadDim + 8 + qh);
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < kMergeBatch; ++j) {
+                if (live[j]) {
+#pragma unroll
+                  for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+                    const float m_new = fmaxf(mx[qi], mv[j][qi]);
+                    const float keep = Exp2(mx[qi] - m_new), add = Exp2(mv[j][qi] - m_new);
+                    a[qi] = fmaf(add, ov[j][qi], a[qi] * keep);
+                    dn[qi] = fmaf(add, lv[j][qi], dn[qi] * keep);
+                    mx[qi] = m_new;
+                  }
+                }
               }
             }
 #pragma unroll
@@ -886,12 +902,12 @@ extern "C" int rl_kernels_init(int device) {
 // Diagnostics build (-DRL_ATTN_TIMELINE): per-warp %globaltimer stamps of the last launch.
 extern "C" int rl_debug_attention_timeline(unsigned long long* host_out, int max_entries) {
   cudaDeviceSynchronize();
-  const int n = rl::attn::kMaxCtas * rl::attn::kWarps * 8;
+  const int n = 32 * rl::attn::kMaxCtas * rl::attn::kWarps * 8;
   return cudaMemcpy(host_out, rl::attn::g_timeline, sizeof(unsigned long long) * (n < max_entries ? n : max_entries),
                     cudaMemcpyDeviceToHost);
 }
 extern "C" int rl_debug_attention_timeline_init(void) {
-  const size_t bytes = sizeof(unsigned long long) * rl::attn::kMaxCtas * rl::attn::kWarps * 8;
+  const size_t bytes = sizeof(unsigned long long) * 32 * rl::attn::kMaxCtas * rl::attn::kWarps * 8;
   if (!rl::attn::g_timeline) cudaMalloc(&rl::attn::g_timeline, bytes);
   return cudaMemset(rl::attn::g_timeline, 0, bytes);
 }
@@ -958,7 +974,12 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
     p.timeline = nullptr;
 #ifdef RL_ATTN_TIMELINE
-    p.timeline = static_cast<unsigned long long*>(g_timeline);
+    {  // one region per launch, 32 regions in rotation
+      static int launch_seq = 0;
+      p.timeline = g_timeline ? static_cast<unsigned long long*>(g_timeline) +
+                                    static_cast<size_t>(launch_seq++ % 32) * kMaxCtas * kWarps * 8
+                              : nullptr;
+    }
 #endif
     const cudaError_t e = LaunchOverlapped(PagedAttentionSplitKernel, dim3(st->ctas), dim3(kThreads), kSmemBytes, s,
                                            p, tile_map);
