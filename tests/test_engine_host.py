@@ -104,6 +104,74 @@ def test_randomised_churn_never_leaks_blocks():
     assert len(out) == 60 and a.free_blocks == 199 and a.reserved == 0
 
 
+def test_step_halves_with_a_scripted_executor():
+    """Engine.step_begin / step_end (the two halves a multi-engine driver interleaves) over a stub executor:
+    same results as step(), one pending step at a time, prefill chunks complete inside step_begin."""
+    from redline_llm_b200.engine import Engine, ModelConfig
+
+    class StubExecutor:
+        graphs = {}
+        h2d_bytes = 0
+        _last_tokens = None
+
+        def __init__(self):
+            self.calls = []
+
+        def fill_mirrors(self, batch, rows):
+            self.calls.append(("fill", len(batch), rows))
+
+        def upload(self, rows):
+            self.calls.append(("upload", rows))
+
+        def run(self, rows):
+            self.calls.append(("run", rows))
+
+        def download_begin(self, rows):
+            self.calls.append(("d2h", rows))
+
+        def download_end(self, rows):
+            self.calls.append(("wait", rows))
+            return [3] * rows
+
+        def prefill_chunk(self, r, start, end):
+            self.calls.append(("prefill", start, end))
+            r.prefilled = end
+            return 5 if end == len(r.prompt) else None
+
+    def make():
+        e = Engine.__new__(Engine)
+        e.cfg = ModelConfig()
+        e.allocator = BlockAllocator(64)
+        e.scheduler = Scheduler(e.allocator, 4, 256, 16, e.cfg.eos_token_id)
+        e.exec = StubExecutor()
+        e.max_seq_len, e.max_batch, e.pad_eager_to_bucket = 256, 4, 0
+        e._next_id, e._pending = 0, None
+        e._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
+        e._hist = {b: 0 for b in BUCKETS}
+        e.add_request(list(range(1, 21)), 3, ignore_eos=True)
+        e.add_request([4, 5], 2, ignore_eos=True)
+        return e
+
+    whole, halves = make(), make()
+    want, got = [], []
+    for _ in range(12):
+        want.append(whole.step())
+        halves.step_begin()
+        with pytest.raises(RuntimeError):
+            halves.step_begin()
+        got.append(halves.step_end())
+    assert got == want
+    with pytest.raises(RuntimeError):
+        halves.step_end()
+    assert whole.stats() == halves.stats() and whole.stats()["running"] == 0
+    calls = halves.exec.calls
+    # a decode step launches everything in step_begin and only waits in step_end
+    i = calls.index(("run", 2)) if ("run", 2) in calls else calls.index(("run", 1))
+    assert calls[i + 1][0] == "d2h" and calls[i + 2][0] == "wait"
+    flat = [t for step in got for t in step]
+    assert sorted(r[0] for r in flat if r[2]) == [0, 1] and all(r[3] in ("", "length") for r in flat)
+
+
 def test_shard_requests_partitions_without_overlap():
     for world in (1, 2, 4, 8):
         seen = sorted(i for r in range(world) for i in shard_requests(512, world, r))
