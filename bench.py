@@ -210,11 +210,15 @@ class DecodeStepWorkload:
         import torch
         self.TOTAL, self.LONG = total, total // 16
         self.linear = linear
-        from redline_llm_b200.engine import Engine, ModelConfig, ModelWeights, blocks_for_tokens, shard_requests
+        from redline_llm_b200.engine import (Engine, ModelConfig, ModelWeights, balanced_order, blocks_for_tokens,
+                                             shard_requests)
         self.torch = torch
         ctx = np.concatenate([wl.randint(wl.SEED_STEP, self.TOTAL - self.LONG, 1024, 8192),
                               np.full(self.LONG, 32768, np.int32)])
         ctx = ctx[wl.permutation(wl.SEED_STEP + 1, self.TOTAL)]
+        # the host-side router: longest first, snake-dealt over 8 shards, so that at every GPU count each GPU serves
+        # the same number of 32 768-token sequences and (within ~1 %) the same number of cached tokens
+        ctx = ctx[balanced_order(ctx, shards=8, seed=wl.SEED_STEP + 2)]
         mine = [int(ctx[i]) for i in shard_requests(self.TOTAL, world, rank)]
         self.cfg = ModelConfig()
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -581,6 +585,8 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
                    "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
                    "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
+                   "router": "host-side: longest first, snake-dealt over 8 shards (every GPU serves 32/N of the "
+                             "32768-token sequences and the same number of cached tokens within 1 %)",
                    "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter fused into QKV, SiLU into gate/up), "
                             "library GEMM for the vocabulary projection, FP16" if args.linear == "tcgen05"
                             else "library (cuBLAS via torch.matmul), FP16"),

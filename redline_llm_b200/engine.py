@@ -78,6 +78,29 @@ def shard_requests(num_requests: int, world: int, rank: int) -> List[int]:
     return list(range(rank, num_requests, world))
 
 
+def balanced_order(costs: Sequence[int], shards: int = 8, seed: int = 0) -> List[int]:
+    """A serving order for requests with the given costs (e.g. context lengths) such that dealing it round-robin
+    (`shard_requests`) over `shards` replicas - or over any divisor of `shards` - gives every replica nearly the
+    same total cost: requests are taken longest first and dealt to the shards in snake order (0..s-1, s-1..0, ...),
+    then the positions inside the shards are shuffled (seeded, the same shuffle for every shard) so that the long
+    requests do not all sit at the front. Index i of the result goes to shard i % shards. Host logic only."""
+    n = len(costs)
+    by_cost = sorted(range(n), key=lambda i: (-int(costs[i]), i))
+    lists: List[List[int]] = [[] for _ in range(shards)]
+    for k, i in enumerate(by_cost):
+        lap, pos = divmod(k, shards)
+        lists[pos if lap % 2 == 0 else shards - 1 - pos].append(i)
+    depth = max(len(x) for x in lists)
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(depth)
+    out: List[int] = []
+    for j in perm:
+        for x in lists:
+            if j < len(x):
+                out.append(x[int(j)])
+    return out
+
+
 class BlockAllocator:
     """Free-list allocator with reservations: a request reserves the blocks it can ever need at
     admission (`reserve_full`), then turns reservations into real blocks at 16-token boundaries."""

@@ -172,6 +172,25 @@ def test_step_halves_with_a_scripted_executor():
     assert sorted(r[0] for r in flat if r[2]) == [0, 1] and all(r[3] in ("", "length") for r in flat)
 
 
+def test_balanced_order_gives_every_replica_the_same_load():
+    """The router order used by the benchmark: a permutation; dealt round-robin over 8, 4 or 2 replicas every
+    replica gets the same number of long requests and the same total context within 1 %."""
+    import random
+    from redline_llm_b200.engine import balanced_order
+    rnd = random.Random(11)
+    costs = [rnd.randint(1024, 8192) for _ in range(480)] + [32768] * 32
+    rnd.shuffle(costs)
+    order = balanced_order(costs, shards=8, seed=3)
+    assert sorted(order) == list(range(512))
+    assert order == balanced_order(costs, shards=8, seed=3)
+    dealt = [costs[i] for i in order]
+    for world in (8, 4, 2):
+        totals = [sum(dealt[i] for i in shard_requests(512, world, r)) for r in range(world)]
+        longs = [sum(1 for i in shard_requests(512, world, r) if dealt[i] == 32768) for r in range(world)]
+        assert len(set(longs)) == 1 and max(totals) <= 1.01 * min(totals), (world, totals, longs)
+    assert balanced_order([5, 1, 9], shards=8) in ([2, 0, 1], [0, 2, 1], [2, 1, 0], [1, 2, 0], [0, 1, 2], [1, 0, 2])
+
+
 def test_shard_requests_partitions_without_overlap():
     for world in (1, 2, 4, 8):
         seen = sorted(i for r in range(world) for i in shard_requests(512, world, r))
