@@ -239,6 +239,9 @@ int rl_launch_decode_linear(void* out, int64_t out_row_stride, const void* x, in
  * GEMM and the two kernels back to back). head_dim must be 128 (a 128-row weight tile is one head, so the CTA
  * that finishes a token of a tile holds that token's whole head). weight is [(q_heads + 2 kv_heads) * 128,
  * in_features]. Shapes the kernel would not split along K take the three-launch route internally.
+ * With dependent launch on (rl_attention_set_prologue_overlap) positions and block_tables are read before the
+ * launch waits for the previous kernel, like seq_lens and block_tables in the attention launcher: they must
+ * not be produced by a kernel still in flight (an executor uploads them at the start of the step).
  */
 int rl_launch_qkv_rope_kv_scatter(void* qkv, int64_t qkv_row_stride, const void* x, int64_t x_row_stride,
                                   const void* weight, int64_t weight_row_stride, const void* bias,
