@@ -7,17 +7,15 @@
 //   ms  = mean(f32(h)^2), FP32             over the ROUNDED h
 //   out = fp16( fp16(f32(h) * rsqrtf(ms + eps)) * weight )   rounding point 2 before the weight
 //
-// Mapping. Rows are cut into 16-byte chunks (8 halves); chunk c = 32*i + lane.
-//   many rows : one WARP per row, the row kept in registers as packed halves
-//               between the two passes (row read once, written once), no shared
-//               memory, no block barrier - the HBM-streaming shape;
-//   few rows  : one CTA per row, one chunk per thread, so a decode batch of 64
-//               rows runs on 6 x 64 warps instead of 64 and the dependent
-//               instruction chain per thread is 8 elements long, not 48.
-// Both use ONE summation order - per chunk left to right from zero, a lane-xor
-// tree over the 32 chunks of each group i, then the groups in ascending i - so a
-// row gives the same bits whichever shape ran it and whatever the batch size.
-// A scalar block-per-row kernel covers odd widths and 2-byte-aligned bases.
+// Mapping. Rows are cut into 16-byte chunks (8 halves). One CTA per row, one chunk per
+// thread (thread = 32*i + lane): the row is read once and written once, the dependent
+// instruction chain per thread is 8 elements long, and a decode batch of 64 rows still
+// runs on 6 x 64 warps. The same shape is also the fastest at HBM-bound sizes (many
+// small CTAs keep more loads in flight per SM than a warp per row with the row in
+// registers: 32.0 against 34.0 us at 16384 x 1536, 5.6 against 8.0 us at 2048 x 1536).
+// Summation order: per chunk left to right from zero, a lane-xor tree over the 32 chunks
+// of each group i, then the groups in ascending i - a row gives the same bits whatever
+// the batch size. A scalar block-per-row kernel covers odd widths and 2-byte-aligned bases.
 #include "common.cuh"
 
 #if defined(__USE_FAST_MATH__)
@@ -65,49 +63,6 @@ __device__ __forceinline__ uint4 NormChunk(const uint4& h, const uint4& w, float
     o[j] = AsU32(__hmul2_rn(__floats2half2_rn(f.x * inv, f.y * inv), AsHalf2(ww[j])));
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
-// Output and the rewritten residual are not read again by this kernel: stream them past L1.
-__device__ __forceinline__ void StgStream16(void* p, uint4 v) {
-  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
-template <int CPL, bool kResidual>
-__global__ void __launch_bounds__(256)
-RmsNormWarpKernel(half* __restrict__ out, half* __restrict__ residual, const half* __restrict__ input,
-                  const half* __restrict__ weight, int num_tokens, int hidden, float eps) {
-  const int warps_per_block = blockDim.x >> 5;
-  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  if (row >= num_tokens) return;
-  const int lane = threadIdx.x & 31;
-  const int chunks = hidden >> 3;
-  const size_t base = static_cast<size_t>(row) * hidden;
-
-  uint4 hv[CPL];
-  float part[CPL];
-#pragma unroll
-  for (int i = 0; i < CPL; ++i) {
-    const int c = i * 32 + lane;
-    part[i] = 0.0f;
-    if (c < chunks) {
-      uint4 x = LdgStream16(input + base + c * 8);
-      if (kResidual) {
-        x = AddChunk(Ldg16(residual + base + c * 8), x);
-        StgStream16(residual + base + c * 8, x);
-      }
-      hv[i] = x;
-      part[i] = ChunkSumSq(x);
-    }
-  }
-  float ss = 0.0f;
-#pragma unroll
-  for (int i = 0; i < CPL; ++i) ss += WarpTreeSum(part[i]);
-  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
-#pragma unroll
-  for (int i = 0; i < CPL; ++i) {
-    const int c = i * 32 + lane;
-    if (c < chunks) StgStream16(out + base + c * 8, NormChunk(hv[i], Ldg16(weight + c * 8), inv));
-  }
 }
 
 // One CTA of 32*CPL threads per row, one chunk per thread (thread = 32*i + lane).
@@ -192,19 +147,11 @@ int Launch(half* out, half* residual, const half* input, const half* weight, int
                                                                    hidden, eps);
     return LaunchStatus("rmsnorm (scalar)");
   }
-  const int sms = CurrentDeviceFacts().sm_count;
   const int cpl = (hidden / 8 + 31) / 32;
-  const bool few_rows = num_tokens <= 8 * sms;  // below that a warp per row leaves SMs idle
-  const int wpb = 8;
-  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
-#define RL_NORM_CASE(N)                                                                             \
-  case N:                                                                                           \
-    if (few_rows)                                                                                   \
-      LaunchOverlapped(RmsNormBlockKernel<N, kResidual>, dim3(num_tokens), dim3(32 * N), 0, stream, \
-                       out, residual, input, weight, hidden, eps);                                  \
-    else                                                                                            \
-      RmsNormWarpKernel<N, kResidual><<<grid, block, 0, stream>>>(out, residual, input, weight,     \
-                                                                  num_tokens, hidden, eps);         \
+#define RL_NORM_CASE(N)                                                                           \
+  case N:                                                                                         \
+    LaunchOverlapped(RmsNormBlockKernel<N, kResidual>, dim3(num_tokens), dim3(32 * N), 0, stream, \
+                     out, residual, input, weight, hidden, eps);                                  \
     break;
   switch (cpl) {
     RL_NORM_CASE(1) RL_NORM_CASE(2) RL_NORM_CASE(3) RL_NORM_CASE(4) RL_NORM_CASE(5)
