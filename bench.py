@@ -387,8 +387,32 @@ def kernel_table(peak, only=None, eager=False):
         pos, tab = dev(c["positions"]), dev(c["tables"])
         pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
         secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pool, tab, tab.shape[1], pos, 64, 12, 2, 128, 1e6), 8)
-        report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1024 + 64 * 8 + 256, "config 2 in one launch; latency-bound")
+        report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1536 + 64 * 8 + 256, "config 2 in one launch; latency-bound")
         del pool, qkv
+    # the same three kernels at a prompt chunk's size: 16384 consecutive positions of one sequence (one table
+    # row shared by every token, row stride 0, as prompt ingestion calls them), buffers rotated past L2
+    big = ("rope_T16384", "kv_scatter_T16384", "rope_kv_scatter_fused_T16384")
+    if any(want(n) for n in big):
+        t, nbuf = 16384, 10
+        src = wl.normal_half(0x2B1, 64 * 2048).reshape(64, 2048)
+        qkv = [dev(np.tile(src, (t // 64, 1))) for _ in range(nbuf)]
+        pos = torch.arange(t, dtype=torch.int32, device="cuda")
+        row = dev((wl.permutation(0x2B2, 2047)[:t // 16] + 1).astype(np.int32).reshape(1, -1))
+        pools = [torch.zeros(2048 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
+        rope_bytes = 2 * t * 1792 * 2 + t * 4
+        if want(big[0]):
+            secs = timed(lambda i: K.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, t, 12, 2, 128, 1e6,
+                                                         k_offset=1536), nbuf, iters=5)
+            report(big[0], secs, rope_bytes, "prompt chunk, cold L2")
+        if want(big[1]):
+            secs = timed(lambda i: K.launch_kv_scatter(pools[i], qkv[i], qkv[i], 2048, 2048, row, 0, pos, t,
+                                                       2, 128, k_offset=1536, v_offset=1792), nbuf, iters=5)
+            report(big[1], secs, 2 * t * 1024 + t * 4 + t // 4, "prompt chunk, cold L2; strided 1 KiB reads")
+        if want(big[2]):
+            secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pools[i], row, 0, pos, t, 12, 2, 128, 1e6),
+                         nbuf, iters=5)
+            report(big[2], secs, rope_bytes + t * 1536 + t // 4, "prompt chunk in one launch, cold L2")
+        del qkv, pools
     # the four linear layers of a decoder block at 64 token rows: weight streams (28 distinct weights, cold L2)
     for name, (n_out, k_in, epi, with_bias) in (("decode_linear_qkv_T64", (2048, 1536, 0, True)),
                                                  ("decode_linear_o_T64", (1536, 1536, 0, False)),

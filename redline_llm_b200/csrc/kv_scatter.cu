@@ -27,22 +27,37 @@ KvScatterKernel(half* __restrict__ pool, const half* __restrict__ k, const half*
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= num_tokens) return;
   const int lane = threadIdx.x & 31;
+  const int words_per_head = head_dim / kPer;
+  const int words_per_side = num_kv_heads * words_per_head;
+  const int words = 2 * words_per_side;
+  const Word* ksrc = reinterpret_cast<const Word*>(k + t * k_row_stride);
+  const Word* vsrc = reinterpret_cast<const Word*>(v + t * v_row_stride);
+  // the token's first kAhead words per lane (all of them for 2 heads x 128 in 16-byte words) are requested
+  // before the position and the table entry, which only the destination depends on
+  constexpr int kAhead = 2;
+  Word held[kAhead];
+#pragma unroll
+  for (int j = 0; j < kAhead; ++j) {
+    const int w = lane + 32 * j;
+    if (w < words) held[j] = w >= words_per_side ? vsrc[w - words_per_side] : ksrc[w];
+  }
   const int p = positions[t];
   const int64_t block = tables[t * table_row_stride + (p >> kKvBlockShift)];
   const int slot = p & (kKvBlock - 1);
-
-  const int words_per_head = head_dim / kPer;
-  const int words_per_side = num_kv_heads * words_per_head;
-  const Word* ksrc = reinterpret_cast<const Word*>(k + t * k_row_stride);
-  const Word* vsrc = reinterpret_cast<const Word*>(v + t * v_row_stride);
-  for (int w = lane; w < 2 * words_per_side; w += 32) {
+  auto cell = [&](int w) {
     const int kv = w >= words_per_side;
     const int r = w - kv * words_per_side;
     const int h = r / words_per_head;
-    const int dw = r - h * words_per_head;
-    const int64_t row = (((block * 2 + kv) * num_kv_heads + h) * kKvBlock + slot) *
-                        static_cast<int64_t>(head_dim);
-    reinterpret_cast<Word*>(pool + row)[dw] = (kv ? vsrc : ksrc)[r];
+    const int64_t row = (((block * 2 + kv) * num_kv_heads + h) * kKvBlock + slot) * static_cast<int64_t>(head_dim);
+    return reinterpret_cast<Word*>(pool + row) + (r - h * words_per_head);
+  };
+#pragma unroll
+  for (int j = 0; j < kAhead; ++j) {
+    const int w = lane + 32 * j;
+    if (w < words) *cell(w) = held[j];
+  }
+  for (int w = lane + 32 * kAhead; w < words; w += 32) {
+    *cell(w) = w >= words_per_side ? vsrc[w - words_per_side] : ksrc[w];
   }
 }
 

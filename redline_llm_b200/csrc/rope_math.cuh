@@ -24,7 +24,7 @@ const InvFreq& RopeTableFor(float theta, int head_dim);
 // Two rotation pairs at once: lo holds elements (d, d+1), hi holds (d + head_dim/2, d+1 + head_dim/2).
 __device__ __forceinline__ void RotateWord(uint32_t& lo, uint32_t& hi, half2 c, half2 s) {
   const half2 x1 = AsHalf2(lo), x2 = AsHalf2(hi);
-  const half2 a = __hadd2_rn(__hmul2_rn(x1, c), __hmul2_rn(__hneg2(x2), s));
+  const half2 a = __hsub2_rn(__hmul2_rn(x1, c), __hmul2_rn(x2, s));  // == x1*c + (-x2)*s, bit for bit
   const half2 b = __hadd2_rn(__hmul2_rn(x2, c), __hmul2_rn(x1, s));
   lo = AsU32(a);
   hi = AsU32(b);

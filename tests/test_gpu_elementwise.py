@@ -213,6 +213,24 @@ def test_rope_position_zero_is_identity_and_long_positions(own):
     rope_gate(q, own.rope(q_in, pos, 12, 128, 1e6, f32=True), q_in, "long positions")
 
 
+def test_rope_prompt_sized_batch_equals_decode_sized_launches(own):
+    """Thousands of rows take the several-rows-per-block mapping; the same rows fed 64 at a time take the
+    one-row mapping. Both must give the same bits (odd row count: the last block is ragged), and a sample
+    of rows is checked against the CPU rotation."""
+    t = 2401
+    q_in = wl.normal_half(0x2E1, t * 1536).reshape(t, 1536)
+    k_in = wl.normal_half(0x2E2, t * 256).reshape(t, 256)
+    pos = wl.randint(0x2E3, t, 0, 32767)
+    q, k = run_rope(q_in, k_in, pos, 1e6, True)
+    for lo in range(0, t, 64):
+        hi = min(t, lo + 64)
+        q1, k1 = run_rope(q_in[lo:hi], k_in[lo:hi], pos[lo:hi], 1e6, True)
+        assert np.array_equal(q[lo:hi], q1) and np.array_equal(k[lo:hi], k1), (lo, hi)
+    rows = np.r_[0:8, 1196:1204, 2393:2401]
+    exact = rope_gate(q[rows], own.rope(q_in[rows], pos[rows], 12, 128, 1e6, f32=True), q_in[rows], "prompt-sized")
+    assert exact > 0.999
+
+
 def test_rope_odd_head_dim_takes_scalar_path(own):
     t, qh, kh, hd = 3, 3, 1, 20
     q_in = wl.uniform_half(17, t * qh * hd, -1.0, 1.0).reshape(t, qh * hd)
@@ -369,9 +387,12 @@ def test_silu_extremes_and_config4_largest(own):
 
 # ------------------------------------------------------- RoPE + scatter fused
 
-@pytest.mark.parametrize("tokens,stride_mode", [(64, "decode"), (7, "decode"), (33, "prefill")])
+@pytest.mark.parametrize("tokens,stride_mode", [(64, "decode"), (7, "decode"), (33, "prefill"), (2401, "prefill")])
 def test_fused_rope_scatter_equals_the_two_launchers_bit_for_bit(own, tokens, stride_mode):
-    c = wl.config_rope_scatter(tokens=tokens, num_blocks=1024)
+    # 2401 rows: the several-rows-per-block mappings of all three kernels, with a ragged last block
+    c = wl.config_rope_scatter(tokens=min(tokens, 64), num_blocks=1024)
+    if tokens > 64:
+        c["qkv"] = wl.normal_half(0x2E4, tokens * 2048).reshape(tokens, 2048)
     tables = c["tables"] % 1024
     tables[tables == 0] = 1
     pos = c["positions"]
