@@ -14,7 +14,7 @@
 namespace rl {
 namespace {
 
-template <typename Word>
+template <typename Word, int kTokens>
 __global__ void __launch_bounds__(128)
 KvScatterKernel(half* __restrict__ pool, const half* __restrict__ k, const half* __restrict__ v,
                 int64_t k_row_stride, int64_t v_row_stride, const int32_t* __restrict__ tables,
@@ -24,40 +24,57 @@ KvScatterKernel(half* __restrict__ pool, const half* __restrict__ k, const half*
   // the attention launch that follows may begin its table walk now (it waits for this grid to
   // complete before it reads the pool)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= num_tokens) return;
+  const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kTokens;
+  if (t0 >= num_tokens) return;
+  const int tokens = static_cast<int>(min(static_cast<int64_t>(kTokens), num_tokens - t0));
   const int lane = threadIdx.x & 31;
   const int words_per_head = head_dim / kPer;
   const int words_per_side = num_kv_heads * words_per_head;
   const int words = 2 * words_per_side;
-  const Word* ksrc = reinterpret_cast<const Word*>(k + t * k_row_stride);
-  const Word* vsrc = reinterpret_cast<const Word*>(v + t * v_row_stride);
-  // the token's first kAhead words per lane (all of them for 2 heads x 128 in 16-byte words) are requested
-  // before the position and the table entry, which only the destination depends on
-  constexpr int kAhead = 2;
-  Word held[kAhead];
-#pragma unroll
-  for (int j = 0; j < kAhead; ++j) {
-    const int w = lane + 32 * j;
-    if (w < words) held[j] = w >= words_per_side ? vsrc[w - words_per_side] : ksrc[w];
-  }
-  const int p = positions[t];
-  const int64_t block = tables[t * table_row_stride + (p >> kKvBlockShift)];
-  const int slot = p & (kKvBlock - 1);
-  auto cell = [&](int w) {
-    const int kv = w >= words_per_side;
-    const int r = w - kv * words_per_side;
-    const int h = r / words_per_head;
-    const int64_t row = (((block * 2 + kv) * num_kv_heads + h) * kKvBlock + slot) * static_cast<int64_t>(head_dim);
-    return reinterpret_cast<Word*>(pool + row) + (r - h * words_per_head);
+  const int64_t slot_elems = head_dim;                                  // one token of one head
+  const int64_t page_elems = 2 * num_kv_heads * kKvBlock * slot_elems;  // [2][heads][16][head_dim]
+  // word w of a token: where it is read (K row or V row) and where it lands inside (page, slot 0)
+  auto src_of = [&](int w, int64_t t) {
+    return w >= words_per_side ? reinterpret_cast<const Word*>(v + t * v_row_stride) + (w - words_per_side)
+                               : reinterpret_cast<const Word*>(k + t * k_row_stride) + w;
   };
+  auto dst_of = [&](int w) {
+    const int side_head = w / words_per_head;  // kv * heads + h
+    return side_head * kKvBlock * slot_elems + (w - side_head * words_per_head) * kPer;
+  };
+  // a token's first kAhead words per lane (all of them for 2 heads x 128 in 16-byte words) are requested,
+  // for every token of the warp, before the positions and table entries that only the destinations need
+  constexpr int kAhead = 2;
+  Word held[kTokens][kAhead];
+  int64_t dst[kAhead];
 #pragma unroll
   for (int j = 0; j < kAhead; ++j) {
     const int w = lane + 32 * j;
-    if (w < words) *cell(w) = held[j];
+    if (w < words) {
+#pragma unroll
+      for (int i = 0; i < kTokens; ++i) {
+        if (i < tokens) held[i][j] = *src_of(w, t0 + i);
+      }
+    }
   }
-  for (int w = lane + 32 * kAhead; w < words; w += 32) {
-    *cell(w) = w >= words_per_side ? vsrc[w - words_per_side] : ksrc[w];
+#pragma unroll
+  for (int j = 0; j < kAhead; ++j) {
+    if (lane + 32 * j < words) dst[j] = dst_of(lane + 32 * j);
+  }
+#pragma unroll
+  for (int i = 0; i < kTokens; ++i) {
+    if (i >= tokens) break;
+    const int64_t t = t0 + i;
+    const int p = positions[t];
+    const int64_t block = tables[t * table_row_stride + (p >> kKvBlockShift)];
+    half* cell = pool + block * page_elems + (p & (kKvBlock - 1)) * slot_elems;
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      if (lane + 32 * j < words) *reinterpret_cast<Word*>(cell + dst[j]) = held[i][j];
+    }
+    for (int w = lane + 32 * kAhead; w < words; w += 32) {
+      *reinterpret_cast<Word*>(cell + dst_of(w)) = *src_of(w, t);
+    }
   }
 }
 
@@ -74,21 +91,24 @@ extern "C" int rl_launch_kv_scatter(void* kv_pool_layer, const void* k, const vo
   if (!kv_pool_layer || !k || !v || !block_tables || !positions)
     return Fail(RL_E_NULL_POINTER, "kv_scatter: null device pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int wpb = num_tokens >= 4 * CurrentDeviceFacts().sm_count ? 4 : 1;
-  const dim3 grid((num_tokens + wpb - 1) / wpb), block(32 * wpb);
   half* pool = static_cast<half*>(kv_pool_layer);
   const half* kk = static_cast<const half*>(k);
   const half* vv = static_cast<const half*>(v);
   const bool vec = head_dim % 8 == 0 && k_row_stride % 8 == 0 && v_row_stride % 8 == 0 &&
                    Aligned16(pool) && Aligned16(k) && Aligned16(v);
-  if (vec) {
-    KvScatterKernel<uint4><<<grid, block, 0, s>>>(pool, kk, vv, k_row_stride, v_row_stride,
-                                                  block_tables, block_table_row_stride, positions,
-                                                  num_tokens, num_kv_heads, head_dim);
-  } else {
-    KvScatterKernel<half><<<grid, block, 0, s>>>(pool, kk, vv, k_row_stride, v_row_stride,
-                                                 block_tables, block_table_row_stride, positions,
-                                                 num_tokens, num_kv_heads, head_dim);
-  }
+  // decode batches: a warp per token, a block per token; prompt chunks: four warps per block, and once
+  // that still fills the device several times over, two tokens per warp
+  const int sms = CurrentDeviceFacts().sm_count;
+  const int wpb = num_tokens >= 4 * sms ? 4 : 1;
+  const int tpw = num_tokens >= 64 * sms ? 2 : 1;
+  const dim3 grid((num_tokens + wpb * tpw - 1) / (wpb * tpw)), block(32 * wpb);
+  auto launch = [&](auto kernel) {
+    kernel<<<grid, block, 0, s>>>(pool, kk, vv, k_row_stride, v_row_stride, block_tables, block_table_row_stride,
+                                  positions, num_tokens, num_kv_heads, head_dim);
+  };
+  if (vec && tpw == 2) launch(KvScatterKernel<uint4, 2>);
+  else if (vec) launch(KvScatterKernel<uint4, 1>);
+  else if (tpw == 2) launch(KvScatterKernel<half, 2>);
+  else launch(KvScatterKernel<half, 1>);
   return LaunchStatus("kv_scatter");
 }

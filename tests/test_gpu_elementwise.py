@@ -286,6 +286,17 @@ def test_scatter_prefill_mode_shares_one_row(own):
     scatter_case(own, tokens, np.arange(tokens, dtype=np.int32), row, 0, k, v, 256, 256, 48)
 
 
+@pytest.mark.parametrize("tokens", [2401, 9601])
+def test_scatter_prompt_chunks_take_the_wide_mappings(own, tokens):
+    """2401 tokens: four warps per block; 9601: also two tokens per warp. Both counts are odd, so the last
+    block and the last warp are ragged."""
+    k = wl.uniform_half(35, tokens * 256, -1.0, 1.0).reshape(tokens, 256)
+    v = wl.uniform_half(36, tokens * 256, -1.0, 1.0).reshape(tokens, 256)
+    blocks = -(-tokens // 16)
+    row = (wl.permutation(37, 700)[:blocks] + 1).astype(np.int32).reshape(1, blocks)
+    scatter_case(own, tokens, np.arange(tokens, dtype=np.int32), row, 0, k, v, 256, 256, 704)
+
+
 def test_scatter_padded_row_lands_in_block_zero_and_boundaries(own):
     pos = np.array([0, 15, 16, 17, 31, 32, 0], np.int32)  # last row = padded slot (position 0, dummy table)
     tables = np.array([[3, 4, 5]] * 6 + [[0, 0, 0]], np.int32)
