@@ -413,6 +413,28 @@ def kernel_table(peak, only=None, eager=False):
                          nbuf, iters=5)
             report(big[2], secs, rope_bytes + t * 1536 + t // 4, "prompt chunk in one launch, cold L2")
         del qkv, pools
+    # the two prompt-side launchers at one chunk of a long prompt: the gather of a 16384-token context into
+    # the dense staging views, and the causal softmax of a 512-row chunk against 8192 keys
+    if want("kv_gather_ctx16384"):
+        ctx, nbuf = 16384, 10
+        row = dev((wl.permutation(0x2B3, 2047)[:ctx // 16] + 1).astype(np.int32))
+        pools = [dev(wl.normal_half(0x2B4 + (i & 1), 2048 * 2 * 2 * 16 * 128)) for i in range(nbuf)]
+        kh = [torch.empty(2, ctx, 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
+        vh = [torch.empty(2, ctx, 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
+        secs = timed(lambda i: K.launch_kv_gather(kh[i], vh[i], ctx * 128, 128, ctx * 128, 128, pools[i], row, ctx,
+                                                  2, 128), nbuf, iters=5)
+        report("kv_gather_ctx16384", secs, 2 * ctx * 1024 + ctx // 4, "one sequence's pages into dense K, V; cold L2")
+        del pools, kh, vh
+    if want("prefill_softmax_12x512x8192"):
+        h, c, kv, start, nbuf = 12, 512, 8192, 7680, 2
+        sc = [torch.randn(h, c, kv, dtype=torch.float32, device="cuda",
+                          generator=torch.Generator("cuda").manual_seed(0x2B6 + i)) * 2.5 for i in range(nbuf)]
+        pr = [torch.empty(h, c, kv, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
+        secs = timed(lambda i: K.launch_prefill_softmax(pr[i], sc[i], h, c, kv, start), nbuf, iters=5)
+        live = sum(min(start + r + 1, kv) for r in range(c))
+        report("prefill_softmax_12x512x8192", secs, h * (live * 4 + c * kv * 2),
+               "chunk rows 7680..8191 against 8192 keys: live FP32 scores read once, FP16 probabilities written")
+        del sc, pr
     # the four linear layers of a decoder block at 64 token rows: weight streams (28 distinct weights, cold L2)
     for name, (n_out, k_in, epi, with_bias) in (("decode_linear_qkv_T64", (2048, 1536, 0, True)),
                                                  ("decode_linear_o_T64", (1536, 1536, 0, False)),

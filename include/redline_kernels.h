@@ -203,7 +203,9 @@ int rl_launch_kv_gather(void* khat, void* vhat, int64_t khat_head_stride, int64_
                         int32_t head_dim, void* stream);
 
 /* Prefill-only: causal row softmax FP32 -> FP16 over dense [heads, chunk_len, kv_len]; row i sees
- * keys j <= chunk_start + i; masked entries become exact +0 and are never read. Replaces
+ * keys j <= chunk_start + i; masked entries become exact +0 and their scores are select-masked: whatever
+ * they hold (NaN included) reaches no result; at most the rest of the 32-byte group that holds the last
+ * live score is loaded, and discarded. Replaces
  * LaunchPrefillSoftmax, src/kernels/kernels.cuh:185-187 (src/kernels/prefill_attention.cu:166-192). */
 int rl_launch_prefill_softmax(void* probs, const float* scores, int32_t num_q_heads, int32_t chunk_len,
                               int32_t kv_len, int32_t chunk_start, void* stream);

@@ -9,8 +9,9 @@
 // LaunchPrefillSoftmax (src/kernels/kernels.cuh:160-187, src/kernels/prefill_attention.cu:103-162):
 // causal row softmax FP32 -> FP16 over [heads, chunk_len, kv_len]; query row i sits at position
 // chunk_start + i and sees keys j <= it; FP32 max and sum, one FP16 rounding of exp(s - max) / sum;
-// masked entries are written as exact +0 and their scores are never read. One CTA per (row, head),
-// three passes over the row (it stays in L1/L2), fixed reduction trees (run-to-run identical bits).
+// masked entries are written as exact +0 and their scores never reach a result. One CTA per (row, head);
+// rows of up to 32768 keys are read once and kept in registers, longer or unaligned ones take three
+// passes over the row (it stays in L2); fixed reduction trees either way (run-to-run identical bits).
 #include "common.cuh"
 
 #if defined(__USE_FAST_MATH__)
@@ -48,6 +49,7 @@ KvGatherKernel(half* __restrict__ khat, half* __restrict__ vhat, int64_t khat_he
 
 constexpr int kSoftmaxThreads = 256;
 
+template <int kThreads>
 __device__ __forceinline__ float BlockReduce(float v, bool is_max, float* scratch) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -58,9 +60,80 @@ __device__ __forceinline__ float BlockReduce(float v, bool is_max, float* scratc
   __syncthreads();
   float r = scratch[0];
 #pragma unroll
-  for (int w = 1; w < kSoftmaxThreads / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  for (int w = 1; w < kThreads / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
   __syncthreads();  // scratch is reused by the next reduction
   return r;
+}
+
+// Rows of up to kThreads * kChunks * 8 scores with kv_len a multiple of 8 and 16-byte aligned bases: the
+// live part of the row is read once, 8 consecutive scores per thread and step, and stays in registers
+// through the max, the exponentials (evaluated once), the sum and the division. Elements of a 32-byte
+// group that lie beyond the causal limit are loaded with the group but replaced by -inf before any use,
+// so their exponential is exactly 0 and so is their probability.
+template <int kThreads, int kChunks>
+__global__ void __launch_bounds__(kThreads)
+PrefillSoftmaxRowKernel(half* __restrict__ probs, const float* __restrict__ scores, int chunk_len, int kv_len,
+                        int chunk_start) {
+  __shared__ float scratch[kThreads / 32];
+  const int row = blockIdx.x, head = blockIdx.y;
+  const size_t base = (static_cast<size_t>(head) * chunk_len + row) * static_cast<size_t>(kv_len);
+  const float* s = scores + base;
+  half* p = probs + base;
+  const int live = min(chunk_start + row + 1, kv_len);
+  float x[kChunks][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int j0 = (c * kThreads + threadIdx.x) << 3;
+    if (j0 < live) {
+      const uint4 a = LdgStream16(s + j0), b = LdgStream16(s + j0 + 4);
+      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      if (j0 + 8 <= live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[c][e] = __uint_as_float(w[e]);
+      } else {  // the one group of the row that straddles the causal limit
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[c][e] = j0 + e < live ? __uint_as_float(w[e]) : -INFINITY;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx = fmaxf(mx, x[c][e]);
+    }
+  }
+  mx = BlockReduce<kThreads>(mx, true, scratch);
+  float sum = 0.0f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int j0 = (c * kThreads + threadIdx.x) << 3;
+    if (j0 < live) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        x[c][e] = expf(x[c][e] - mx);  // exactly 0 for the replaced elements
+        sum += x[c][e];
+      }
+    }
+  }
+  sum = BlockReduce<kThreads>(sum, false, scratch);
+  // e / sum for every element of the row: the reciprocal once, then per element the product and one
+  // residual correction, which is the IEEE quotient whenever it is large enough to survive the FP16
+  // rounding that follows (sum lies in [1, kv_len] and e in [0, 1])
+  const float rcp = __frcp_rn(sum);
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int j0 = (c * kThreads + threadIdx.x) << 3;
+    if (j0 >= kv_len) continue;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (j0 < live) {
+      uint32_t* o = &out.x;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float q0 = x[c][2 * e] * rcp, q1 = x[c][2 * e + 1] * rcp;
+        q0 = fmaf(fmaf(-q0, sum, x[c][2 * e]), rcp, q0);
+        q1 = fmaf(fmaf(-q1, sum, x[c][2 * e + 1]), rcp, q1);
+        o[e] = AsU32(__floats2half2_rn(q0, q1));  // replaced elements hold e = 0 and give exact +0
+      }
+    }
+    Stg16(p + j0, out);
+  }
 }
 
 __global__ void __launch_bounds__(kSoftmaxThreads)
@@ -74,10 +147,10 @@ PrefillSoftmaxKernel(half* __restrict__ probs, const float* __restrict__ scores,
   const int live = min(chunk_start + row + 1, kv_len);
   float mx = -INFINITY;
   for (int j = threadIdx.x; j < live; j += kSoftmaxThreads) mx = fmaxf(mx, s[j]);
-  mx = BlockReduce(mx, true, scratch);
+  mx = BlockReduce<kSoftmaxThreads>(mx, true, scratch);
   float sum = 0.0f;
   for (int j = threadIdx.x; j < live; j += kSoftmaxThreads) sum += expf(s[j] - mx);
-  sum = BlockReduce(sum, false, scratch);
+  sum = BlockReduce<kSoftmaxThreads>(sum, false, scratch);
   for (int j = threadIdx.x; j < kv_len; j += kSoftmaxThreads)
     p[j] = j < live ? __float2half_rn(expf(s[j] - mx) / sum) : __ushort_as_half(0);
 }
@@ -118,7 +191,22 @@ extern "C" int rl_launch_prefill_softmax(void* probs, const float* scores, int32
   if (!probs || !scores) return Fail(RL_E_NULL_POINTER, "prefill_softmax: null device pointer");
   if (chunk_start < 0) return Fail(RL_E_BAD_SHAPE, "prefill_softmax: negative chunk_start");
   if (num_q_heads > 65535) return Fail(RL_E_TOO_LARGE, "prefill_softmax: more than 65535 heads");
-  PrefillSoftmaxKernel<<<dim3(chunk_len, num_q_heads), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<half*>(probs), scores, chunk_len, kv_len, chunk_start);
+  const dim3 grid(chunk_len, num_q_heads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  half* out = static_cast<half*>(probs);
+  const bool vec = kv_len % 8 == 0 && Aligned16(probs) && Aligned16(scores);
+  if (vec && kv_len <= 256 * 1 * 8) {
+    PrefillSoftmaxRowKernel<256, 1><<<grid, 256, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  } else if (vec && kv_len <= 256 * 2 * 8) {
+    PrefillSoftmaxRowKernel<256, 2><<<grid, 256, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  } else if (vec && kv_len <= 256 * 4 * 8) {
+    PrefillSoftmaxRowKernel<256, 4><<<grid, 256, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  } else if (vec && kv_len <= 1024 * 2 * 8) {
+    PrefillSoftmaxRowKernel<1024, 2><<<grid, 1024, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  } else if (vec && kv_len <= 1024 * 4 * 8) {
+    PrefillSoftmaxRowKernel<1024, 4><<<grid, 1024, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  } else {  // odd lengths, unaligned bases, rows beyond 32768 keys: three passes over the row
+    PrefillSoftmaxKernel<<<grid, kSoftmaxThreads, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
+  }
   return LaunchStatus("prefill_softmax");
 }

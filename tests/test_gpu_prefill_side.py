@@ -62,7 +62,11 @@ def run_softmax(scores, chunk_start):
     return host(d_p)
 
 
-@pytest.mark.parametrize("h,c,kv,start", [(12, 8, 8, 0), (12, 17, 300, 283), (2, 1, 1, 0), (3, 64, 2049, 1985), (12, 5, 33000, 32995)])
+# the last six shapes take the read-once kernel's five tiers (kv_len a multiple of 8, up to 32768 keys), one
+# of them with the causal limit in the middle of the row; the others take the three-pass kernel
+@pytest.mark.parametrize("h,c,kv,start", [(12, 8, 8, 0), (12, 17, 300, 283), (2, 1, 1, 0), (3, 64, 2049, 1985), (12, 5, 33000, 32995),
+                                          (4, 9, 2048, 2039), (3, 21, 2056, 997), (2, 5, 4096, 4091), (2, 3, 8192, 8189),
+                                          (2, 3, 16384, 16381), (1, 2, 32768, 32766)])
 def test_prefill_softmax_against_fp64_with_poisoned_masked_region(own, h, c, kv, start):
     rng = np.random.default_rng(h * 1000 + c)
     sc = rng.normal(0, 2.5, (h, c, kv)).astype(np.float32)
