@@ -206,10 +206,11 @@ class DecodeStepWorkload:
     TOTAL, LONG, WAVE, NEW = 512, 32, 64, 256
 
     def __init__(self, rank: int, world: int, new_tokens: int = 256, total: int = 512, overlap: bool = True,
-                 linear: str = "tcgen05"):
+                 linear: str = "tcgen05", vocab_projection: str = None):
         import torch
         self.TOTAL, self.LONG = total, total // 16
         self.linear = linear
+        self.vocab_projection = vocab_projection or "library"
         from redline_llm_b200.engine import (Engine, ModelConfig, ModelWeights, balanced_order, blocks_for_tokens,
                                              shard_requests)
         self.torch = torch
@@ -230,7 +231,8 @@ class DecodeStepWorkload:
             blocks = sum(blocks_for_tokens(c + new_tokens) for c in wave) + 8
             gb = blocks * self.cfg.block_bytes() / (1 << 30)
             e = Engine(kv_pool_gb=gb, max_batch=self.WAVE, max_seq_len=max_seq, config=self.cfg, weights=self.weights,
-                       device=dev.index, graph_buckets=[64], prologue_overlap=overlap, decode_linear=linear)
+                       device=dev.index, graph_buckets=[64], prologue_overlap=overlap, decode_linear=linear,
+                       vocab_projection=self.vocab_projection)
             for j, c in enumerate(wave):
                 e.add_synthetic_request(c, new_tokens, seed=wl.SEED_STEP + 1000 * rank + w0 + j)
             self.engines.append(e)
@@ -242,7 +244,9 @@ class DecodeStepWorkload:
         self.kv_bytes_per_token = self.cfg.layers * 2 * self.cfg.kv_heads * self.cfg.head_dim * 2
         # own kernels per layer: 2 norms and attention, plus RoPE+scatter and SiLU beside library GEMMs, or the
         # four linear layers (RoPE+scatter fused into the QKV product, SiLU into gate/up); + embed, final norm, argmax
-        self.launches_per_step = len(self.engines) * (self.cfg.layers * (7 if linear == "tcgen05" else 5) + 3)
+        # and, with the own linear kernel, the vocabulary projection
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * (7 if linear == "tcgen05" else 5) + 3
+                                                      + (1 if self.vocab_projection == "tcgen05" else 0))
         self.h2d = self.d2h = 0
 
     def step(self):  # inputs already resident: graph replays only
@@ -597,7 +601,7 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     from redline_llm_b200 import kernels as K
     need = args.warmup + args.steps + 8
     w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences, overlap=not args.no_overlap,
-                           linear=args.linear)
+                           linear=args.linear, vocab_projection=args.vocab_projection)
     peak, peak_kind = measured_peaks()
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
@@ -633,9 +637,10 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                    "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
                    "router": "host-side: longest first, snake-dealt over 8 shards (every GPU serves 32/N of the "
                              "32768-token sequences and the same number of cached tokens within 1 %)",
-                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter fused into QKV, SiLU into gate/up), "
-                            "library GEMM for the vocabulary projection, FP16" if args.linear == "tcgen05"
-                            else "library (cuBLAS via torch.matmul), FP16"),
+                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter fused into QKV, SiLU into gate/up) "
+                            "FP16" if args.linear == "tcgen05" else "library (cuBLAS via torch.matmul), FP16"),
+                   "vocabulary_projection": ("own tcgen05 kernel" if w.vocab_projection == "tcgen05"
+                                             else "library GEMM (torch.matmul)"),
                    "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
                    "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2),
                    "step_hbm_bytes_per_gpu": int(step_bytes), "step_GBps_per_gpu": round(step_gbs, 1),
@@ -694,6 +699,8 @@ def main():
                     help="decode_step workload: sequences in the job (512 = the configuration; fewer for profiling)")
     ap.add_argument("--linear", choices=["tcgen05", "library"], default="tcgen05",
                     help="decode_step: linear layers by this library's tcgen05 kernel (default) or by the library GEMM")
+    ap.add_argument("--vocab-projection", choices=["tcgen05", "library"], default=None,
+                    help="decode_step: the vocabulary projection by this library's kernel or by the library GEMM (default)")
     ap.add_argument("--linear-stages", type=int, default=None, help="ring depth of the tcgen05 linear kernel (2..8)")
     ap.add_argument("--linear-splits", type=int, default=None, help="largest K split of the tcgen05 linear kernel (1,2,4,8)")
     ap.add_argument("--no-overlap", action="store_true",

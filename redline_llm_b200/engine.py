@@ -9,7 +9,7 @@ bucket (src/core/model_executor.cpp:523-633,721-782). The decode layer sequence 
 (src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library; the four
 linear layers of a block are this library's tcgen05 weight-streaming kernel (SiLU-mul fused into the
 gate/up product) or, with decode_linear="library", library GEMMs as in the reference (torch.matmul ->
-cuBLAS); the vocabulary projection is always a library GEMM; the embedding gather and the greedy
+cuBLAS); the vocabulary projection is a library GEMM unless vocab_projection="tcgen05"; the embedding gather and the greedy
 argmax at the two ends of the step are this library's too.
 
 One Engine drives one GPU; multi-GPU serving is one Engine per GPU with requests sharded on the
@@ -304,8 +304,11 @@ class ModelExecutor:
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
         # Linear layers of the decode step: "tcgen05" = this library's weight-streaming kernel (with the
         # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
-        # The vocabulary projection always stays with the library.
+        # The vocabulary projection has its own switch of the same two values. Alone, this library's kernel runs
+        # it in 79.0 us against the library GEMM's 82.1 (64 x 151936 x 1536); inside the captured step the library
+        # GEMM came out 24 us per step ahead (21.22k against 21.06k tok/s, two runs each), so it is the default.
         self.decode_linear = "tcgen05"
+        self.vocab_projection = "library"
         self.fuse_qkv_rope = True      # RoPE + KV scatter in the QKV product's epilogue (tcgen05 path only)
         self.act = torch.zeros(B, cfg.inter, dtype=f16, device=device)         # silu(gate) * up
         K.init(device.index if device.index is not None else -1)
@@ -364,7 +367,10 @@ class ModelExecutor:
                 K.launch_silu_mul(gu, gu, rows, cfg.inter)
                 torch.matmul(gu[:, :cfg.inter], L["down"].t(), out=mlp)
         K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, rows, cfg.hidden, cfg.eps)
-        torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
+        if self.vocab_projection == "tcgen05":
+            K.launch_decode_linear(self.logits[:rows], normed, w.lm_head, num_tokens=rows)
+        else:
+            torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
         K.launch_greedy_argmax(self.tokens, self.logits, rows, cfg.vocab)
 
     def warm_and_capture(self, buckets: Sequence[int]) -> None:
@@ -528,7 +534,7 @@ class Engine:
                  debug_dump_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
                  device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
                  graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True,
-                 decode_linear: str = "tcgen05"):
+                 decode_linear: str = "tcgen05", vocab_projection: Optional[str] = None):
         import torch
         if admission_policy != "reserve_full":
             raise ValueError("only the reserve_full admission policy is provided")
@@ -553,6 +559,7 @@ class Engine:
             raise ValueError("decode_linear must be 'tcgen05' or 'library'")
         self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
         self.exec.decode_linear = decode_linear
+        self.exec.vocab_projection = vocab_projection or "library"
         self.max_seq_len, self.max_batch = max_seq_len, max_batch
         self.pad_eager_to_bucket = pad_eager_to_bucket
         buckets = [b for b in BUCKETS if b <= select_bucket(max_batch)]

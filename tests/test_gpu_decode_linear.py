@@ -97,6 +97,18 @@ def test_product_within_one_step_of_fp64(N, Kd, with_bias, T):
     assert (got[T:] == 0x7E00).all(), "rows past num_tokens were written"
 
 
+@pytest.mark.parametrize("T", [5, 64])
+def test_many_row_tiles_take_the_short_ring(T):
+    """A vocabulary-sized output (57 000 rows: 446 row tiles, three times the SM count, the last one
+    partial) runs with the short ring and several CTAs per SM; same gate as every other shape."""
+    N, Kd = 57000, 264
+    x, w = make(SEED + N + T, T, N, Kd)
+    got = run(x, w, T, N)
+    assert check_product(got, x, w, T) > 0.98
+    assert (got[T:] == 0x7E00).all()
+    assert K.decode_linear_health() == 0
+
+
 def test_strided_views_and_untouched_columns():
     # the engine's qkv buffer: out rows 2048 wide inside a wider allocation, x rows padded
     T, N, Kd = 64, 2048, 1536
