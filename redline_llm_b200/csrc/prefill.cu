@@ -8,7 +8,8 @@
 //
 // LaunchPrefillSoftmax (src/kernels/kernels.cuh:160-187, src/kernels/prefill_attention.cu:103-162):
 // causal row softmax FP32 -> FP16 over [heads, chunk_len, kv_len]; query row i sits at position
-// chunk_start + i and sees keys j <= it; FP32 max and sum, one FP16 rounding of exp(s - max) / sum;
+// chunk_start + i and sees keys j <= it; FP32 max and sum, one FP16 rounding of exp(s - max) / sum
+// (the read-once kernel forms the same quotient from per-thread partial maxima and sums, see there);
 // masked entries are written as exact +0 and their scores never reach a result. One CTA per (row, head);
 // rows of up to 32768 keys are read once and kept in registers, longer or unaligned ones take three
 // passes over the row (it stays in L2); fixed reduction trees either way (run-to-run identical bits).
@@ -109,23 +110,32 @@ __device__ __forceinline__ float BlockReduce(float v, bool is_max, float* scratc
   return r;
 }
 
+// A (max, sum of exp(x - max)) pair over part of a row.
+struct MaxSum {
+  float m, s;
+};
+
 // Rows of up to kThreads * kChunks * 8 scores with kv_len a multiple of 8 and 16-byte aligned bases: the
-// live part of the row is read once, 8 consecutive scores per thread and step, and stays in registers
-// through the max, the exponentials (evaluated once), the sum and the division. Elements of a 32-byte
-// group that lie beyond the causal limit are loaded with the group but replaced by -inf before any use,
-// so their exponential is exactly 0 and so is their probability.
+// live part of the row is read once, 8 consecutive scores per thread and step, and stays in registers.
+// Each thread takes the max of its own scores and their exponentials against that max at once, with no
+// block-wide step in between; fixed trees then merge the threads' (max, sum) pairs, and a thread's
+// results are its exponentials times exp(own max - row max) / row sum: one exponential and one multiply
+// per element, FP32 throughout, one rounding to FP16. Elements of a 32-byte group that lie beyond the
+// causal limit are loaded with the group but replaced by -inf before any use, so their exponential is
+// exactly 0 and so is their probability.
 template <int kThreads, int kChunks>
 __global__ void __launch_bounds__(kThreads)
 PrefillSoftmaxRowKernel(half* __restrict__ probs, const float* __restrict__ scores, int chunk_len, int kv_len,
                         int chunk_start) {
-  __shared__ float scratch[kThreads / 32];
+  static_assert(kThreads % 32 == 0 && kThreads <= 1024, "one scratch pair per warp, at most 32 warps");
+  __shared__ MaxSum scratch[kThreads / 32];
   const int row = blockIdx.x, head = blockIdx.y;
   const size_t base = (static_cast<size_t>(head) * chunk_len + row) * static_cast<size_t>(kv_len);
   const float* s = scores + base;
   half* p = probs + base;
   const int live = min(chunk_start + row + 1, kv_len);
   float x[kChunks][8];
-  float mx = -INFINITY;
+  MaxSum mine = {-INFINITY, 0.0f};
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     const int j0 = (c * kThreads + threadIdx.x) << 3;
@@ -140,27 +150,42 @@ PrefillSoftmaxRowKernel(half* __restrict__ probs, const float* __restrict__ scor
         for (int e = 0; e < 8; ++e) x[c][e] = j0 + e < live ? __uint_as_float(w[e]) : -INFINITY;
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) mx = fmaxf(mx, x[c][e]);
+      for (int e = 0; e < 8; ++e) mine.m = fmaxf(mine.m, x[c][e]);
     }
   }
-  mx = BlockReduce<kThreads>(mx, true, scratch);
-  float sum = 0.0f;
+  // scores of -inf (a caller's own masking) must give 0, not exp(-inf + inf), when they are all a thread has
+  const float local_max = mine.m == -INFINITY ? 0.0f : mine.m;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     const int j0 = (c * kThreads + threadIdx.x) << 3;
     if (j0 < live) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        x[c][e] = expf(x[c][e] - mx);  // exactly 0 for the replaced elements
-        sum += x[c][e];
+        x[c][e] = expf(x[c][e] - local_max);
+        mine.s += x[c][e];
       }
     }
   }
-  sum = BlockReduce<kThreads>(sum, false, scratch);
-  // e / sum for every element of the row: the reciprocal once, then per element the product and one
-  // residual correction, which is the IEEE quotient whenever it is large enough to survive the FP16
-  // rounding that follows (sum lies in [1, kv_len] and e in [0, 1])
-  const float rcp = __frcp_rn(sum);
+  // (max, sum) over the row: the max by a lane tree, each lane's sum rescaled to it once, the sums by the same
+  // tree; then the same again over the warps' pairs (every warp redundantly). Fixed order: same bits every run.
+  float warp_max = mine.m;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) warp_max = fmaxf(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, off));
+  float warp_sum = mine.m == -INFINITY ? 0.0f : mine.s * expf(mine.m - warp_max);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) warp_sum += __shfl_xor_sync(0xffffffffu, warp_sum, off);
+  const int lane = threadIdx.x & 31;
+  if (lane == 0) scratch[threadIdx.x >> 5] = MaxSum{warp_max, warp_sum};
+  __syncthreads();
+  const MaxSum theirs = lane < kThreads / 32 ? scratch[lane] : MaxSum{-INFINITY, 0.0f};
+  float row_max = theirs.m;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, off));
+  float row_sum = theirs.m == -INFINITY ? 0.0f : theirs.s * expf(theirs.m - row_max);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) row_sum += __shfl_xor_sync(0xffffffffu, row_sum, off);
+  // exp(own max - row max) / row sum; a thread without live scores stores only zeros
+  const float factor = mine.m == -INFINITY ? 0.0f : expf(mine.m - row_max) / row_sum;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     const int j0 = (c * kThreads + threadIdx.x) << 3;
@@ -169,11 +194,8 @@ PrefillSoftmaxRowKernel(half* __restrict__ probs, const float* __restrict__ scor
     if (j0 < live) {
       uint32_t* o = &out.x;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float q0 = x[c][2 * e] * rcp, q1 = x[c][2 * e + 1] * rcp;
-        q0 = fmaf(fmaf(-q0, sum, x[c][2 * e]), rcp, q0);
-        q1 = fmaf(fmaf(-q1, sum, x[c][2 * e + 1]), rcp, q1);
-        o[e] = AsU32(__floats2half2_rn(q0, q1));  // replaced elements hold e = 0 and give exact +0
+      for (int e = 0; e < 4; ++e) {  // replaced elements hold 0 and give exact +0
+        o[e] = AsU32(__floats2half2_rn(x[c][2 * e] * factor, x[c][2 * e + 1] * factor));
       }
     }
     Stg16(p + j0, out);
@@ -246,7 +268,7 @@ extern "C" int rl_launch_prefill_softmax(void* probs, const float* scores, int32
     PrefillSoftmaxRowKernel<256, 1><<<grid, 256, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
   } else if (vec && kv_len <= 512 * 1 * 8) {
     PrefillSoftmaxRowKernel<512, 1><<<grid, 512, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
-  } else if (vec && kv_len <= 512 * 2 * 8) {  // 64.6 us at 12 x 512 x 8192 against 68.7 (256 x 4) and 76.3 (1024 x 1)
+  } else if (vec && kv_len <= 512 * 2 * 8) {  // 61.0 us at 12 x 512 x 8192 against 67.5 (256 x 4) and 82.2 (128 x 8)
     PrefillSoftmaxRowKernel<512, 2><<<grid, 512, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
   } else if (vec && kv_len <= 1024 * 2 * 8) {
     PrefillSoftmaxRowKernel<1024, 2><<<grid, 1024, 0, s>>>(out, scores, chunk_len, kv_len, chunk_start);
