@@ -17,9 +17,9 @@
 // thread row per head. Each thread requests one 8-element chunk of the low half
 // of its head and the matching chunk of the high half with 16-byte loads;
 // meanwhile the block evaluates sincosf once per (row, pair) into shared
-// memory; then the chunks are rotated with half2 arithmetic (fp16 x fp16 and fp16 + fp16 are each one
-// correctly rounded half operation, equal to the FP32-then-round form; the _rn
-// intrinsics forbid fusing them into an fma).
+// memory; then the chunks are rotated with half2 arithmetic (fp16 x fp16 and
+// fp16 +- fp16 are each one correctly rounded half operation, equal to the
+// FP32-then-round form; the _rn intrinsics forbid fusing them into an fma).
 #include <cmath>
 #include <mutex>
 
