@@ -210,7 +210,7 @@ class DecodeStepWorkload:
         import torch
         self.TOTAL, self.LONG = total, total // 16
         self.linear = linear
-        self.vocab_projection = vocab_projection or "library"
+        self.vocab_projection = vocab_projection or linear
         from redline_llm_b200.engine import (Engine, ModelConfig, ModelWeights, balanced_order, blocks_for_tokens,
                                              shard_requests)
         self.torch = torch
@@ -700,7 +700,7 @@ def main():
     ap.add_argument("--linear", choices=["tcgen05", "library"], default="tcgen05",
                     help="decode_step: linear layers by this library's tcgen05 kernel (default) or by the library GEMM")
     ap.add_argument("--vocab-projection", choices=["tcgen05", "library"], default=None,
-                    help="decode_step: the vocabulary projection by this library's kernel or by the library GEMM (default)")
+                    help="decode_step: the vocabulary projection by this library's kernel or by the library GEMM (default: as --linear)")
     ap.add_argument("--linear-stages", type=int, default=None, help="ring depth of the tcgen05 linear kernel (2..8)")
     ap.add_argument("--linear-splits", type=int, default=None, help="largest K split of the tcgen05 linear kernel (1,2,4,8)")
     ap.add_argument("--no-overlap", action="store_true",

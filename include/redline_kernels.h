@@ -225,6 +225,8 @@ int rl_launch_prefill_softmax(void* probs, const float* scores, int32_t num_q_he
  *               applied to the rounded GEMM output, without storing the [num_tokens, 2*out_features]
  *               intermediate. bias must be NULL.
  * Results do not depend on arrival order or on the ring depth (fixed summation order).
+ * Outputs of at least three 128-row tiles per SM (a vocabulary projection) run with a 3-stage ring, several
+ * CTAs per SM, and their weights at normal L2 priority; every other shape streams its weights evict-first.
  * First call per device must happen outside stream capture (it opts in to large shared memory and
  * allocates a 256-byte error flag).
  */

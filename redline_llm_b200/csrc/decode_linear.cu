@@ -86,6 +86,7 @@ struct Params {
   int splits;            // CTAs per row tile along K = cluster size: 1, 2, 4 or 8
   int split_shift;       // log2(splits)
   int stages;            // ring depth
+  int weights_sweep_l2;  // weight tiles at normal L2 priority instead of evict-first
   int epilogue;
   int tmem_cols;         // 32 or 64
   int out_vec;           // out rows are 16-byte aligned: vector stores allowed
@@ -158,7 +159,7 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // The first ring of weight tiles is requested at once: weights never depend on the previous
     // kernel of the stream, so this runs ahead of the dependency gate and of the TMEM set-up.
-    const uint64_t stream_policy = L2PolicyEvictFirst();
+    const uint64_t stream_policy = p.weights_sweep_l2 ? L2PolicyEvictNormal() : L2PolicyEvictFirst();
     for (int i = 0; i < pre; ++i) {
       const uint32_t dst = ring + i * kStageBytes, bar = full0 + i * 8;
       MbarExpectTx(bar, stage_tx);
@@ -223,7 +224,8 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: activations once the previous kernel has completed, then the steady state
-      const uint64_t stream_policy = L2PolicyEvictFirst(), keep_policy = L2PolicyEvictLast();
+      const uint64_t stream_policy = p.weights_sweep_l2 ? L2PolicyEvictNormal() : L2PolicyEvictFirst();
+      const uint64_t keep_policy = L2PolicyEvictLast();
       asm volatile("griddepcontrol.wait;" ::: "memory");
       RL_LSTAMP(9);
       for (int i = 0; i < pre; ++i)
@@ -662,8 +664,14 @@ int Launch(void* out, int64_t out_row_stride, const void* x, int64_t x_row_strid
   if (p.splits > 1 && p.stages > kMaxStages - 1) p.stages = kMaxStages - 1;  // room for the receive area
   // Many more row tiles than SMs (the vocabulary projection: 1187 tiles): a short ring lets three CTAs share
   // an SM, so one CTA's prologue and epilogue hide behind the others' streams (64 x 151936 x 1536: 100.9 us
-  // with 6 stages, 84.4 with 4, 79.0 with 3; the library GEMM takes 82.1)
-  if (p.splits == 1 && tiles >= 3 * st->sm_count && p.stages > kManyTileStages) p.stages = kManyTileStages;
+  // with 6 stages, 84.4 with 4, 79.0 with 3, all with evict-first weight tiles; the library GEMM takes 82.1).
+  // Such a launch also takes its weights at normal L2 priority (82.3 us alone): the sweep of some hundred MB
+  // through L2 retires the dead lines of the step (logits, activations, freshly written K/V) once per step,
+  // which inside the decode step measured 24 us per step better than leaving them for the following launches
+  // to push out.
+  const bool many_tiles = p.splits == 1 && tiles >= 3 * st->sm_count;
+  if (many_tiles && p.stages > kManyTileStages) p.stages = kManyTileStages;
+  p.weights_sweep_l2 = many_tiles ? 1 : 0;
   p.split_shift = p.splits == 8 ? 3 : p.splits == 4 ? 2 : p.splits == 2 ? 1 : 0;
   p.epilogue = epilogue;
   p.tmem_cols = p.tokens_padded <= 32 ? 32 : 64;

@@ -9,7 +9,7 @@ bucket (src/core/model_executor.cpp:523-633,721-782). The decode layer sequence 
 (src/core/model_executor.cpp:908-957): every non-GEMM stage is a launcher of this library; the four
 linear layers of a block are this library's tcgen05 weight-streaming kernel (SiLU-mul fused into the
 gate/up product) or, with decode_linear="library", library GEMMs as in the reference (torch.matmul ->
-cuBLAS); the vocabulary projection is a library GEMM unless vocab_projection="tcgen05"; the embedding gather and the greedy
+cuBLAS); the vocabulary projection follows the same switch (vocab_projection= overrides it); the embedding gather and the greedy
 argmax at the two ends of the step are this library's too.
 
 One Engine drives one GPU; multi-GPU serving is one Engine per GPU with requests sharded on the
@@ -304,11 +304,12 @@ class ModelExecutor:
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
         # Linear layers of the decode step: "tcgen05" = this library's weight-streaming kernel (with the
         # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
-        # The vocabulary projection has its own switch of the same two values. Alone, this library's kernel runs
-        # it in 79.0 us against the library GEMM's 82.1 (64 x 151936 x 1536); inside the captured step the library
-        # GEMM came out 24 us per step ahead (21.22k against 21.06k tok/s, two runs each), so it is the default.
+        # The vocabulary projection has its own switch of the same two values and follows decode_linear unless
+        # set. This library's kernel streams its 467 MB of weights at normal L2 priority, as the library GEMM
+        # does: with evict-first tiles the projection itself was 5 us faster but the step 24 us slower, the
+        # sweep through L2 evidently clearing lines that otherwise burden the next wave's launches.
         self.decode_linear = "tcgen05"
-        self.vocab_projection = "library"
+        self.vocab_projection = "tcgen05"
         self.fuse_qkv_rope = True      # RoPE + KV scatter in the QKV product's epilogue (tcgen05 path only)
         self.act = torch.zeros(B, cfg.inter, dtype=f16, device=device)         # silu(gate) * up
         K.init(device.index if device.index is not None else -1)
@@ -559,7 +560,7 @@ class Engine:
             raise ValueError("decode_linear must be 'tcgen05' or 'library'")
         self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
         self.exec.decode_linear = decode_linear
-        self.exec.vocab_projection = vocab_projection or "library"
+        self.exec.vocab_projection = vocab_projection or decode_linear
         self.max_seq_len, self.max_batch = max_seq_len, max_batch
         self.pad_eager_to_bucket = pad_eager_to_bucket
         buckets = [b for b in BUCKETS if b <= select_bucket(max_batch)]
