@@ -146,8 +146,9 @@ int rl_attention_set_prologue_overlap(int enable);
  * capture. Every call clears the array's counters in stream order and then reuses the same
  * array (it keeps the previous call's contents otherwise), so two calls of THIS entry point that
  * overlap on one GPU - issued on different streams, say - race on it; serialise them. The
- * allocating launcher has its own workspace and does not interfere. rl_attention_health reports
- * on the allocating launcher's workspace only.
+ * allocating launcher has its own workspace and does not interfere. A bounded wait that gave up
+ * sets a flag inside the array that stays set across calls until rl_attention_health - which
+ * reports on this array as well as on the allocating launcher's workspace - has returned it.
  * This entry point has no counterpart in the reference.
  */
 int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, const void* q,

@@ -30,14 +30,25 @@ f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
 
 
-def build(force: bool = False) -> None:
-    """Compile the checker (and, where the reference tree is mounted, _ref)."""
-    if force or not os.path.exists(_OWN_PATH) or (
-        os.path.getmtime(_OWN_PATH) < os.path.getmtime(os.path.join(_HERE, "redline_oracle.c"))
-    ):
-        subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    elif not os.path.exists(_REF_PATH) and os.path.isdir("/root/reference/tests/reference"):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+def _make(*targets: str) -> None:
+    env = dict(os.environ)
+    subprocess.run(["make", "-C", _HERE, "-j8", *targets], check=True, capture_output=True, env=env)
+
+
+def build(force: bool = False, gpu_ref: bool = False) -> None:
+    """Compile the CPU checker and, where the reference tree is mounted (the Makefile's REF, or the
+    environment variable REDLINE_REFERENCE_DIR), the reference's own CPU code into _ref/. With
+    `gpu_ref` also the GPU-side comparators of the Makefile's `gpuref` target (the reference's CUDA
+    kernels behind a C ABI, and the reference's C++ host over either kernel library); those link
+    against this repository's built CUDA library, so it must exist. Where the tree is absent the
+    prebuilt files under _ref/ are used as they are."""
+    src = os.path.join(_HERE, "redline_oracle.c")
+    if force or not os.path.exists(_OWN_PATH) or os.path.getmtime(_OWN_PATH) < os.path.getmtime(src):
+        _make("all")
+    elif not os.path.exists(_REF_PATH):
+        _make("ref")
+    if gpu_ref:
+        _make("gpuref")
 
 
 def _sig(fn, res, *args):

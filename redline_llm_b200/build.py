@@ -14,10 +14,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libredline_b200.so")
 
+# The CUDA toolkit: $CUDA_HOME, else the conventional install prefix. nvcc and the runtime library's
+# rpath are both taken from it ($NVCC overrides the compiler alone).
+CUDA_HOME = os.environ.get("CUDA_HOME") or os.environ.get("CUDA_PATH") or "/usr/local/cuda"
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall", "-shared", "-cudart", "shared",
-    "-Xlinker", "-rpath,/usr/local/cuda/lib64",
+    "-Xlinker", "-rpath," + os.path.join(CUDA_HOME, "lib64"),
 ]
 
 
@@ -37,7 +41,7 @@ def stale() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB
-    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    nvcc = os.environ.get("NVCC") or os.path.join(CUDA_HOME, "bin", "nvcc")
     cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + sources()
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

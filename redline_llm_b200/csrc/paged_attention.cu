@@ -887,6 +887,12 @@ int CheckContract(const char* fn, const void* out, int64_t out_stride, const voi
 }  // namespace attn
 }  // namespace rl
 
+namespace rl {
+namespace attn {
+void* StaticScratchIfReady(int dev);  // device address of the built-in scratch array once the static launcher ran
+}
+}  // namespace rl
+
 extern "C" int rl_kernels_init(int device) {
   if (device >= 0) {
     const cudaError_t e = cudaSetDevice(device);
@@ -918,11 +924,20 @@ extern "C" int rl_attention_health(int* flag_out) {
   using namespace rl::attn;
   if (!flag_out) return Fail(RL_E_NULL_POINTER, "rl_attention_health: null pointer");
   *flag_out = 0;
-  DeviceState& st = g_state[CurrentDeviceIndex()];
-  if (!st.ready) return RL_OK;
+  const int dev = CurrentDeviceIndex();
+  // Both scratch areas carry a flag: the allocated workspace of rl_launch_paged_attention_decode and the
+  // array built into the library that rl_launch_paged_attention_decode_static uses. Either is read (and
+  // cleared) only if its launcher has run on this device; the result is the OR of the two.
+  void* areas[2] = {g_state[dev].ready ? g_state[dev].workspace : nullptr, StaticScratchIfReady(dev)};
+  if (!areas[0] && !areas[1]) return RL_OK;
   cudaError_t e = cudaDeviceSynchronize();
-  if (e == cudaSuccess) e = cudaMemcpy(flag_out, st.workspace, sizeof(int), cudaMemcpyDeviceToHost);
-  if (e == cudaSuccess && *flag_out != 0) e = cudaMemset(st.workspace, 0, sizeof(int));
+  for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+    if (!areas[i]) continue;
+    int flag = 0;
+    e = cudaMemcpy(&flag, areas[i], sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && flag != 0) e = cudaMemset(areas[i], 0, sizeof(int));
+    *flag_out |= flag;
+  }
   if (e != cudaSuccess) return Fail(static_cast<int>(e), "rl_attention_health: %s", cudaGetErrorString(e));
   return RL_OK;
 }
@@ -992,12 +1007,15 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
 // Allocation-free variant of the attention launcher.
 //
 // Some hosts may not allocate device memory at all: a process that was handed a
-// fixed memory budget and a sealed allocator, a plugin running inside somebody
-// else's CUDA context under a "no cudaMalloc after start-up" rule, a thread that
-// is already inside stream capture when it first needs the kernel. For them the
+// fixed memory budget and a sealed allocator, or a plugin running inside somebody
+// else's CUDA context under a "no cudaMalloc after start-up" rule. For them the
 // split/merge scratch lives in the library image itself: a file-scope device
 // array of kStaticScratchBytes, resident on every GPU that loads the library
 // until the process exits. Inputs and outputs are still the caller's.
+//
+// The first call on a device resolves the array's device address, opts the kernel
+// in to its shared memory and looks up one driver entry point; make that call
+// outside stream capture. Later calls issue a memset node and the launch only.
 // ---------------------------------------------------------------------------
 namespace rl {
 namespace attn {
@@ -1035,7 +1053,7 @@ int EnsureStaticReady(StaticState** out_state) {
   if (facts.max_smem_optin < kSmemBytes)
     return Fail(RL_E_WORKSPACE, "paged_attention (static): %d B of shared memory per block, %d needed",
                 facts.max_smem_optin, kSmemBytes);
-  if (facts.sm_count > kMaxCtas)
+  if (facts.sm_count * kCtasPerSm > kMaxCtas)
     return Fail(RL_E_TOO_LARGE, "paged_attention (static): %d SMs, the built-in scratch covers %d CTAs",
                 facts.sm_count, kMaxCtas);
   cudaError_t e = cudaFuncSetAttribute(PagedAttentionSplitKernel,
@@ -1048,10 +1066,13 @@ int EnsureStaticReady(StaticState** out_state) {
     return Fail(e != cudaSuccess ? static_cast<int>(e) : RL_E_WORKSPACE,
                 "paged_attention (static): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
   st.scratch = ptr;
-  st.ctas = facts.sm_count;
+  // the same grid as the allocating launcher, so that both cut the page range alike and merge in the same order
+  st.ctas = facts.sm_count * kCtasPerSm < kMaxCtas ? facts.sm_count * kCtasPerSm : kMaxCtas;
   st.ready = true;
   return RL_OK;
 }
+
+void* StaticScratchIfReady(int dev) { return g_static_state[dev].ready ? g_static_state[dev].scratch : nullptr; }
 
 }  // namespace attn
 }  // namespace rl
@@ -1083,9 +1104,10 @@ extern "C" int rl_launch_paged_attention_decode_static(void* out, int64_t out_ro
   if ((rc = EncodeTileMap(kv_pool_layer, num_kv_heads, &tile_map)) != RL_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left. Partial records are fully rewritten before they
-  // are read; the error flag and the ticket counters must start at zero, so they are cleared here,
-  // in stream order, before the kernel.
-  const cudaError_t e = cudaMemsetAsync(st->scratch, 0, sizeof(int) * kMetaInts, s);
+  // are read; the ticket counters must start at zero, so they are cleared here, in stream order, before
+  // the kernel. The error flag (meta[0]) is NOT cleared: it stays set until rl_attention_health has
+  // reported it (the array is zero when the library is loaded).
+  const cudaError_t e = cudaMemsetAsync(static_cast<int*>(st->scratch) + kTicketOff, 0, sizeof(int) * kMaxCtas, s);
   if (e != cudaSuccess)
     return Fail(static_cast<int>(e), "paged_attention_decode_static: clearing the counters: %s", cudaGetErrorString(e));
   Params p;

@@ -42,7 +42,8 @@ class ModelConfig:
     vocab: int = 151936
     rope_theta: float = 1e6
     eps: float = 1e-6
-    eos_token_id: int = 151645
+    eos_token_id: int = 151645                       # <|im_end|>; config.json's scalar
+    extra_eos_token_ids: Tuple[int, ...] = (151643,)   # the rest of generation_config.json's stop set (src/core/config.cpp:54-56)
 
     @property
     def qkv_width(self):
@@ -162,9 +163,10 @@ class Scheduler:
     """FCFS admission, prefill-before-decode, bucketed decode batches."""
 
     def __init__(self, allocator: BlockAllocator, max_batch: int, max_seq_len: int, prefill_chunk: int,
-                 eos_token_id: int = 151645):
+                 eos_token_id=151645):
         self.alloc, self.max_batch, self.max_seq_len, self.chunk = allocator, max_batch, max_seq_len, prefill_chunk
-        self.eos = eos_token_id
+        # one id or the whole stop set; compared as a set (src/core/scheduler.cpp: IsEosToken)
+        self.eos = frozenset([eos_token_id] if isinstance(eos_token_id, int) else eos_token_id)
         self.waiting: deque = deque()
         self.running: List[Request] = []
         self.aborts = 0
@@ -211,14 +213,18 @@ class Scheduler:
         return ("decode", batch)
 
     def complete(self, r: Request, token: int) -> Tuple[int, int, bool, str]:
-        """Appends the sampled (or forced) token, applies the stop checks, frees blocks on finish."""
+        """Appends the sampled token - or, under teacher forcing, the scripted one - applies the stop checks
+        to the APPENDED token and frees blocks on finish. The returned tuple still reports the engine's own
+        sampled token, so a parity run can score every position along a fixed continuation
+        (src/core/scheduler.cpp:284-300, src/core/request.hpp:33-41)."""
+        appended = token
         if r.forced_tokens is not None and len(r.output) < len(r.forced_tokens):
-            token = r.forced_tokens[len(r.output)]
-        r.output.append(int(token))
-        if len(r.output) >= r.max_new_tokens:
+            appended = r.forced_tokens[len(r.output)]
+        r.output.append(int(appended))
+        if not r.ignore_eos and appended in self.eos:
+            r.finished, r.reason = True, "eos"     # EOS wins a simultaneous length stop
+        elif len(r.output) >= r.max_new_tokens:
             r.finished, r.reason = True, "length"
-        elif not r.ignore_eos and token == self.eos:
-            r.finished, r.reason = True, "eos"
         if r.finished:
             self.release(r)
         return (r.req_id, int(token), r.finished, r.reason)
@@ -301,6 +307,7 @@ class ModelExecutor:
         self.tokens_ready = torch.cuda.Event()   # recorded behind the D2H copy of the sampled tokens
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
+        self.prefill_logits = None
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
         # Linear layers of the decode step: "tcgen05" = this library's weight-streaming kernel (with the
         # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
@@ -521,6 +528,7 @@ class ModelExecutor:
             return None
         K.launch_rms_norm_residual(normed, x, mlp, w.final_norm, n, cfg.hidden, cfg.eps)
         logits = torch.matmul(normed[-1:], w.lm_head.t())
+        self.prefill_logits = logits   # kept for parity audits of the first generated token
         tok = torch.zeros(1, dtype=torch.int32, device=dev)
         K.launch_greedy_argmax(tok, logits, 1, cfg.vocab)
         return int(tok.item())
@@ -550,7 +558,8 @@ class Engine:
         torch.cuda.set_device(self.device)
         num_blocks = max(2, int(kv_pool_gb * (1 << 30)) // self.cfg.block_bytes())
         self.allocator = BlockAllocator(num_blocks)
-        self.scheduler = Scheduler(self.allocator, max_batch, max_seq_len, prefill_chunk, self.cfg.eos_token_id)
+        self.scheduler = Scheduler(self.allocator, max_batch, max_seq_len, prefill_chunk,
+                                   (self.cfg.eos_token_id,) + tuple(self.cfg.extra_eos_token_ids))
         from . import kernels as K
         # attention's table walk may overlap the RoPE+scatter kernel before it: seq_lens and the block
         # tables are uploaded at the start of a step, never written by that kernel
@@ -646,8 +655,9 @@ class Engine:
         for r, t in zip(batch, toks):
             r.cached += 1
             out.append(self.scheduler.complete(r, t))
-        # what the next step feeds back (forced tokens included); any finished request changes the batch
-        self.exec._last_tokens = np.fromiter((o[1] for o in out), dtype=np.int32, count=len(out))
+        # what the next step feeds back: the APPENDED tokens (the scripted ones under teacher forcing); any
+        # finished request changes the batch, which fill_mirrors notices by itself
+        self.exec._last_tokens = np.fromiter((r.output[-1] for r in batch), dtype=np.int32, count=len(batch))
         return out
 
     def stats(self) -> dict:

@@ -1,7 +1,8 @@
 """Generates the committed golden vectors under tests/golden/.
 
 Run where the reference tree is mounted (its location comes from the
-REDLINE_REFERENCE environment variable):  python tests/golden/make_golden.py
+REDLINE_REFERENCE_DIR environment variable):
+    REDLINE_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py
 
 Sources of truth, none of them this repository's code:
   * the reference's committed RoPE capture tests/data/rope_fixture.json
@@ -22,7 +23,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 import oracle  # noqa: E402
 
-REF_TREE = os.environ.get("REDLINE_REFERENCE", "/root/reference")
+REF_TREE = os.environ.get("REDLINE_REFERENCE_DIR")
+if not REF_TREE or not os.path.isdir(REF_TREE):
+    raise SystemExit("set REDLINE_REFERENCE_DIR to the reference checkout")
 
 
 def rope_capture():

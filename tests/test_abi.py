@@ -38,3 +38,58 @@ def test_contract_errors_are_reported_without_a_gpu():
     assert b"head_dim" in L.rl_last_error()
     assert L.rl_launch_paged_attention_decode(0, 1536, 8, 1536, 16, 8, 8, 1, 4, 12, 2, 128, 0.1, 0) == -1
     assert L.rl_launch_rope_inplace(8, 8, 1536, 256, 8, 4, 12, 2, 130, 1e6, 0) == -2
+
+
+def test_reference_side_comparators_load_where_they_were_built():
+    """oracle/_ref holds, where the reference tree was mounted at build time: the reference's CUDA kernels
+    behind a C ABI, and the reference's own C++ host (its pybind module) linked once to this library and
+    once to its own kernels. Without a GPU they must still load and resolve every symbol; the host module
+    must fail a missing model directory with the binding's RuntimeError, before touching CUDA."""
+    import subprocess
+    import sys
+
+    import pytest
+
+    from oracle import ref_kernels as R
+    if not R.available():
+        pytest.skip("oracle/_ref was built without the reference tree")
+    lib = ctypes.CDLL(R.LIB_PATH)
+    for n in R.SYMBOLS:
+        assert hasattr(lib, n), n
+    for d in (R.HOST_B200_DIR, R.HOST_REF_DIR):
+        code = ("import sys; sys.path.insert(0, %r); import redline\n"
+                "assert redline.__version__ == '0.1.0'\n"
+                "for m in ('add_request', 'step', 'has_capacity', 'stats'): assert hasattr(redline.Engine, m)\n"
+                "try:\n    redline.Engine('/nonexistent-model-dir')\nexcept RuntimeError as e:\n    print('RuntimeError', e)\n") % d
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and "RuntimeError" in r.stdout, (d, r.stdout, r.stderr[-2000:])
+
+
+def test_checkpoint_writer_produces_a_well_formed_safetensors_file(tmp_path):
+    """tests/ref_host.py writes the checkpoint the reference's loader reads; here its container format is
+    checked on a miniature model (header length, JSON, contiguous offsets, names of docs/MODEL_SPEC.md:182-199)."""
+    import json
+    import struct
+
+    import torch
+
+    from redline_llm_b200.engine import ModelConfig, ModelWeights
+    from tests import ref_host
+    cfg = ModelConfig(layers=2, hidden=64, inter=96, q_heads=2, kv_heads=1, head_dim=32, vocab=50)
+    w = ModelWeights(cfg, torch.device("cpu"), seed=3)
+    d = ref_host.write_model_dir(str(tmp_path), cfg, w)
+    raw = open(os.path.join(d, "model.safetensors"), "rb").read()
+    n = struct.unpack("<Q", raw[:8])[0]
+    hdr = json.loads(raw[8:8 + n])
+    assert hdr.pop("__metadata__") == {"format": "pt"} and len(hdr) == 2 + 12 * cfg.layers and n % 8 == 0
+    end = 0
+    for name, e in hdr.items():
+        assert e["dtype"] == "F16" and e["data_offsets"][0] == end
+        end = e["data_offsets"][1]
+        assert end - e["data_offsets"][0] == 2 * int(torch.tensor(e["shape"]).prod())
+    assert len(raw) == 8 + n + end
+    q = hdr["model.layers.1.self_attn.q_proj.weight"]
+    got = torch.frombuffer(bytearray(raw[8 + n + q["data_offsets"][0]:8 + n + q["data_offsets"][1]]), dtype=torch.float16)
+    assert torch.equal(got.view(64, 64), w.layers[1]["qkv"][:64])
+    assert hdr["model.layers.0.mlp.up_proj.weight"]["shape"] == [96, 64]
+    assert json.load(open(os.path.join(d, "config.json")))["torch_dtype"] == "bfloat16"
