@@ -214,12 +214,9 @@ class DecodeStepWorkload:
         from redline_llm_b200.engine import (Engine, ModelConfig, ModelWeights, balanced_order, blocks_for_tokens,
                                              shard_requests)
         self.torch = torch
-        ctx = np.concatenate([wl.randint(wl.SEED_STEP, self.TOTAL - self.LONG, 1024, 8192),
-                              np.full(self.LONG, 32768, np.int32)])
-        ctx = ctx[wl.permutation(wl.SEED_STEP + 1, self.TOTAL)]
         # the host-side router: longest first, snake-dealt over 8 shards, so that at every GPU count each GPU serves
         # the same number of 32 768-token sequences and (within ~1 %) the same number of cached tokens
-        ctx = ctx[balanced_order(ctx, shards=8, seed=wl.SEED_STEP + 2)]
+        ctx = decode_step_contexts(self.TOTAL)
         mine = [int(ctx[i]) for i in shard_requests(self.TOTAL, world, rank)]
         self.cfg = ModelConfig()
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -313,6 +310,8 @@ def kernel_table(peak, only=None, eager=False):
     entries whose name contains it; `eager` launches directly instead of replaying a CUDA graph (profilers)."""
     import torch
     from redline_llm_b200 import kernels as K
+    from oracle import ref_kernels as R     # the reference's own CUDA kernels, when oracle/_ref holds them: `ref_us`
+    have_ref = R.available()
     out = {}
 
     def want(name):
@@ -328,9 +327,16 @@ def kernel_table(peak, only=None, eager=False):
         t = time_region(replay, iters, torch.cuda.synchronize)
         return t * 1e-3 / (iters * nbuf)
 
-    def report(name, secs, nbytes, note):
+    def both(fn, nbuf, iters=20):
+        """fn(module, i): the same launch through this library and through the reference's kernel library."""
+        return timed(lambda i: fn(K, i), nbuf, iters), (timed(lambda i: fn(R, i), nbuf, iters) if have_ref else None)
+
+    def report(name, secs, nbytes, note, ref_secs=None):
         out[name] = {"us": round(secs * 1e6, 3), "GB/s": round(nbytes / secs / 1e9, 1),
                      "frac_of_measured_peak": round(nbytes / secs / 1e9 / peak, 4), "bytes": nbytes, "note": note}
+        if ref_secs is not None:
+            out[name].update({"ref_us": round(ref_secs * 1e6, 3), "ref_GB/s": round(nbytes / ref_secs / 1e9, 1),
+                              "speedup_vs_ref_kernel": round(ref_secs / secs, 2)})
 
     for t, note in ((64, "config 1; latency-bound, L2-resident"), (16384, "large-T, cold L2")):
         if not want(f"rmsnorm_residual_T{t}"):
@@ -341,8 +347,8 @@ def kernel_table(peak, only=None, eager=False):
         r = [dev(np.tile(c["residual"], (t // 64, 1))) for _ in range(nbuf)]
         o = [torch.empty(t, 1536, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
         w = dev(c["weight"])
-        secs = timed(lambda i: K.launch_rms_norm_residual(o[i], r[i], x[i], w, t, 1536, 1e-6), nbuf)
-        report(f"rmsnorm_residual_T{t}", secs, 4 * t * 1536 * 2 + 1536 * 2, note)
+        secs, rsecs = both(lambda M, i: M.launch_rms_norm_residual(o[i], r[i], x[i], w, t, 1536, 1e-6), nbuf)
+        report(f"rmsnorm_residual_T{t}", secs, 4 * t * 1536 * 2 + 1536 * 2, note, rsecs)
         del x, r, o
     if want("rope_T64") or want("kv_scatter_T64"):
         c = wl.config_rope_scatter(64)
@@ -351,13 +357,13 @@ def kernel_table(peak, only=None, eager=False):
         pos, tab = dev(c["positions"]), dev(c["tables"])
         pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
         if want("rope_T64"):
-            secs = timed(lambda i: K.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, 64, 12, 2, 128, 1e6,
+            secs, rsecs = both(lambda M, i: M.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, 64, 12, 2, 128, 1e6,
                                                          k_offset=1536), nbuf)
-            report("rope_T64", secs, 2 * 64 * 1792 * 2 + 256, "config 2; latency-bound")
+            report("rope_T64", secs, 2 * 64 * 1792 * 2 + 256, "config 2; latency-bound", rsecs)
         if want("kv_scatter_T64"):
-            secs = timed(lambda i: K.launch_kv_scatter(pool, qkv[i], qkv[i], 2048, 2048, tab, tab.shape[1], pos, 64,
+            secs, rsecs = both(lambda M, i: M.launch_kv_scatter(pool, qkv[i], qkv[i], 2048, 2048, tab, tab.shape[1], pos, 64,
                                                        2, 128, k_offset=1536, v_offset=1792), nbuf)
-            report("kv_scatter_T64", secs, 64 * 1024 * 2 + 64 * 8, "config 2; latency-bound")
+            report("kv_scatter_T64", secs, 64 * 1024 * 2 + 64 * 8, "config 2; latency-bound", rsecs)
         del pool, qkv
     for t, note in ((64, "config 4; L2-resident"), (512, "config 4; L2-resident"), (4096, "config 4; HBM-bound")):
         if not want(f"silu_mul_T{t}"):
@@ -368,22 +374,22 @@ def kernel_table(peak, only=None, eager=False):
         # dense output buffers: writing in place would feed each launch the previous launch's results, which
         # decay towards subnormals over the timed iterations; bytes moved are the same (2 reads + 1 write)
         outs = [torch.empty(t, 8960, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
-        secs = timed(lambda i: K.launch_silu_mul(outs[i], bufs[i], t, 8960), nbuf)
-        report(f"silu_mul_T{t}", secs, 3 * t * 8960 * 2, note + "; dense out")
+        secs, rsecs = both(lambda M, i: M.launch_silu_mul(outs[i], bufs[i], t, 8960), nbuf)
+        report(f"silu_mul_T{t}", secs, 3 * t * 8960 * 2, note + "; dense out", rsecs)
         del bufs, outs
     if want("greedy_argmax_64x151936"):
         nbuf = 8
         lg = [dev(wl.normal_half(0xA46 + i, 64 * 151936).reshape(64, 151936)) for i in range(nbuf)]
         tok = torch.zeros(64, dtype=torch.int32, device="cuda")
-        secs = timed(lambda i: K.launch_greedy_argmax(tok, lg[i], 64, 151936), nbuf)
-        report("greedy_argmax_64x151936", secs, 64 * 151936 * 2 + 64 * 4, "decode batch of logits; 8-CTA clusters per row")
+        secs, rsecs = both(lambda M, i: M.launch_greedy_argmax(tok, lg[i], 64, 151936), nbuf)
+        report("greedy_argmax_64x151936", secs, 64 * 151936 * 2 + 64 * 4, "decode batch of logits; 8-CTA clusters per row", rsecs)
         del lg
     if want("embed_gather_T64"):
         table = dev(wl.normal_half(0xE1, 32768 * 1536).reshape(32768, 1536))
         ids = dev(wl.randint(0xE2, 64, 0, 32767))
         o = [torch.empty(64, 1536, dtype=torch.int16, device="cuda") for _ in range(8)]
-        secs = timed(lambda i: K.launch_embed_gather(o[i], 1536, table, ids, 64, 1536), 8)
-        report("embed_gather_T64", secs, 2 * 64 * 1536 * 2 + 64 * 4, "latency-bound")
+        secs, rsecs = both(lambda M, i: M.launch_embed_gather(o[i], 1536, table, ids, 64, 1536), 8)
+        report("embed_gather_T64", secs, 2 * 64 * 1536 * 2 + 64 * 4, "latency-bound", rsecs)
         del table, o
     if want("rope_kv_scatter_fused_T64"):
         c = wl.config_rope_scatter(64)
@@ -391,7 +397,12 @@ def kernel_table(peak, only=None, eager=False):
         pos, tab = dev(c["positions"]), dev(c["tables"])
         pool = torch.zeros(8192 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda")
         secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pool, tab, tab.shape[1], pos, 64, 12, 2, 128, 1e6), 8)
-        report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1536 + 64 * 8 + 256, "config 2 in one launch; latency-bound")
+
+        def ref_pair(i):   # what the reference's executor launches for the same work
+            R.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, 64, 12, 2, 128, 1e6, k_offset=1536)
+            R.launch_kv_scatter(pool, qkv[i], qkv[i], 2048, 2048, tab, tab.shape[1], pos, 64, 2, 128, k_offset=1536, v_offset=1792)
+        report("rope_kv_scatter_fused_T64", secs, 2 * 64 * 1792 * 2 + 64 * 1536 + 64 * 8 + 256,
+               "config 2 in one launch; latency-bound; ref_us = the reference's two launches", timed(ref_pair, 8) if have_ref else None)
         del pool, qkv
     # the same three kernels at a prompt chunk's size: 16384 consecutive positions of one sequence (one table
     # row shared by every token, row stride 0, as prompt ingestion calls them), buffers rotated past L2
@@ -405,13 +416,13 @@ def kernel_table(peak, only=None, eager=False):
         pools = [torch.zeros(2048 * 2 * 2 * 16 * 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
         rope_bytes = 2 * t * 1792 * 2 + t * 4
         if want(big[0]):
-            secs = timed(lambda i: K.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, t, 12, 2, 128, 1e6,
+            secs, rsecs = both(lambda M, i: M.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, t, 12, 2, 128, 1e6,
                                                          k_offset=1536), nbuf, iters=5)
-            report(big[0], secs, rope_bytes, "prompt chunk, cold L2")
+            report(big[0], secs, rope_bytes, "prompt chunk, cold L2", rsecs)
         if want(big[1]):
-            secs = timed(lambda i: K.launch_kv_scatter(pools[i], qkv[i], qkv[i], 2048, 2048, row, 0, pos, t,
+            secs, rsecs = both(lambda M, i: M.launch_kv_scatter(pools[i], qkv[i], qkv[i], 2048, 2048, row, 0, pos, t,
                                                        2, 128, k_offset=1536, v_offset=1792), nbuf, iters=5)
-            report(big[1], secs, 2 * t * 1024 + t * 4 + t // 4, "prompt chunk, cold L2; strided 1 KiB reads")
+            report(big[1], secs, 2 * t * 1024 + t * 4 + t // 4, "prompt chunk, cold L2; strided 1 KiB reads", rsecs)
         if want(big[2]):
             secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pools[i], row, 0, pos, t, 12, 2, 128, 1e6),
                          nbuf, iters=5)
@@ -425,20 +436,32 @@ def kernel_table(peak, only=None, eager=False):
         pools = [dev(wl.normal_half(0x2B4 + (i & 1), 2048 * 2 * 2 * 16 * 128)) for i in range(nbuf)]
         kh = [torch.empty(2, ctx, 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
         vh = [torch.empty(2, ctx, 128, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
-        secs = timed(lambda i: K.launch_kv_gather(kh[i], vh[i], ctx * 128, 128, ctx * 128, 128, pools[i], row, ctx,
+        secs, rsecs = both(lambda M, i: M.launch_kv_gather(kh[i], vh[i], ctx * 128, 128, ctx * 128, 128, pools[i], row, ctx,
                                                   2, 128), nbuf, iters=5)
-        report("kv_gather_ctx16384", secs, 2 * ctx * 1024 + ctx // 4, "one sequence's pages into dense K, V; cold L2")
+        report("kv_gather_ctx16384", secs, 2 * ctx * 1024 + ctx // 4, "one sequence's pages into dense K, V; cold L2", rsecs)
         del pools, kh, vh
     if want("prefill_softmax_12x512x8192"):
         h, c, kv, start, nbuf = 12, 512, 8192, 7680, 2
         sc = [torch.randn(h, c, kv, dtype=torch.float32, device="cuda",
                           generator=torch.Generator("cuda").manual_seed(0x2B6 + i)) * 2.5 for i in range(nbuf)]
         pr = [torch.empty(h, c, kv, dtype=torch.int16, device="cuda") for _ in range(nbuf)]
-        secs = timed(lambda i: K.launch_prefill_softmax(pr[i], sc[i], h, c, kv, start), nbuf, iters=5)
+        secs, rsecs = both(lambda M, i: M.launch_prefill_softmax(pr[i], sc[i], h, c, kv, start), nbuf, iters=5)
         live = sum(min(start + r + 1, kv) for r in range(c))
         report("prefill_softmax_12x512x8192", secs, h * (live * 4 + c * kv * 2),
-               "chunk rows 7680..8191 against 8192 keys: live FP32 scores read once, FP16 probabilities written")
+               "chunk rows 7680..8191 against 8192 keys: live FP32 scores read once, FP16 probabilities written", rsecs)
         del sc, pr
+    # paged attention at the configuration's shape (batch 64, contexts U[1024,1280]) and at long contexts
+    # (U[4096,8192]), layer pools rotated past L2; the reference's kernel walks each (sequence, head) serially
+    for name, (lo, hi, layers) in (("paged_attention_b64_ctx1024-1280", (1024, 1280, 10)),
+                                   ("paged_attention_b64_ctx4096-8192", (4096, 8192, 3))):
+        if not want(name):
+            continue
+        aw = AttentionWorkload(0, layers, lo, hi)
+        secs, rsecs = both(lambda M, i: M.launch_paged_attention_decode(aw.out, 1536, aw.q, 2048, aw.pools[i], aw.tables,
+                                                                        aw.lens, 64, aw.mbps, 12, 2, 128, aw.c["scale"]),
+                           layers, iters=10)
+        report(name, secs, aw.bytes_per_launch, f"{layers} layer pools in rotation, cold L2", rsecs)
+        del aw
     # the four linear layers of a decoder block at 64 token rows: weight streams (28 distinct weights, cold L2)
     for name, (n_out, k_in, epi, with_bias) in (("decode_linear_qkv_T64", (2048, 1536, 0, True)),
                                                  ("decode_linear_o_T64", (1536, 1536, 0, False)),
@@ -487,54 +510,87 @@ def cpu_attention(sample_seqs: int, use_ref: bool):
     return nbytes / dt / 1e9, cores, kind, f"{n} of 64 sequences of config 3, one layer pool, FP64 two-pass softmax", dt
 
 
-def reference_line(args, metric, unit, value, ms_per_step, config, cpu, dtype):
+def reference_line(args, metric, unit, value, ms_per_step, config, cpu, dtype, steps, warmup, note):
+    """`steps` / `warmup` are the counts that were actually run and timed (the request may be capped)."""
     return {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if unit == "tok/s" else "weak", "vs_baseline": None, "dtype": dtype,
-            "data": "synthetic", "config": config, "cpu_baseline": cpu,
+            "data": "synthetic", "config": config, "cpu_baseline": cpu, "note": note,
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
 
 
+REFERENCE_ARM_BUDGET_S = 90.0   # host seconds the timed steps of the reference arm may take in total
+
+
+def decode_step_contexts(total: int = 512):
+    """Context lengths of the decode-step workload in serving order (host arithmetic only): total - total/16
+    uniform in [1024, 8192] plus total/16 of 32768 tokens, shuffled, then ordered by the host-side router."""
+    from redline_llm_b200.engine import balanced_order
+    long_rows = total // 16
+    ctx = np.concatenate([wl.randint(wl.SEED_STEP, total - long_rows, 1024, 8192), np.full(long_rows, 32768, np.int32)])
+    ctx = ctx[wl.permutation(wl.SEED_STEP + 1, total)]
+    return ctx[balanced_order(ctx, shards=8, seed=wl.SEED_STEP + 2)]
+
+
+def decode_step_config(total, world, extra=None):
+    """The workload description both arms print (static facts only; what was measured goes elsewhere)."""
+    c = {"workload": DecodeStepWorkload.name, "sequences": total, "wave": DecodeStepWorkload.WAVE, "new_tokens": 256,
+         "contexts": "480 uniform in [1024, 8192] + 32 of 32768 (x sequences/512)", "model": "Qwen2.5-1.5B architecture, "
+         "random init FP16 ~N(0,0.02): 28 layers, hidden 1536, FFN 8960, 12 Q / 2 KV heads, d=128, vocab 151936",
+         "sharding": "sequences dealt over the GPUs by a host-side router, decoded in waves of 64 per GPU"}
+    c.update(extra or {})
+    return c
+
+
 def run_reference_arm(args, rank, world):
-    """The reference's own CPU implementation of the path on the host cores (rank 0 only)."""
+    """The reference's own CPU implementation of the path on the host cores (rank 0 only). Inputs are generated
+    on the host from the same seeded streams; neither a GPU nor this repository's CUDA library is touched."""
     if rank != 0:
         return
     if args.workload == "attention":
         cores = os.cpu_count() or 1
         n = min(64, max(8, 2 * cores))
-        for _ in range(args.warmup):
-            cpu_attention(n, True)
-        runs = [cpu_attention(n, True) for _ in range(args.steps)]
+        first = cpu_attention(n, True)                                   # also the warm-up
+        steps = max(1, min(args.steps, int(REFERENCE_ARM_BUDGET_S / max(first[4], 1e-3))))
+        runs = [cpu_attention(n, True) for _ in range(steps)]
         value = float(np.mean([r[0] for r in runs]))
         cpu = {"value": round(value, 4), "unit": "GB/s", "cores": runs[0][1], "kind": runs[0][2], "sample": runs[0][3]}
         print(json.dumps(reference_line(
             args, METRIC, "GB/s", round(value, 4), round(1e3 * float(np.mean([r[4] for r in runs])), 3),
-            {"workload": AttentionWorkload.name, "batch": 64, "note": "each step is a bounded sample on the host cores"},
-            cpu, "f64")), flush=True)
+            {"workload": AttentionWorkload.name, "batch_per_gpu": 64}, cpu, "f64", steps, 1,
+            f"each step is a bounded sample ({n} of 64 sequences) on the host cores; {steps} of the {args.steps} "
+            f"requested steps fit the {REFERENCE_ARM_BUDGET_S:.0f} s budget")), flush=True)
         return
-    # decode step: the model and its KV cache live on the GPU only as a generator of the synthetic inputs;
-    # every timed operation below runs on the host cores.
-    import torch
-    if not torch.cuda.is_available():
-        print(json.dumps({"impl": "reference", "unavailable": "the synthetic model and cache are generated on a GPU"}))
-        return
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    w = DecodeStepWorkload(0, 64, new_tokens=8)  # 8 sequences: one small wave is enough for the sample
-    for e in w.engines:
-        e.step()
-    rows = sample_rows(w, 2)
-    steps = max(1, min(args.steps, 3))
-    runs = [cpu_decode_step(w, rows, True) for _ in range(steps)]
-    dt = float(np.mean([r[0] for r in runs]))
+    from oracle.decode_step import CpuDecoder, HostWeights, host_step_inputs
+    from redline_llm_b200.engine import ModelConfig
+    cfg = ModelConfig()
+    ctx = decode_step_contexts(args.sequences)
+    wave0 = [int(c) for c in ctx[0::max(1, args.gpus)][:DecodeStepWorkload.WAVE]]
+    mean = float(np.mean(ctx))
+    rows = sorted(int(i) for i in np.argsort(np.abs(np.asarray(wave0, np.float64) - mean))[:2])
+    sample_ctx = [wave0[i] for i in rows]
+    dec = CpuDecoder(cfg, HostWeights(cfg, seed=0x5EED), use_ref=True)
+    inputs = host_step_inputs(cfg, sample_ctx, wl.SEED_STEP + 77)
+    scale = 1.0 / float(np.sqrt(cfg.head_dim))
+
+    def one():
+        ids, pos, lens, ctab, pools = inputs
+        return dec.step_host(ids, pos, lens, ctab, [p.copy() for p in pools], scale)[0]
+    first = one()                                                        # warm-up (page faults, BLAS threads)
+    steps = max(1, min(args.steps, int(REFERENCE_ARM_BUDGET_S / max(first, 1e-3))))
+    times = [one() for _ in range(steps)]
+    dt = float(np.mean(times))
     value = len(rows) / dt
-    cpu = {"value": round(value, 4), "unit": "tok/s", "cores": runs[0][3], "kind": runs[0][4],
-           "sample": f"{len(rows)} sequences x 1 decode step, all 28 layers, contexts "
-                     f"{[w.lens[0][i] for i in rows]} (closest to the job's mean), BLAS FP32 GEMMs"}
-    print(json.dumps(reference_line(args, "decode tok/s", "tok/s", round(value, 4), round(1e3 * dt, 3),
-                                    {"workload": DecodeStepWorkload.name, "note": "each step is a bounded sample "
-                                     "(2 sequences) of the workload on the host cores"}, cpu, "f64 kernels / f32 GEMM")),
-          flush=True)
+    cpu = {"value": round(value, 4), "unit": "tok/s", "cores": dec.threads, "kind": dec.kind,
+           "sample": f"{len(rows)} sequences x 1 decode step, all 28 layers, contexts {sample_ctx} (closest to the "
+                     f"job's mean context); tok/s is per {len(rows)}-sequence step as run - the 3.1 GB of weights are "
+                     f"amortised over {len(rows)} tokens, not extrapolated to a 64-row batch; BLAS FP32 GEMMs"}
+    print(json.dumps(reference_line(
+        args, "decode tok/s", "tok/s", round(value, 4), round(1e3 * dt, 3), decode_step_config(args.sequences, world),
+        cpu, "f64 kernels / f32 GEMM", steps, 1,
+        f"each step is a bounded sample of the workload on the host cores; {steps} of the {args.steps} requested "
+        f"steps fit the {REFERENCE_ARM_BUDGET_S:.0f} s budget, after 1 warm-up step")), flush=True)
 
 
 def run_attention(args, rank, local_rank, world, barrier, dist):
@@ -596,10 +652,41 @@ def run_attention(args, rank, local_rank, world, barrier, dist):
     print(json.dumps(line), flush=True)
 
 
+def timed_repeats(fn, steps, repeats, barrier):
+    """`repeats` timed regions of exactly `steps` calls each (CUDA events, barrier + synchronize on both sides)."""
+    return [time_region(fn, steps, barrier) for _ in range(repeats)]
+
+
+def spread(tokens, steps, ms_list):
+    v = sorted(tokens * steps / (m * 1e-3) for m in ms_list)
+    return {"median": round(float(np.median(v)), 1), "min": round(v[0], 1), "max": round(v[-1], 1), "repeats": len(v)}
+
+
+def free_running_check(cfg, weights, quick: bool):
+    """The whole greedy decode of one wave of the workload (64 sequences, one of 32768 tokens, 256 new tokens)
+    through the shipped path, against the independent path (oracle/free_run.py). Returns the report without
+    its per-token arrays."""
+    from oracle import free_run
+    contexts = free_run.config5_wave_contexts(0xB200C0F5, 64, long_rows=1)
+    order = np.argsort(contexts)
+    rep = free_run.lockstep_decode(cfg, weights, contexts, 64 if quick else 256, seed=0x5EED0000,
+                                   cpu_audit_steps=(0,) if quick else (0, 255), cpu_audit_rows=[int(order[2])],
+                                   cpu_audit_divergences=2)
+    rep.pop("tokens_free_running")
+    listed = rep.pop("disagreement_list")
+    rep["audits_ok"] = free_run.audits_ok(rep)
+    rep["disagreement_margins"] = sorted(round(d["checker_margin_to_token"], 4) for d in listed)[-8:]
+    for au in rep["cpu_audits"]:
+        for k in list(au):
+            if isinstance(au[k], float):
+                au[k] = round(au[k], 5)
+    return rep
+
+
 def run_decode_step(args, rank, local_rank, world, barrier, dist):
     import torch
     from redline_llm_b200 import kernels as K
-    need = args.warmup + args.steps + 8
+    need = args.warmup + (2 * args.repeats + 1) * args.steps + 8
     w = DecodeStepWorkload(rank, world, new_tokens=max(256, need), total=args.sequences, overlap=not args.no_overlap,
                            linear=args.linear, vocab_projection=args.vocab_projection)
     peak, peak_kind = measured_peaks()
@@ -607,18 +694,17 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         for _ in range(args.warmup):
             w.step_e2e()          # also uploads real inputs for the resident-input timing below
         barrier()
-        ms = time_region(w.step, args.steps, barrier)
-    barrier()
-    ms_e2e = time_region(w.step_e2e, args.steps, barrier)
+        ms_all = timed_repeats(w.step, args.steps, args.repeats, barrier)
+        barrier()
+        ms_e2e_all = timed_repeats(w.step_e2e, args.steps, args.repeats, barrier)
     att_s, att_bytes = w.profile_attention()
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
+        t = torch.tensor(ms_all + ms_e2e_all, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every region: the slowest rank's time
+        ms_all, ms_e2e_all = t[:args.repeats].tolist(), t[args.repeats:].tolist()
+    ms, ms_e2e = float(np.median(ms_all)), float(np.median(ms_e2e_all))
     health = K.attention_health()
     linear_health = K.decode_linear_health()
-    if rank != 0:
-        return
     tokens = w.TOTAL
     # HBM bytes one step must move on this rank: the weights once per wave, every cached token's K/V once
     # (at the contexts the timed replays saw), the new tokens' K/V written
@@ -628,39 +714,47 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     value = tokens * args.steps / (ms * 1e-3)
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
     achieved = att_bytes / att_s / 1e9
-    line = {
-        "metric": "decode tok/s", "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-        "config": {"workload": w.name, "sequences": tokens, "sequences_per_gpu": w.tokens_per_step,
-                   "wave": DecodeStepWorkload.WAVE, "waves_per_gpu": len(w.engines), "new_tokens": 256,
-                   "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
-                   "router": "host-side: longest first, snake-dealt over 8 shards (every GPU serves 32/N of the "
-                             "32768-token sequences and the same number of cached tokens within 1 %)",
-                   "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter fused into QKV, SiLU into gate/up) "
-                            "FP16" if args.linear == "tcgen05" else "library (cuBLAS via torch.matmul), FP16"),
-                   "vocabulary_projection": ("own tcgen05 kernel" if w.vocab_projection == "tcgen05"
-                                             else "library GEMM (torch.matmul)"),
-                   "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
-                   "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2),
-                   "step_hbm_bytes_per_gpu": int(step_bytes), "step_GBps_per_gpu": round(step_gbs, 1),
-                   "step_frac_of_measured_hbm": round(step_gbs / peak, 4),
-                   "step_pct_of_8TBps": round(100 * step_gbs / 8000.0, 2)},
-        "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
-                     "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
-                     "traffic": int(att_bytes * ATTENTION_TRAFFIC_RATIO),
-                     "traffic_note": "dram read+write per launch scaled by units from the ncu capture at batch 64, "
-                                     "contexts 4096-8192 (profiles/paged_attention_split_kernel.txt): 1.008 x algorithmic",
-                     "algorithmic_bytes_per_launch": int(att_bytes),
-                     "us_per_launch": round(att_s * 1e6, 2),
-                     "timed": "CUDA events over graph replays of the step's 28 attention launches per wave "
-                              "(same inputs and layer pools as the step, cold L2)"},
-        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
-        "gpu_launches": w.launches_per_step * args.steps * world,
-        "clocks": clocks.summary(),
-        "check": {"attention_health": health, "linear_health": linear_health},
-    }
-    if not args.no_cpu_baseline and world == 1:
+    line = None
+    if rank == 0:
+        line = {
+            "metric": "decode tok/s", "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": decode_step_config(tokens, world),
+            "details": {
+                "sequences_per_gpu": w.tokens_per_step, "waves_per_gpu": len(w.engines),
+                "launch": "one CUDA-graph replay per wave", "prologue_overlap": not args.no_overlap,
+                "router": "host-side: longest first, snake-dealt over 8 shards (every GPU serves 32/N of the "
+                          "32768-token sequences and the same number of cached tokens within 1 %)",
+                "gemm": ("own tcgen05 weight-streaming kernel for the four linear layers of a block (RoPE + KV scatter "
+                         "fused into QKV, SiLU into gate/up) FP16" if args.linear == "tcgen05"
+                         else "library (cuBLAS via torch.matmul), FP16"),
+                "vocabulary_projection": ("own tcgen05 kernel" if w.vocab_projection == "tcgen05"
+                                          else "library GEMM (torch.matmul)"),
+                "cold_l2": "every step streams 3.1 GB of weights per wave and the waves' KV, far larger than L2",
+                "attention_pct_of_8TBps": round(100 * achieved / 8000.0, 2),
+                "step_hbm_bytes_per_gpu": int(step_bytes), "step_GBps_per_gpu": round(step_gbs, 1),
+                "step_frac_of_measured_hbm": round(step_gbs / peak, 4),
+                "step_pct_of_8TBps": round(100 * step_gbs / 8000.0, 2)},
+            "timing": {"repeats": args.repeats, "value": spread(tokens, args.steps, ms_all),
+                       "e2e": spread(tokens, args.steps, ms_e2e_all),
+                       "note": "value / e2e / ms_per_step are the medians of `repeats` timed regions of `steps` steps each"},
+            "roofline": {"bound": "hbm", "kernel": "PagedAttentionSplitKernel", "achieved": round(achieved, 1),
+                         "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                         "traffic": int(att_bytes * ATTENTION_TRAFFIC_RATIO),
+                         "traffic_note": "dram read+write per launch scaled by units from the ncu capture at batch 64, "
+                                         "contexts 4096-8192 (profiles/paged_attention_split_kernel.txt): 1.008 x algorithmic",
+                         "algorithmic_bytes_per_launch": int(att_bytes),
+                         "us_per_launch": round(att_s * 1e6, 2),
+                         "timed": "CUDA events over graph replays of the step's 28 attention launches per wave "
+                                  "(same inputs and layer pools as the step, cold L2)"},
+            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h},
+            "gpu_launches": w.launches_per_step * args.steps * 2 * args.repeats * world,
+            "clocks": clocks.summary(),
+            "check": {"attention_health": health, "linear_health": linear_health},
+        }
+    cfg, weights = w.cfg, w.weights
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
         rows = sample_rows(w, 2)
         dt, cpu_tok, cpu_logits, threads, kind = cpu_decode_step(w, rows, True)
         e = w.engines[0]
@@ -675,9 +769,40 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
         line["check"].update({"step_logits_max_abs_vs_cpu": float(np.abs(gpu_logits - cpu_logits).max()),
                               "step_logits_scale": float(np.abs(cpu_logits).max()),
                               "greedy_tokens_equal_cpu": bool((gpu_tok == cpu_tok).all())})
-    if not args.no_kernel_table:
-        del w
+    del w
+    torch.cuda.empty_cache()
+    # The same step with the library GEMMs left in place (cuBLAS through torch.matmul for the four linear layers of
+    # a block and the vocabulary projection; this library's norm / RoPE / scatter / attention / SiLU kernels around
+    # them): the configuration in which only the non-GEMM kernels are replaced.
+    if args.linear == "tcgen05" and not args.no_library_leg:
+        reps = max(1, min(3, args.repeats))
+        wl_lib = DecodeStepWorkload(rank, world, new_tokens=max(256, args.warmup + (2 * reps + 1) * args.steps + 8),
+                                    total=args.sequences, overlap=not args.no_overlap, linear="library")
+        for _ in range(args.warmup):
+            wl_lib.step_e2e()
+        barrier()
+        lib_ms = timed_repeats(wl_lib.step, args.steps, reps, barrier)
+        barrier()
+        lib_e2e = timed_repeats(wl_lib.step_e2e, args.steps, reps, barrier)
+        if world > 1:
+            t = torch.tensor(lib_ms + lib_e2e, device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            lib_ms, lib_e2e = t[:reps].tolist(), t[reps:].tolist()
+        if rank == 0:
+            line["value_library_gemm"] = spread(tokens, args.steps, lib_ms)["median"]
+            line["e2e_library_gemm"] = spread(tokens, args.steps, lib_e2e)["median"]
+            line["timing"]["value_library_gemm"] = spread(tokens, args.steps, lib_ms)
+            line["timing"]["e2e_library_gemm"] = spread(tokens, args.steps, lib_e2e)
+            line["gpu_launches"] += wl_lib.launches_per_step * args.steps * 2 * reps * world
+        del wl_lib
         torch.cuda.empty_cache()
+    if rank != 0:
+        return
+    if not args.no_free_running and world == 1:
+        line["check"]["free_running"] = free_running_check(cfg, weights, args.quick_check)
+    del weights
+    torch.cuda.empty_cache()
+    if not args.no_kernel_table:
         line["kernels"] = kernel_table(peak)
     print(json.dumps(line), flush=True)
 
@@ -706,6 +831,10 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain attention launches (no programmatic dependent launch of the prologue)")
     ap.add_argument("--kernel", default=None, help="kernels workload: only entries whose name contains this")
+    ap.add_argument("--repeats", type=int, default=5, help="decode_step: timed regions of --steps steps each; the line carries the median")
+    ap.add_argument("--no-library-leg", action="store_true", help="decode_step: skip the extra timed pass with the library GEMMs")
+    ap.add_argument("--no-free-running", action="store_true", help="decode_step: skip the whole-decode greedy check (N=1 only)")
+    ap.add_argument("--quick-check", action="store_true", help="decode_step: 64 instead of 256 tokens in the whole-decode check")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)

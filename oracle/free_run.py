@@ -64,7 +64,7 @@ def make_checker_engine(cfg, weights, kv_pool_gb, max_batch, max_seq_len, device
 def lockstep_decode(cfg, weights, contexts: Sequence[int], new_tokens: int, seed: int, device: int = 0,
                     engine_kwargs: Optional[dict] = None, cpu_audit_steps: Sequence[int] = (),
                     cpu_audit_rows: Sequence[int] = (), cpu_audit_divergences: int = 0,
-                    cpu_row_limit: int = 8192, logit_tol_frac: float = 0.03) -> Dict:
+                    cpu_row_limit: int = 8192, logit_tol_frac: float = 0.01) -> Dict:
     """Decodes `new_tokens` tokens of len(contexts) cached sequences (synthetic seeded K/V, as the benchmark's)
     free-running through the default engine and teacher-forced through the checker engine; returns the
     report described in the module docstring. `logit_tol_frac` x (largest |logit| seen) is the logit
