@@ -426,7 +426,12 @@ def kernel_table(peak, only=None, eager=False):
         if want(big[2]):
             secs = timed(lambda i: K.launch_rope_kv_scatter(qkv[i], 2048, pools[i], row, 0, pos, t, 12, 2, 128, 1e6),
                          nbuf, iters=5)
-            report(big[2], secs, rope_bytes + t * 1536 + t // 4, "prompt chunk in one launch, cold L2")
+
+            def ref_pair_big(i):
+                R.launch_rope_inplace(qkv[i], qkv[i], 2048, 2048, pos, t, 12, 2, 128, 1e6, k_offset=1536)
+                R.launch_kv_scatter(pools[i], qkv[i], qkv[i], 2048, 2048, row, 0, pos, t, 2, 128, k_offset=1536, v_offset=1792)
+            report(big[2], secs, rope_bytes + t * 1536 + t // 4, "prompt chunk in one launch, cold L2; ref_us = the "
+                   "reference's two launches", timed(ref_pair_big, nbuf, iters=5) if have_ref else None)
         del qkv, pools
     # the two prompt-side launchers at one chunk of a long prompt: the gather of a 16384-token context into
     # the dense staging views, and the causal softmax of a 512-row chunk against 8192 keys
