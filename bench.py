@@ -116,14 +116,17 @@ def graphed(fn):
     return g.replay
 
 
-def time_region(fn, steps, stream_sync):
-    """CUDA-event time (ms) of `steps` calls of fn on the current stream."""
+def time_region(fn, steps, stream_sync, finish=None):
+    """CUDA-event time (ms) of `steps` calls of fn on the current stream; `finish` (e.g. retiring steps still in
+    flight) runs inside the region, after the last call."""
     import torch
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     stream_sync()
     start.record()
     for _ in range(steps):
         fn()
+    if finish is not None:
+        finish()
     end.record()
     stream_sync()
     return start.elapsed_time(end)
@@ -240,9 +243,10 @@ class DecodeStepWorkload:
             + wts.lm_head.numel() * 2  # streamed once per wave per step (the embedding rows gathered are negligible)
         self.kv_bytes_per_token = self.cfg.layers * 2 * self.cfg.kv_heads * self.cfg.head_dim * 2
         # own kernels per layer: 2 norms and attention, plus RoPE+scatter and SiLU beside library GEMMs, or the
-        # four linear layers (RoPE+scatter fused into the QKV product, SiLU into gate/up); + embed, final norm, argmax
+        # four linear layers (RoPE+scatter fused into the QKV product, SiLU into gate/up); + embed, final norm, argmax,
+        # the device-side input advance
         # and, with the own linear kernel, the vocabulary projection
-        self.launches_per_step = len(self.engines) * (self.cfg.layers * (7 if linear == "tcgen05" else 5) + 3
+        self.launches_per_step = len(self.engines) * (self.cfg.layers * (7 if linear == "tcgen05" else 5) + 4
                                                       + (1 if self.vocab_projection == "tcgen05" else 0))
         self.h2d = self.d2h = 0
 
@@ -250,16 +254,27 @@ class DecodeStepWorkload:
         for e in self.engines:
             e.exec.run(self.WAVE)
 
-    def step_e2e(self):  # the public API: host mirrors -> H2D -> replay -> D2H of the sampled tokens
-        # every wave's step is begun (mirrors filled, H2D, graph replay and D2H enqueued) before the first
-        # one is ended, so the host work of wave i+1 overlaps the device work of wave i
+    def step_e2e(self):
+        """One step of every wave through the public API: pinned H2D of the step's control block (and of ids /
+        positions / seq_lens / changed table rows whenever the host has to rebuild them), graph replay, D2H of
+        the sampled tokens. `step_pipelined` launches a wave's next step behind the one in flight - the device
+        feeds the sampled tokens back itself - and then retires the older one, so the host's bookkeeping runs
+        under the device's work; every step's tokens are still read on the host, one call late."""
         self.h2d = self.d2h = 0
         for e in self.engines:
-            e.step_begin()
+            e.step_pipelined()
             self.h2d += e.exec.h2d_bytes
             self.d2h += 4 * self.WAVE
+
+    def drain(self):
         for e in self.engines:
-            e.step_end()
+            e.drain()
+
+    def resident_inputs(self):
+        """Uploads every wave's next inputs once, device-side advance off: `step()` then replays over them."""
+        self.drain()
+        for e in self.engines:
+            assert e.upload_next_inputs() == self.WAVE
 
     def profile_attention(self, replays: int = 3):
         """The attention kernel's own duration inside this step: for every wave, the step's 28 attention
@@ -657,9 +672,9 @@ def run_attention(args, rank, local_rank, world, barrier, dist):
     print(json.dumps(line), flush=True)
 
 
-def timed_repeats(fn, steps, repeats, barrier):
+def timed_repeats(fn, steps, repeats, barrier, finish=None):
     """`repeats` timed regions of exactly `steps` calls each (CUDA events, barrier + synchronize on both sides)."""
-    return [time_region(fn, steps, barrier) for _ in range(repeats)]
+    return [time_region(fn, steps, barrier, finish) for _ in range(repeats)]
 
 
 def spread(tokens, steps, ms_list):
@@ -697,11 +712,14 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
     peak, peak_kind = measured_peaks()
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
-            w.step_e2e()          # also uploads real inputs for the resident-input timing below
+            w.step_e2e()
+        w.resident_inputs()       # nothing in flight; every wave's next inputs on the device, advance off
         barrier()
         ms_all = timed_repeats(w.step, args.steps, args.repeats, barrier)
         barrier()
-        ms_e2e_all = timed_repeats(w.step_e2e, args.steps, args.repeats, barrier)
+        # each region launches exactly `steps` steps per wave and retires them all before its end event
+        ms_e2e_all = timed_repeats(w.step_e2e, args.steps, args.repeats, barrier, finish=w.drain)
+        w.resident_inputs()       # for the attention profile and the CPU check below
     att_s, att_bytes = w.profile_attention()
     if world > 1:
         t = torch.tensor(ms_all + ms_e2e_all, device="cuda", dtype=torch.float64)
@@ -785,10 +803,11 @@ def run_decode_step(args, rank, local_rank, world, barrier, dist):
                                     total=args.sequences, overlap=not args.no_overlap, linear="library")
         for _ in range(args.warmup):
             wl_lib.step_e2e()
+        wl_lib.resident_inputs()
         barrier()
         lib_ms = timed_repeats(wl_lib.step, args.steps, reps, barrier)
         barrier()
-        lib_e2e = timed_repeats(wl_lib.step_e2e, args.steps, reps, barrier)
+        lib_e2e = timed_repeats(wl_lib.step_e2e, args.steps, reps, barrier, finish=wl_lib.drain)
         if world > 1:
             t = torch.tensor(lib_ms + lib_e2e, device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

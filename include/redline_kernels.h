@@ -159,6 +159,20 @@ int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, c
                                             int32_t head_dim, float scale, void* stream);
 
 /*
+ * Decode input plumbing on the device: after a step's greedy argmax, prepare the next step's inputs in
+ * place - input_ids[i] <- control[1 + i] if that is >= 0 (a scripted token), else sampled_tokens[i];
+ * positions[i] <- seq_lens[i]; seq_lens[i] += 1 - for every row with seq_len > 0, when control[0] != 0
+ * (control = int32[1 + num_rows] in device memory; control[0] == 0 leaves everything as it is). Placed at
+ * the end of the captured decode sequence it lets an executor replay the graph of an unchanged batch
+ * without reading the tokens back first; block tables must then already hold the page the next token
+ * falls into. Replaces, on the device, the host loop of src/core/model_executor.cpp:784-874 for the
+ * steady state (the reference rebuilds and uploads the three arrays every step, :876-892).
+ */
+int rl_launch_decode_advance(int32_t* input_ids, int32_t* positions, int32_t* seq_lens,
+                             const int32_t* sampled_tokens, const int32_t* control, int32_t num_rows,
+                             void* stream);
+
+/*
  * Device-side health of the attention kernel on the current device: 0 when every
  * page load it waited for arrived, 1 when a bounded wait gave up (the output of
  * that launch is then undefined). Synchronises the device; meant for tests and

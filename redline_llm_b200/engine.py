@@ -293,7 +293,14 @@ class ModelExecutor:
         self.h_step_inputs = torch.zeros(3, B, dtype=i32).pin_memory()
         self.h_ids, self.h_pos, self.h_lens = self.h_step_inputs[0], self.h_step_inputs[1], self.h_step_inputs[2]
         self.h_tables = torch.zeros(B, self.mbps, dtype=i32).pin_memory()
-        self.h_tokens = torch.zeros(B, dtype=i32).pin_memory()
+        # Sampled tokens come back through a ring of two pinned buffers, each with its event, so that a second
+        # step can be in flight while the host still reads the first one's tokens.
+        self.h_tokens = torch.zeros(2, B, dtype=i32).pin_memory()
+        # Control block of the device-side input advance (the last kernel of the decode sequence): [0] advance
+        # on/off, [1 + i] a scripted token for row i or -1. Uploaded every step from a ring of two pinned copies.
+        self.ctrl = torch.zeros(1 + B, dtype=i32, device=device)
+        self.h_ctrl = torch.zeros(2, 1 + B, dtype=i32).pin_memory()
+        self._np_ctrl = self.h_ctrl.numpy()
         self._np_ids, self._np_pos = self.h_ids.numpy(), self.h_pos.numpy()
         self._np_lens, self._np_tables = self.h_lens.numpy(), self.h_tables.numpy()
         self.row_owner: List[Optional[int]] = [None] * B   # request id whose table sits in row i
@@ -304,7 +311,7 @@ class ModelExecutor:
         self._last_rows = 0
         self._last_tokens = None                            # tokens appended by the previous step (numpy)
         self.graphs: Dict[int, object] = {}
-        self.tokens_ready = torch.cuda.Event()   # recorded behind the D2H copy of the sampled tokens
+        self.tokens_ready = [torch.cuda.Event(), torch.cuda.Event()]   # recorded behind the D2H copy of the sampled tokens
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
         self.prefill_logits = None
@@ -380,6 +387,11 @@ class ModelExecutor:
         else:
             torch.matmul(normed, w.lm_head.t(), out=self.logits[:rows])
         K.launch_greedy_argmax(self.tokens, self.logits, rows, cfg.vocab)
+        # next step's ids / positions / seq_lens from this step's tokens, on the device (a no-op while
+        # control[0] == 0, as during warm-up and capture; the host still uploads all three whenever the batch changed)
+        advance = getattr(K, "launch_decode_advance", None)
+        if advance is not None:
+            advance(self.ids, self.positions, self.seq_lens, self.tokens, self.ctrl, rows)
 
     def warm_and_capture(self, buckets: Sequence[int]) -> None:
         """Eager warm-up of every bucket (first launches happen outside capture), then one graph each."""
@@ -451,14 +463,37 @@ class ModelExecutor:
                 self.row_len[i] = nb
                 self.dirty_rows.append(i)
 
-    def upload(self, rows: int) -> None:
-        self.step_inputs.copy_(self.h_step_inputs, non_blocking=True)
-        if len(self.dirty_rows) > rows // 2:
+    def _grow_rows(self, batch: List[Request]) -> None:
+        """Table rows of an unchanged batch: append the pages the requests gained since the last upload."""
+        tab = self._np_tables
+        self.dirty_rows = []
+        for i, r in enumerate(batch):
+            nb = len(r.blocks)
+            if self.row_len[i] != nb:
+                tab[i, self.row_len[i]:nb] = r.blocks[self.row_len[i]:nb]
+                self.row_len[i] = nb
+                self.dirty_rows.append(i)
+
+    def upload(self, rows: int, slot: int = 0, scripted: Optional[Sequence[int]] = None, advance: bool = False,
+               inputs: bool = True) -> None:
+        """H2D of one step's inputs from the pinned mirrors: the control block always; ids / positions / seq_lens
+        unless the device has advanced them itself (`inputs=False`); the table rows that changed."""
+        c = self._np_ctrl[slot]
+        c[0] = 1 if advance else 0
+        c[1:] = -1
+        if scripted is not None:
+            c[1:1 + len(scripted)] = scripted
+        self.ctrl.copy_(self.h_ctrl[slot], non_blocking=True)
+        if inputs:
+            self.step_inputs.copy_(self.h_step_inputs, non_blocking=True)
+        whole = len(self.dirty_rows) > rows // 2
+        if whole:
             self.tables[:rows].copy_(self.h_tables[:rows], non_blocking=True)
         else:
             for i in self.dirty_rows:
                 self.tables[i].copy_(self.h_tables[i], non_blocking=True)
-        self.h2d_bytes = self.h_step_inputs.numel() * 4 + 4 * self.mbps * (rows if len(self.dirty_rows) > rows // 2 else len(self.dirty_rows))
+        self.h2d_bytes = (self.h_ctrl[slot].numel() * 4 + (self.h_step_inputs.numel() * 4 if inputs else 0)
+                          + 4 * self.mbps * (rows if whole else len(self.dirty_rows)))
 
     def run(self, rows: int) -> None:
         g = self.graphs.get(rows)
@@ -471,13 +506,13 @@ class ModelExecutor:
         self.download_begin(rows)
         return self.download_end(rows)
 
-    def download_begin(self, rows: int) -> None:
-        self.h_tokens[:rows].copy_(self.tokens[:rows], non_blocking=True)
-        self.tokens_ready.record()
+    def download_begin(self, rows: int, slot: int = 0) -> None:
+        self.h_tokens[slot, :rows].copy_(self.tokens[:rows], non_blocking=True)
+        self.tokens_ready[slot].record()
 
-    def download_end(self, rows: int):
-        self.tokens_ready.synchronize()
-        return self.h_tokens[:rows].tolist()
+    def download_end(self, rows: int, slot: int = 0):
+        self.tokens_ready[slot].synchronize()
+        return self.h_tokens[slot, :rows].tolist()
 
     # ---- prompt ingestion (not on the hot path): chunked, eager, the reference's gather/GEMM/softmax/GEMM composite
     def prefill_chunk(self, r: Request, start: int, end: int) -> Optional[int]:
@@ -543,7 +578,8 @@ class Engine:
                  debug_dump_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
                  device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
                  graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True,
-                 decode_linear: str = "tcgen05", vocab_projection: Optional[str] = None):
+                 decode_linear: str = "tcgen05", vocab_projection: Optional[str] = None,
+                 device_feedback: bool = True):
         import torch
         if admission_policy != "reserve_full":
             raise ValueError("only the reserve_full admission policy is provided")
@@ -577,7 +613,11 @@ class Engine:
             buckets = [b for b in buckets if b in set(graph_buckets)]
         self.exec.warm_and_capture(buckets)
         self._next_id = 0
-        self._pending = None   # a step begun and not yet ended
+        # Steps begun and not yet ended, oldest first. One, unless `device_feedback` lets a second decode step of
+        # the same batch be launched on the tokens the first one leaves on the device (try_step_begin).
+        self._queue: deque = deque()
+        self.device_feedback = bool(device_feedback)
+        self._slot = 0
         self._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
         self._hist = {b: 0 for b in BUCKETS}
 
@@ -608,52 +648,135 @@ class Engine:
     # forward pass without waiting for it; step_end() waits for the sampled tokens and returns what step()
     # returns. Between the two the host is free to begin the steps of other engines. step() is the pair.
     def step_begin(self) -> None:
-        if self._pending is not None:
+        if self._queue:
             raise RuntimeError("step_begin: the previous step has not been ended")
         plan = self.scheduler.plan_step()
         self._stats["steps"] += 1
         if plan[0] == "idle":
-            self._pending = ("done", [])
+            self._queue.append(("done", []))
             return
         if plan[0] == "flush":
             out = []
             for r in plan[1]:
                 self.scheduler.release(r)
                 out.append((r.req_id, -1, True, r.reason))
-            self._pending = ("done", out)
+            self._queue.append(("done", out))
             return
         if plan[0] == "prefill":
             _, r, start, end = plan
             tok = self.exec.prefill_chunk(r, start, end)
             self._stats["prefill_tokens"] += end - start
             if tok is None:
-                self._pending = ("done", [])
+                self._queue.append(("done", []))
                 return
             r.cached = len(r.prompt)
-            self._pending = ("done", [self.scheduler.complete(r, tok)])
+            self._queue.append(("done", [self.scheduler.complete(r, tok)]))
             return
         batch = plan[1]
         rows = select_bucket(max(len(batch), self.pad_eager_to_bucket))
         self.exec.fill_mirrors(batch, rows)
-        self.exec.upload(rows)
+        self._slot ^= 1
+        self.exec.upload(rows, self._slot, self._scripted(batch, 0), advance=self.device_feedback)
         self.exec.run(rows)
-        self.exec.download_begin(rows)
-        self._pending = ("decode", list(batch), rows)
+        self.exec.download_begin(rows, self._slot)
+        self._queue.append(("decode", list(batch), rows, self._slot))
+
+    @staticmethod
+    def _scripted(batch: List[Request], ahead: int) -> List[int]:
+        """The teacher-forcing token of each request's output number len(output) + ahead, or -1."""
+        out = []
+        for r in batch:
+            k = len(r.output) + ahead
+            out.append(r.forced_tokens[k] if r.forced_tokens is not None and k < len(r.forced_tokens) else -1)
+        return out
+
+    def try_step_begin(self) -> bool:
+        """step_begin() when nothing is in flight. With one decode step in flight and `device_feedback` on, launches
+        the NEXT decode step of the same batch right behind it - its token ids, positions and seq_lens are the
+        ones the step in flight leaves on the device (rl_launch_decode_advance), so the host has not had to read
+        that step's tokens - provided the batch cannot change in between: nobody waits for admission and no
+        request reaches max_new_tokens with the step in flight. A request that stops on an end-of-sequence
+        token is noticed one step late; the extra step's token for it is discarded (its K/V went to a page the
+        request had reserved). Returns False, launching nothing, when the step in flight must be ended first."""
+        if not self._queue:
+            self.step_begin()
+            return True
+        last = self._queue[-1]
+        if not self.device_feedback or len(self._queue) >= 2 or last[0] != "decode" or self.scheduler.waiting:
+            return False
+        _, batch, rows, _ = last
+        running = self.scheduler.running[: BUCKETS[-1]]
+        if len(running) != len(batch) or any(a is not b for a, b in zip(running, batch)):
+            return False
+        if any(r.finished or len(r.output) + 2 > r.max_new_tokens for r in batch):
+            return False
+        for r in batch:
+            if r.seq_len + 1 > self.exec.mbps * KV_BLOCK:
+                return False
+            self.scheduler._grow(r, r.seq_len + 1)      # the step in flight appends one token, this one the next
+        self._stats["steps"] += 1
+        ex = self.exec
+        ex._grow_rows(batch)
+        ex._last_batch_ids = None                        # the host mirrors of ids / positions / lens are now stale
+        self._slot ^= 1
+        ex.upload(rows, self._slot, self._scripted(batch, 1), advance=True, inputs=False)
+        ex.run(rows)
+        ex.download_begin(rows, self._slot)
+        self._queue.append(("decode", batch, rows, self._slot))
+        return True
+
+    @property
+    def in_flight(self) -> int:
+        return len(self._queue)
+
+    def step_pipelined(self) -> List[Tuple[int, int, bool, str]]:
+        """One call per step for a driver that keeps the GPU busy: launch the next step if that needs no result
+        of the one in flight, then end the oldest step if two are in flight (or nothing could be launched).
+        Results therefore arrive one call late while a batch is in its steady state; call drain() at the end."""
+        launched = self.try_step_begin()
+        if len(self._queue) >= 2 or (not launched and self._queue):
+            return self.step_end()
+        return []
+
+    def drain(self) -> List[Tuple[int, int, bool, str]]:
+        out = []
+        while self._queue:
+            out.extend(self.step_end())
+        return out
+
+    def upload_next_inputs(self) -> int:
+        """Plans the next decode batch and uploads its inputs without running it, with the device-side advance
+        switched off: afterwards `exec.run(rows)` can be replayed any number of times over the same resident
+        inputs (the benchmark's device-only timing). Returns the number of batch rows (0 when no decode step
+        is due)."""
+        if self._queue:
+            raise RuntimeError("upload_next_inputs: a step is in flight")
+        plan = self.scheduler.plan_step()
+        if plan[0] != "decode":
+            return 0
+        batch = plan[1]
+        rows = select_bucket(max(len(batch), self.pad_eager_to_bucket))
+        self.exec.fill_mirrors(batch, rows)
+        self.exec._last_batch_ids = None    # no step follows this upload: the next fill starts from the requests
+        self.exec.upload(rows, self._slot, None, advance=False)
+        return rows
 
     def step_end(self) -> List[Tuple[int, int, bool, str]]:
-        if self._pending is None:
+        if not self._queue:
             raise RuntimeError("step_end without step_begin")
-        pending, self._pending = self._pending, None
+        pending = self._queue.popleft()
         if pending[0] == "done":
             return pending[1]
-        _, batch, rows = pending
-        toks = self.exec.download_end(rows)
+        _, batch, rows, slot = pending
+        toks = self.exec.download_end(rows, slot)
         self._stats["graph_replays" if rows in self.exec.graphs else "eager_decodes"] += 1
-        self._stats["decode_tokens"] += len(batch)
         self._hist[rows] += 1
         out = []
         for r, t in zip(batch, toks):
+            if r.finished:      # stopped by the previous step while this one was already in flight
+                continue
             r.cached += 1
+            self._stats["decode_tokens"] += 1
             out.append(self.scheduler.complete(r, t))
         # what the next step feeds back: the APPENDED tokens (the scripted ones under teacher forcing); any
         # finished request changes the batch, which fill_mirrors notices by itself

@@ -25,7 +25,7 @@ ABI_SYMBOLS = (
     "rl_launch_embed_gather", "rl_launch_greedy_argmax", "rl_launch_rope_kv_scatter",
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
-    "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter",
+    "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter", "rl_launch_decode_advance",
 )
 
 
@@ -67,6 +67,7 @@ def lib() -> C.CDLL:
         L.rl_launch_qkv_rope_kv_scatter.argtypes = [vp, i64, vp, i64, vp, i64, vp, i32, i32, vp, vp, i64, vp,
                                                     i32, i32, i32, f32, vp]
         L.rl_decode_linear_set_stages.argtypes = [C.c_int]
+        L.rl_launch_decode_advance.argtypes = [vp, vp, vp, vp, vp, i32, vp]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -183,6 +184,14 @@ def launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidde
 def launch_greedy_argmax(out_tokens, logits, num_seqs, vocab_size, stream=None):
     _check(lib().rl_launch_greedy_argmax(out_tokens.data_ptr(), _ptr(logits), num_seqs, vocab_size,
                                          _stream(stream)), "LaunchGreedyArgmax")
+
+
+def launch_decode_advance(input_ids, positions, seq_lens, sampled_tokens, control, num_rows, stream=None):
+    """Next step's inputs from this step's sampled tokens, in place on the device (control = int32[1 + rows]:
+    [0] advance on/off, [1 + i] a scripted token for row i or -1)."""
+    _check(lib().rl_launch_decode_advance(input_ids.data_ptr(), positions.data_ptr(), seq_lens.data_ptr(),
+                                          sampled_tokens.data_ptr(), control.data_ptr(), num_rows,
+                                          _stream(stream)), "decode advance")
 
 
 def set_attention_prologue_overlap(enable: bool) -> None:

@@ -104,55 +104,83 @@ def test_randomised_churn_never_leaks_blocks():
     assert len(out) == 60 and a.free_blocks == 199 and a.reserved == 0
 
 
+class StubExecutor:
+    """Stands in for the device: a 'decode step' samples token (31 * id + 7 * seq_len) % 13 for every live row,
+    and - as the last kernel of the real decode sequence does - advances ids / seq_lens in place when the
+    uploaded control block says so, feeding a scripted token where one is given."""
+    graphs = {}
+    h2d_bytes = 0
+    mbps = 16
+    _last_tokens = None
+    _last_batch_ids = None
+
+    def __init__(self):
+        self.calls = []
+        self.ids, self.lens, self.tokens = [0] * 64, [0] * 64, [0] * 64
+        self.host, self.ctrl, self.out = [], (False, []), {}
+
+    def fill_mirrors(self, batch, rows):
+        self.calls.append(("fill", len(batch), rows))
+        self.host = [((r.output[-1] if r.output else r.prompt[-1]), r.seq_len) for r in batch]
+        self.host += [(0, 0)] * (rows - len(batch))
+
+    def _grow_rows(self, batch):
+        self.calls.append(("grow", len(batch)))
+
+    def upload(self, rows, slot=0, scripted=None, advance=False, inputs=True):
+        self.calls.append(("upload", rows, inputs))
+        if inputs:
+            for i, (tok, ln) in enumerate(self.host):
+                self.ids[i], self.lens[i] = tok, ln
+        self.ctrl = (advance, list(scripted or []))
+
+    def run(self, rows):
+        self.calls.append(("run", rows))
+        for i in range(rows):
+            self.tokens[i] = (31 * self.ids[i] + 7 * self.lens[i]) % 13
+        advance, scripted = self.ctrl
+        for i in range(rows):
+            if advance and self.lens[i] > 0:
+                self.ids[i] = scripted[i] if i < len(scripted) and scripted[i] >= 0 else self.tokens[i]
+                self.lens[i] += 1
+
+    def download_begin(self, rows, slot=0):
+        self.calls.append(("d2h", rows))
+        self.out[slot] = list(self.tokens[:rows])
+
+    def download_end(self, rows, slot=0):
+        self.calls.append(("wait", rows))
+        return self.out[slot]
+
+    def prefill_chunk(self, r, start, end):
+        self.calls.append(("prefill", start, end))
+        r.prefilled = end
+        return 5 if end == len(r.prompt) else None
+
+
+def stub_engine(requests, device_feedback=True, max_batch=4, eos=7):
+    from collections import deque
+
+    from redline_llm_b200.engine import Engine, ModelConfig
+    e = Engine.__new__(Engine)
+    e.cfg = ModelConfig()
+    e.allocator = BlockAllocator(64)
+    e.scheduler = Scheduler(e.allocator, max_batch, 256, 16, eos)
+    e.exec = StubExecutor()
+    e.max_seq_len, e.max_batch, e.pad_eager_to_bucket = 256, max_batch, 0
+    e._next_id, e._queue, e._slot, e.device_feedback = 0, deque(), 0, device_feedback
+    e._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
+    e._hist = {b: 0 for b in BUCKETS}
+    for rq in requests:
+        e.add_request(*rq[:2], **(rq[2] if len(rq) > 2 else {}))
+    return e
+
+
 def test_step_halves_with_a_scripted_executor():
     """Engine.step_begin / step_end (the two halves a multi-engine driver interleaves) over a stub executor:
     same results as step(), one pending step at a time, prefill chunks complete inside step_begin."""
-    from redline_llm_b200.engine import Engine, ModelConfig
-
-    class StubExecutor:
-        graphs = {}
-        h2d_bytes = 0
-        _last_tokens = None
-
-        def __init__(self):
-            self.calls = []
-
-        def fill_mirrors(self, batch, rows):
-            self.calls.append(("fill", len(batch), rows))
-
-        def upload(self, rows):
-            self.calls.append(("upload", rows))
-
-        def run(self, rows):
-            self.calls.append(("run", rows))
-
-        def download_begin(self, rows):
-            self.calls.append(("d2h", rows))
-
-        def download_end(self, rows):
-            self.calls.append(("wait", rows))
-            return [3] * rows
-
-        def prefill_chunk(self, r, start, end):
-            self.calls.append(("prefill", start, end))
-            r.prefilled = end
-            return 5 if end == len(r.prompt) else None
-
-    def make():
-        e = Engine.__new__(Engine)
-        e.cfg = ModelConfig()
-        e.allocator = BlockAllocator(64)
-        e.scheduler = Scheduler(e.allocator, 4, 256, 16, e.cfg.eos_token_id)
-        e.exec = StubExecutor()
-        e.max_seq_len, e.max_batch, e.pad_eager_to_bucket = 256, 4, 0
-        e._next_id, e._pending = 0, None
-        e._stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, graph_replays=0, eager_decodes=0)
-        e._hist = {b: 0 for b in BUCKETS}
-        e.add_request(list(range(1, 21)), 3, ignore_eos=True)
-        e.add_request([4, 5], 2, ignore_eos=True)
-        return e
-
-    whole, halves = make(), make()
+    reqs = [(list(range(1, 21)), 3, dict(ignore_eos=True)), ([4, 5], 2, dict(ignore_eos=True))]
+    whole, halves = stub_engine(reqs), stub_engine(reqs)
     want, got = [], []
     for _ in range(12):
         want.append(whole.step())
@@ -170,6 +198,47 @@ def test_step_halves_with_a_scripted_executor():
     assert calls[i + 1][0] == "d2h" and calls[i + 2][0] == "wait"
     flat = [t for step in got for t in step]
     assert sorted(r[0] for r in flat if r[2]) == [0, 1] and all(r[3] in ("", "length") for r in flat)
+
+
+def test_pipelined_steps_on_device_fed_tokens_equal_one_step_at_a_time():
+    """try_step_begin launches the next decode step behind the one in flight - the device advances ids and
+    seq_lens itself - while the batch cannot change; results (tokens as the engine sampled them, finish flags,
+    reasons) and final accounting must equal stepping one at a time, including a stop on an end-of-sequence
+    token noticed one step late, length stops, teacher forcing (with an end-of-sequence token in the script),
+    and later admissions."""
+    reqs = [([3, 1, 4, 1, 5], 12, dict(ignore_eos=True)),
+            ([2, 7, 1], 9),                                          # stops when the stub samples token 7
+            (list(range(1, 30)), 20, dict(forced_tokens=[1, 2, 3, 4, 5, 6, 8, 7, 9, 9, 9])),   # scripted stop at 7
+            ([9], 6, dict(ignore_eos=True, forced_tokens=[11, 12])),
+            ([5, 5], 15), ([6], 4, dict(ignore_eos=True))]          # admitted once rows free up (max_batch 4)
+
+    def collect(e, stepper):
+        out = {}
+        for _ in range(400):
+            for rid, tok, fin, why in stepper(e):
+                out.setdefault(rid, []).append((tok, fin, why))
+            s = e.stats()
+            if s["running"] == 0 and s["waiting"] == 0 and not e.in_flight:
+                break
+        return out
+
+    sync = stub_engine(reqs, device_feedback=False)
+    want = collect(sync, lambda e: e.step())
+    pipe = stub_engine(reqs)
+    got = collect(pipe, lambda e: e.step_pipelined())
+    assert got == want
+    assert any(f and w == "eos" for v in want.values() for (_, f, w) in v)
+    ws, gs = sync.stats(), pipe.stats()
+    for k in ("prefill_tokens", "decode_tokens", "free_blocks", "reserved_blocks", "aborts", "running", "waiting"):
+        assert ws[k] == gs[k], k
+    assert gs["free_blocks"] == gs["total_blocks"] - 1 and gs["reserved_blocks"] == 0
+    # steady-state steps really were launched without the host inputs: uploads with inputs=False exist,
+    # and two steps were in flight at some point
+    assert any(c[0] == "upload" and c[2] is False for c in pipe.exec.calls)
+    runs = [i for i, c in enumerate(pipe.exec.calls) if c[0] == "run"]
+    assert any(not any(c[0] == "wait" for c in pipe.exec.calls[a:b]) for a, b in zip(runs, runs[1:]))
+    # with feedback off nothing is ever launched ahead
+    assert all(c[2] for c in sync.exec.calls if c[0] == "upload")
 
 
 def test_balanced_order_gives_every_replica_the_same_load():

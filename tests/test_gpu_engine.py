@@ -128,6 +128,45 @@ def test_cuda_graph_replay_equals_eager_token_for_token(weights):
     assert outs[0] == outs[1]
 
 
+def test_pipelined_steps_on_device_fed_tokens_equal_synchronous_steps(weights):
+    """step_pipelined keeps two decode steps in flight: the second reads the token ids, positions and seq_lens the
+    first one's last kernel left on the device, and table rows are extended ahead of time. Tokens, finish
+    reasons and block accounting equal one-step-at-a-time stepping with the feedback switched off - with
+    requests of different lengths (the batch shrinks), natural end-of-sequence stops noticed one step late,
+    teacher forcing, and a waiting request admitted in between."""
+    rng = np.random.default_rng(13)
+    vocab = CFG.vocab
+    reqs = [(rng.integers(0, vocab - 1, 37).tolist(), 40, dict(ignore_eos=True)),
+            (rng.integers(0, vocab - 1, 5).tolist(), 33, dict()),
+            (rng.integers(0, vocab - 1, 64).tolist(), 18, dict(ignore_eos=True, forced_tokens=rng.integers(0, vocab - 1, 10).tolist())),
+            (rng.integers(0, vocab - 1, 16).tolist(), 25, dict(forced_tokens=[5, 6, CFG.eos_token_id, 8])),
+            (rng.integers(0, vocab - 1, 21).tolist(), 50, dict(ignore_eos=True)),
+            (rng.integers(0, vocab - 1, 9).tolist(), 12, dict(ignore_eos=True))]
+
+    def collect(e, stepper):
+        out = {}
+        for _ in range(3000):
+            for rid, tok, fin, why in stepper(e):
+                out.setdefault(rid, []).append((tok, fin, why))
+            s = e.stats()
+            if s["running"] == 0 and s["waiting"] == 0 and not e.in_flight:
+                break
+        return out
+
+    results = []
+    for feedback, stepper in ((False, lambda e: e.step()), (True, lambda e: e.step_pipelined()), (True, lambda e: e.step())):
+        e = make_engine(weights, max_batch=4, device_feedback=feedback)
+        for p, n, kw in reqs:
+            e.add_request(p, n, **kw)
+        results.append((collect(e, stepper), e.stats()))
+    (want, ws), (got, gs), (plain, ps) = results
+    assert got == want and plain == want
+    assert want[3][-1][1:] == (True, "eos") and len(want[3]) == 3
+    for k in ("prefill_tokens", "decode_tokens", "free_blocks", "reserved_blocks", "running", "waiting"):
+        assert ws[k] == gs[k] == ps[k], k
+    assert gs["free_blocks"] == gs["total_blocks"] - 1
+
+
 def test_steps_in_two_halves_across_engines_equal_whole_steps(weights):
     """step_begin on every engine, then step_end on every engine (what a multi-replica driver does)
     returns exactly what step() returns engine by engine."""
