@@ -159,6 +159,31 @@ int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, c
                                             int32_t head_dim, float scale, void* stream);
 
 /*
+ * Fused paged prefill attention: the `chunk_len` query rows of one prompt chunk (absolute positions
+ * chunk_start .. chunk_start + chunk_len - 1 of ONE sequence, already rotated by RoPE, rows q_row_stride
+ * elements apart) attend causally to every key of that sequence up to their own position, read straight
+ * from the paged pool through the sequence's block-table row (which must cover chunk_start + chunk_len
+ * tokens; the chunk's own K/V must already have been scattered). Scores q.k * scale in FP32, masking by
+ * SELECT (key position <= query position; slots and pages past the context never reach a result),
+ * softmax with FP32 statistics, probabilities rounded to FP16 for P.V, FP32 accumulation, one FP16
+ * rounding; out[row, head * 128 ..] is written for the chunk's rows only. head_dim must be 128,
+ * num_q_heads a multiple of num_kv_heads (<= 8 KV heads); q, out and the pool slice 16-byte aligned, row
+ * strides multiples of 8. One CTA per (128-row query tile, query head): TMA page tiles, tcgen05 for
+ * Q.K^T and P.V with accumulators in tensor memory.
+ * No single launcher of the reference corresponds: this replaces its prefill composite LaunchKvGather ->
+ * cuBLASLt scores -> LaunchPrefillSoftmax -> cuBLASLt P.V (src/core/model_executor.cpp:1219-1290), the
+ * fused kernel its design notes name as the follow-up (docs/DESIGN.md:872-876 of the reference).
+ */
+int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stride, const void* q, int64_t q_row_stride,
+                                      const void* kv_pool_layer, const int32_t* block_table_row,
+                                      int32_t max_blocks_per_seq, int32_t chunk_start, int32_t chunk_len,
+                                      int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+                                      void* stream);
+
+/* Health of the prefill attention kernel's bounded waits on the current device (as rl_attention_health). */
+int rl_prefill_attention_health(int* flag_out);
+
+/*
  * Decode input plumbing on the device: after a step's greedy argmax, prepare the next step's inputs in
  * place - input_ids[i] <- control[1 + i] if that is >= 0 (a scripted token), else sampled_tokens[i];
  * positions[i] <- seq_lens[i]; seq_lens[i] += 1 - for every row with seq_len > 0, when control[0] != 0

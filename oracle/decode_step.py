@@ -67,16 +67,20 @@ class CpuDecoder:
                 else self.own.rope(h, pos, heads, c.head_dim, c.rope_theta))
 
     def step(self, ex, rows):
-        """The decode step the executor `ex` last uploaded, for its batch rows `rows`, recomputed on the
-        host: reads ids / positions / seq_lens / tables and those sequences' pages from the device, then
-        returns (seconds of host compute, tokens int32[len(rows)], logits float32[len(rows), vocab])."""
+        """The decode step the executor `ex` last uploaded from its host mirrors (a step begun with
+        Engine.step / step_begin / upload_next_inputs, not one launched on device-fed inputs), for its batch rows
+        `rows`, recomputed on the host: takes ids / positions / seq_lens / tables from the mirrors and those
+        sequences' pages from the device, then returns (seconds of host compute, tokens int32[len(rows)], logits float32[len(rows), vocab])."""
         import torch
         cfg = self.cfg
-        sel = torch.as_tensor(list(rows), device=ex.ids.device)
-        ids = ex.ids.index_select(0, sel).cpu().numpy()
-        pos = ex.positions.index_select(0, sel).cpu().numpy()
-        lens = ex.seq_lens.index_select(0, sel).cpu().numpy()
-        tables = ex.tables.index_select(0, sel).cpu().numpy()
+        rows = list(rows)
+        # The executor's pinned host mirrors hold what was uploaded for the step that has just run; the device
+        # copies of ids / positions / seq_lens may already have been advanced to the next step's values by the
+        # last kernel of the decode sequence.
+        ids = ex.h_ids.numpy()[rows].copy()
+        pos = ex.h_pos.numpy()[rows].copy()
+        lens = ex.h_lens.numpy()[rows].copy()
+        tables = ex.h_tables.numpy()[rows].copy()
         used = np.unique(tables[tables > 0])
         remap = np.zeros(int(tables.max()) + 1, np.int32)
         remap[used] = np.arange(1, len(used) + 1, dtype=np.int32)

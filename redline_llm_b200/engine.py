@@ -315,6 +315,7 @@ class ModelExecutor:
         self.scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self.attention_events = None  # set by profile runs
         self.prefill_logits = None
+        self.prefill_attention = "fused"   # or "composite": gather -> library GEMM -> softmax -> library GEMM
         self.fuse_rope_scatter = True  # one launch for RoPE + scatter; False = the reference's two launches
         # Linear layers of the decode step: "tcgen05" = this library's weight-streaming kernel (with the
         # SiLU-mul fused into the gate/up product), "library" = torch.matmul (cuBLAS), as the reference.
@@ -528,12 +529,19 @@ class ModelExecutor:
         normed, mlp = torch.empty_like(x), torch.empty_like(x)
         qkv = torch.empty(n, cfg.qkv_width, dtype=torch.float16, device=dev)
         gu = torch.empty(n, 2 * cfg.inter, dtype=torch.float16, device=dev)
-        # staging for the prefill attention composite (src/core/model_executor.cpp:1219-1290):
-        # kv_gather -> scores GEMMs -> causal softmax -> PV GEMMs, the GEMMs being library calls
-        khat = torch.empty(cfg.kv_heads, end, cfg.head_dim, dtype=torch.float16, device=dev)
-        vhat = torch.empty_like(khat)
+        # Attention of the chunk over the sequence's cache: this library's fused paged kernel (TMA page tiles,
+        # tcgen05), or - prefill_attention = "composite" - the reference's composite
+        # (src/core/model_executor.cpp:1219-1290): kv_gather -> scores GEMMs -> causal softmax -> PV GEMMs, the
+        # GEMMs being library calls and the staging below their scratch.
+        fused = (self.prefill_attention == "fused" and cfg.head_dim == 128
+                 and hasattr(K, "launch_paged_prefill_attention"))
         group = cfg.q_heads // cfg.kv_heads
-        probs = torch.empty(cfg.q_heads, n, end, dtype=torch.float16, device=dev)
+        if fused:
+            attn = torch.empty(n, cfg.q_width, dtype=torch.float16, device=dev)
+        else:
+            khat = torch.empty(cfg.kv_heads, end, cfg.head_dim, dtype=torch.float16, device=dev)
+            vhat = torch.empty_like(khat)
+            probs = torch.empty(cfg.q_heads, n, end, dtype=torch.float16, device=dev)
         for li, L in enumerate(w.layers):
             if li == 0:
                 K.launch_rms_norm(normed, x, L["in_norm"], n, cfg.hidden, cfg.eps)
@@ -545,14 +553,18 @@ class ModelExecutor:
             K.launch_kv_scatter(self.pool[li], qkv, qkv, cfg.qkv_width, cfg.qkv_width, row, 0, pos, n,
                                 cfg.kv_heads, cfg.head_dim, k_offset=cfg.q_width,
                                 v_offset=cfg.q_width + cfg.kv_width)
-            K.launch_kv_gather(khat, vhat, end * cfg.head_dim, cfg.head_dim, end * cfg.head_dim, cfg.head_dim,
-                               self.pool[li], row, end, cfg.kv_heads, cfg.head_dim)
-            q = qkv[:, :cfg.q_width].view(n, cfg.q_heads, cfg.head_dim).permute(1, 0, 2)      # [q_heads, n, d]
-            kx = khat.repeat_interleave(group, dim=0)                                          # [q_heads, end, d]
-            scores = torch.bmm(q.float(), kx.float().transpose(1, 2)) * self.scale             # FP32, scaled
-            K.launch_prefill_softmax(probs, scores.contiguous(), cfg.q_heads, n, end, start)
-            o = torch.bmm(probs, vhat.repeat_interleave(group, dim=0))                         # [q_heads, n, d]
-            attn = o.permute(1, 0, 2).reshape(n, cfg.q_width).contiguous()
+            if fused:
+                K.launch_paged_prefill_attention(attn, cfg.q_width, qkv, cfg.qkv_width, self.pool[li], row, self.mbps,
+                                                 start, n, cfg.q_heads, cfg.kv_heads, cfg.head_dim, self.scale)
+            else:
+                K.launch_kv_gather(khat, vhat, end * cfg.head_dim, cfg.head_dim, end * cfg.head_dim, cfg.head_dim,
+                                   self.pool[li], row, end, cfg.kv_heads, cfg.head_dim)
+                q = qkv[:, :cfg.q_width].view(n, cfg.q_heads, cfg.head_dim).permute(1, 0, 2)      # [q_heads, n, d]
+                kx = khat.repeat_interleave(group, dim=0)                                          # [q_heads, end, d]
+                scores = torch.bmm(q.float(), kx.float().transpose(1, 2)) * self.scale             # FP32, scaled
+                K.launch_prefill_softmax(probs, scores.contiguous(), cfg.q_heads, n, end, start)
+                o = torch.bmm(probs, vhat.repeat_interleave(group, dim=0))                         # [q_heads, n, d]
+                attn = o.permute(1, 0, 2).reshape(n, cfg.q_width).contiguous()
             torch.matmul(attn, L["o"].t(), out=mlp)
             K.launch_rms_norm_residual(normed, x, mlp, L["post_norm"], n, cfg.hidden, cfg.eps)
             torch.matmul(normed, L["gate_up"].t(), out=gu)
@@ -579,7 +591,7 @@ class Engine:
                  device: int = 0, seed: int = 0x5EED, weights: Optional[ModelWeights] = None,
                  graph_buckets: Optional[Sequence[int]] = None, prologue_overlap: bool = True,
                  decode_linear: str = "tcgen05", vocab_projection: Optional[str] = None,
-                 device_feedback: bool = True):
+                 device_feedback: bool = True, prefill_attention: str = "fused"):
         import torch
         if admission_policy != "reserve_full":
             raise ValueError("only the reserve_full admission policy is provided")
@@ -606,6 +618,9 @@ class Engine:
         self.exec = ModelExecutor(self.cfg, self.weights, num_blocks, max_seq_len, self.device, enable_cuda_graphs)
         self.exec.decode_linear = decode_linear
         self.exec.vocab_projection = vocab_projection or decode_linear
+        if prefill_attention not in ("fused", "composite"):
+            raise ValueError("prefill_attention must be 'fused' or 'composite'")
+        self.exec.prefill_attention = prefill_attention
         self.max_seq_len, self.max_batch = max_seq_len, max_batch
         self.pad_eager_to_bucket = pad_eager_to_bucket
         buckets = [b for b in BUCKETS if b <= select_bucket(max_batch)]

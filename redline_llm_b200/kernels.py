@@ -26,6 +26,7 @@ ABI_SYMBOLS = (
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
     "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter", "rl_launch_decode_advance",
+    "rl_launch_paged_prefill_attention", "rl_prefill_attention_health",
 )
 
 
@@ -68,6 +69,8 @@ def lib() -> C.CDLL:
                                                     i32, i32, i32, f32, vp]
         L.rl_decode_linear_set_stages.argtypes = [C.c_int]
         L.rl_launch_decode_advance.argtypes = [vp, vp, vp, vp, vp, i32, vp]
+        L.rl_launch_paged_prefill_attention.argtypes = [vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]
+        L.rl_prefill_attention_health.argtypes = [C.POINTER(C.c_int)]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -184,6 +187,23 @@ def launch_embed_gather(out, out_row_stride, embed, input_ids, num_tokens, hidde
 def launch_greedy_argmax(out_tokens, logits, num_seqs, vocab_size, stream=None):
     _check(lib().rl_launch_greedy_argmax(out_tokens.data_ptr(), _ptr(logits), num_seqs, vocab_size,
                                          _stream(stream)), "LaunchGreedyArgmax")
+
+
+def launch_paged_prefill_attention(out, out_row_stride, q, q_row_stride, kv_pool_layer, block_table_row,
+                                   max_blocks_per_seq, chunk_start, chunk_len, num_q_heads, num_kv_heads, head_dim,
+                                   scale, stream=None, q_offset=0):
+    """Causal attention of one prompt chunk of one sequence over its paged cache, fused (no gather, no score
+    matrix in global memory): replaces the gather -> scores GEMM -> softmax -> P.V GEMM composite."""
+    _check(lib().rl_launch_paged_prefill_attention(
+        _ptr(out), out_row_stride, _ptr(q, q_offset), q_row_stride, _ptr(kv_pool_layer), block_table_row.data_ptr(),
+        max_blocks_per_seq, chunk_start, chunk_len, num_q_heads, num_kv_heads, head_dim, scale, _stream(stream)),
+        "paged prefill attention")
+
+
+def prefill_attention_health() -> int:
+    flag = C.c_int(0)
+    _check(lib().rl_prefill_attention_health(C.byref(flag)), "rl_prefill_attention_health")
+    return flag.value
 
 
 def launch_decode_advance(input_ids, positions, seq_lens, sampled_tokens, control, num_rows, stream=None):
