@@ -46,6 +46,15 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Measured dense bf16 GEMM peak (TFLOP/s, burst) of this pool's B200s; the stated fallback otherwise."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"])
+    return 1590.0
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled every 50 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -482,6 +491,43 @@ def kernel_table(peak, only=None, eager=False):
                            layers, iters=10)
         report(name, secs, aw.bytes_per_launch, f"{layers} layer pools in rotation, cold L2", rsecs)
         del aw
+    # fused paged prefill attention: one prompt chunk of 2048 rows at the start of a prompt and deep inside one
+    # (context 8192), against the composite it replaces (gather -> FP32 scores -> causal softmax -> P.V, the two
+    # products by the library); compute-bound, so the figure of merit is FLOP/s against the measured GEMM peak
+    for name, (start, n) in (("paged_prefill_attention_rows2048_ctx2048", (0, 2048)),
+                             ("paged_prefill_attention_rows2048_ctx8192", (6144, 2048))):
+        if not want(name):
+            continue
+        end = start + n
+        blocks = end // 16
+        c = wl.config_attention(lens=[end], num_blocks=blocks + 8, seed=0x9F1 + start, fill="uniform")
+        pool, row = dev(c["pool"]), dev(np.ascontiguousarray(c["tables"][0]))
+        qkv = [dev(wl.normal_half(0x9F3 + i, n * 2048).reshape(n, 2048)) for i in range(2)]
+        outs = [torch.empty(n, 1536, dtype=torch.int16, device="cuda") for _ in range(2)]
+        secs = timed(lambda i: K.launch_paged_prefill_attention(outs[i], 1536, qkv[i], 2048, pool, row, blocks, start, n,
+                                                                12, 2, 128, c["scale"]), 2, iters=5)
+        khat = torch.empty(2, end, 128, dtype=torch.float16, device="cuda")
+        vhat = torch.empty_like(khat)
+        probs = torch.empty(12, n, end, dtype=torch.float16, device="cuda")
+
+        def composite(i):
+            K.launch_kv_gather(khat, vhat, end * 128, 128, end * 128, 128, pool, row, end, 2, 128)
+            q = qkv[i].view(torch.float16)[:, :1536].view(n, 12, 128).permute(1, 0, 2)
+            sc = torch.bmm(q.float(), khat.repeat_interleave(6, 0).float().transpose(1, 2)) * c["scale"]
+            K.launch_prefill_softmax(probs, sc, 12, n, end, start)
+            return torch.bmm(probs, vhat.repeat_interleave(6, 0))
+        for _ in range(2):
+            composite(0)
+        csecs = time_region(lambda: composite(0), 3, torch.cuda.synchronize) * 1e-3 / 3
+        flops = 12 * 4 * 128 * sum(start + r + 1 for r in range(n))
+        tpeak = tensor_peak()
+        out[name] = {"us": round(secs * 1e6, 2), "TFLOP/s": round(flops / secs / 1e12, 1),
+                     "frac_of_measured_tensor_peak": round(flops / secs / 1e12 / tpeak, 4), "flops": flops,
+                     "bytes": 2 * n * 1536 * 2 + end * 1024 + blocks * 4,
+                     "composite_us": round(csecs * 1e6, 2), "speedup_vs_composite": round(csecs / secs, 2),
+                     "note": "causal flops only (4 * 128 per query-key pair); tensor peak = measured cuBLAS bf16 burst; "
+                             "composite = kv_gather + FP32 torch.bmm + causal softmax + FP16 torch.bmm, eager"}
+        del pool, qkv, outs, khat, vhat, probs
     # the four linear layers of a decoder block at 64 token rows: weight streams (28 distinct weights, cold L2)
     for name, (n_out, k_in, epi, with_bias) in (("decode_linear_qkv_T64", (2048, 1536, 0, True)),
                                                  ("decode_linear_o_T64", (1536, 1536, 0, False)),

@@ -10,23 +10,29 @@
 // probabilities rounded to FP16 for the P.V product, FP32 accumulation, one FP16 rounding of acc / l -
 // with nothing but Q, the pages and the output ever touching global memory.
 //
-// Mapping. One CTA per (128-row query tile, query head); 128 threads, thread t owns query row t.
-//  * Q tile and K/V blocks of 128 keys (8 pages) arrive by TMA with the 128-byte swizzle. A page tile
-//    of the pool is [16 tokens][128 dims]; each 64-dim half of it is one 2 KiB tensor copy landing at row
-//    16 * page of a [128 rows][128 B] region, so eight pages form exactly the K-major operand tile
-//    tcgen05 expects - block-table indirection costs nothing but the copy's coordinate. K/V blocks are
-//    double-buffered; the six query heads of a KV group and all query tiles re-read the same pages from L2.
-//  * S = Q.K^T: tcgen05.mma, M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major
-//    in shared memory, FP32 accumulator in tensor memory (columns 0-127).
-//  * Softmax: each thread reads its row of S from tensor memory (tcgen05.ld 32x32b) twice - once for the
-//    row maximum, once to exponentiate - in the exp2 domain with the running maximum of an online
-//    softmax, and writes P as FP16 into shared memory in the swizzled K-major layout by hand.
-//  * O_blk = P.V: tcgen05.mma with A = P (K-major) and B = V as it lies in the pool - [key][dim], i.e.
-//    MN-major: atoms of 8 keys x 64 dims, 1024 B between key groups, one region per 64-dim half -
-//    into tensor-memory columns 128-255; the thread then folds it into its row's running output held in
-//    registers, scaled by exp2(m_old - m_new).
-//  * The next block's S is issued right behind P.V, so the tensor pipe works on it while the threads fold.
-// Every mbarrier wait is bounded and reports through the attention health flag.
+// Mapping. One CTA per (128-row query tile, query head); nine warps.
+//  * Warp 8 is the issuer: one lane requests every tile by TMA and issues every tcgen05.mma. Q tile and K/V
+//    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
+//    [16 tokens][128 dims]; each 64-dim half of it is one 2 KiB tensor copy landing at row 16 * page of a
+//    [128 rows][128 B] region, so eight pages form exactly the K-major operand tile tcgen05 expects -
+//    block-table indirection costs nothing but the copy's coordinate. K and V blocks are double-buffered;
+//    the six query heads of a KV group and all query tiles re-read the same pages from L2.
+//  * S = Q.K^T: M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major in shared
+//    memory, FP32 accumulator in tensor memory. Two S buffers (columns 0-127, 128-255): the product of
+//    block j+2 is issued as soon as the softmax of block j has released its buffer, so the tensor pipe runs
+//    under the softmax of block j+1.
+//  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
+//    its own quarter of the tensor-memory lanes). Each thread reads its half row of S from tensor memory
+//    (tcgen05.ld 32x32b) twice - the maximum, exchanged with its partner through shared memory, then the
+//    exponentials (ex2.approx in the exp2 domain) - and writes P as FP16 into shared memory in the swizzled
+//    K-major layout by hand (two P buffers). The running reference maximum is only moved when a row's
+//    maximum exceeds it by more than 2^8: P then stays below 2^8 (exact in FP16's range), and the rescaling of
+//    the running output - a read-modify-write of the row in tensor memory - almost never happens after the
+//    first block; numerator and denominator always share one reference, so the result does not depend on it.
+//  * O += P.V: A = P (K-major) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
+//    8 keys x 64 dims, 1024 B between key groups, one region per 64-dim half - accumulated over all
+//    blocks in tensor-memory columns 256-383; read once at the end, divided by the row sum, rounded once.
+// Every mbarrier wait is bounded and reports through rl_prefill_attention_health.
 #include <cuda.h>
 
 #include <mutex>
@@ -41,18 +47,22 @@ using namespace rl::tc;
 constexpr int kHeadDim = 128;
 constexpr int kBM = 128;                 // query rows per CTA
 constexpr int kBN = 128;                 // keys per block (8 pages)
-constexpr int kThreads = 128;
+constexpr int kSoftmaxThreads = 256;     // warps 0-7: two threads per query row
+constexpr int kThreads = kSoftmaxThreads + 32;   // + the issuer warp
 constexpr int kPagesPerBlock = kBN / kKvBlock;
 constexpr int kRegionBytes = 128 * 128;  // [128 rows][64 halves], 128-byte swizzle
 constexpr int kTileBytes = 2 * kRegionBytes;   // two 64-wide halves
 constexpr int kQOff = 0;
 constexpr int kKOff = kQOff + kTileBytes;          // 2 buffers
 constexpr int kVOff = kKOff + 2 * kTileBytes;      // 2 buffers
-constexpr int kPOff = kVOff + 2 * kTileBytes;
-constexpr int kBarOff = kPOff + kTileBytes;        // mbarriers + tmem slot
-constexpr int kSmemBytes = kBarOff + 128 + 1024;   // + slack to align the base to 1024
-static_assert(kSmemBytes <= 227 * 1024, "prefill attention shared memory exceeds the per-CTA limit");
-constexpr int kTmemCols = 256;           // S: columns 0-127, P.V: 128-255
+constexpr int kPOff = kVOff + 2 * kTileBytes;      // 2 buffers
+constexpr int kBarOff = kPOff + 2 * kTileBytes;    // mbarriers, tmem slot
+constexpr int kXOff = kBarOff + 128;               // row maxima [2 iterations][2 halves][128] (row sums reuse one half at the end)
+constexpr int kSmemNeeded = kXOff + 4 * 128 * 4;   // from a 1024-byte aligned base
+constexpr int kSmemBytes = 227 * 1024;             // everything a CTA may have: the rest is slack for aligning the base
+static_assert(kSmemNeeded <= kSmemBytes, "prefill attention shared memory exceeds the per-CTA limit");
+constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383
+constexpr float kRescaleThreshold = 8.0f;   // log2: P never exceeds 2^8
 
 struct Params {
   half* out;
@@ -84,20 +94,46 @@ __device__ __forceinline__ void TmaLoadHalfTile(uint32_t dst, const CUtensorMap*
       "l"(map), "r"(0), "r"(half_idx), "r"(tile), "r"(bar), "l"(policy)
       : "memory");
 }
+__device__ __forceinline__ void MbarArrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float Ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 16 accumulator columns of this thread's lane back into tensor memory.
+__device__ __forceinline__ void TmemStore16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void TmemWaitStores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
 
 __global__ void __launch_bounds__(kThreads, 1)
 PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap q_map,
                             const __grid_constant__ CUtensorMap tile_map) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // The tiles fill all but a few hundred bytes of what a CTA may have: should the base ever need more
+  // alignment padding than that, report it instead of running past the end.
+  if (static_cast<int>(smem - smem_raw) + kSmemNeeded > kSmemBytes) {
+    if (threadIdx.x == 0) atomicExch(p.error_flag, 3);
+    return;
+  }
   const uint32_t s_q = SmemAddr(smem + kQOff), s_k = SmemAddr(smem + kKOff), s_v = SmemAddr(smem + kVOff);
   const uint32_t s_p = SmemAddr(smem + kPOff);
   const uint32_t bars = SmemAddr(smem + kBarOff);
-  const uint32_t bar_q = bars, bar_k0 = bars + 8, bar_v0 = bars + 24, bar_s = bars + 40, bar_o = bars + 48;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 64);
+  const uint32_t bar_q = bars, bar_k0 = bars + 8, bar_v0 = bars + 24, bar_s0 = bars + 40, bar_p0 = bars + 56,
+                 bar_o = bars + 72, bar_done = bars + 80;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 96);
+  float* xmax = reinterpret_cast<float*>(smem + kXOff);          // [2][2][128]
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // long tiles first: the last query tile of the chunk attends to the most keys
   const int tile_q = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int head = blockIdx.y;
@@ -106,22 +142,21 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   const int kv_len = p.chunk_start + p.chunk_len;
   const int last_pos = min(p.chunk_start + row0 + kBM, kv_len) - 1;   // newest key any row of this tile sees
   const int nblk = last_pos / kBN + 1;
-  const int my_pos = min(p.chunk_start + row0 + tid, kv_len - 1);      // rows past the chunk are computed, never stored
 
   if (tid == 0) {
     MbarInit(bar_q, 1);
     for (int i = 0; i < 2; ++i) {
       MbarInit(bar_k0 + 8 * i, 1);
       MbarInit(bar_v0 + 8 * i, 1);
+      MbarInit(bar_s0 + 8 * i, 1);
+      MbarInit(bar_p0 + 8 * i, kSoftmaxThreads);
     }
-    MbarInit(bar_s, 1);
     MbarInit(bar_o, 1);
+    MbarInit(bar_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
   }
-  if (warp == 1) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      SmemAddr(const_cast<uint32_t*>(tmem_slot))),
                  "r"(kTmemCols)
@@ -132,50 +167,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   __syncthreads();
   TcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kBN;
-
-  const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
-  // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: 8 pages x 2 halves, each 2 KiB at row 16 * page.
-  auto load_block = [&](int j, int kv) {
-    const int buf = j & 1;
-    const uint32_t base = (kv ? s_v : s_k) + buf * kTileBytes;
-    const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * buf;
-    MbarExpectTx(bar, kTileBytes);
-#pragma unroll 1
-    for (int pg = 0; pg < kPagesPerBlock; ++pg) {
-      const int page = j * kPagesPerBlock + pg;
-      const int block = page < p.max_blocks ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
-      const int tile = (block * 2 + kv) * p.kv_heads + kv_head;
-      TmaLoadHalfTile(base + pg * (kKvBlock * 128), &tile_map, 0, tile, bar, keep);
-      TmaLoadHalfTile(base + kRegionBytes + pg * (kKvBlock * 128), &tile_map, 1, tile, bar, keep);
-    }
-  };
-  const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
-  // S = Q.K_j^T into tensor-memory columns 0-127 (thread 0 only).
-  auto issue_qk = [&](int j) {
-    const uint32_t kb = s_k + (j & 1) * kTileBytes;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) Umma(tmem_s, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
-    }
-    UmmaCommit(bar_s);
-  };
-  // O_blk = P.V_j into columns 128-255: K = 16 keys per instruction, V read MN-major where it landed.
-  auto issue_pv = [&](int j) {
-    const uint32_t vb = s_v + (j & 1) * kTileBytes;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint64_t a = TileDesc(s_p + h * kRegionBytes);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint64_t b = TileDescMn(vb + (h * 4 + k) * (16 * 128), kRegionBytes);
-        Umma(tmem_o, a + 2 * k, b, idesc_mn, (h | k) ? 1u : 0u);
-      }
-    }
-    UmmaCommit(bar_o);
-  };
+  const uint32_t tmem_o = tmem_base + 2 * kBN;
 
   bool ok = true;
   auto wait = [&](uint32_t bar, int parity) {
@@ -185,139 +177,227 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     }
   };
 
-  if (tid == 0) {
-    MbarExpectTx(bar_q, kTileBytes);
-    TmaLoad2D(s_q, &q_map, head * kHeadDim, row0, bar_q, normal);
-    TmaLoad2D(s_q + kRegionBytes, &q_map, head * kHeadDim + 64, row0, bar_q, normal);
-    load_block(0, 0);
-    load_block(0, 1);
-    if (nblk > 1) {
-      load_block(1, 0);
-      load_block(1, 1);
-    }
-    wait(bar_q, 0);
-    wait(bar_k0, 0);
-    TcFenceAfter();
-    if (ok) issue_qk(0);
-  }
+  if (warp == 8) {
+    // ------------------------------------------------------------ issuer: TMA requests and MMA issue
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
+      const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
+      // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: 8 pages x 2 halves, each 2 KiB at row 16 * page.
+      auto load_block = [&](int j, int kv) {
+        const int buf = j & 1;
+        const uint32_t base = (kv ? s_v : s_k) + buf * kTileBytes;
+        const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * buf;
+        MbarExpectTx(bar, kTileBytes);
+#pragma unroll 1
+        for (int pg = 0; pg < kPagesPerBlock; ++pg) {
+          const int page = j * kPagesPerBlock + pg;
+          const int block = page < p.max_blocks ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+          const int tile = (block * 2 + kv) * p.kv_heads + kv_head;
+          TmaLoadHalfTile(base + pg * (kKvBlock * 128), &tile_map, 0, tile, bar, keep);
+          TmaLoadHalfTile(base + kRegionBytes + pg * (kKvBlock * 128), &tile_map, 1, tile, bar, keep);
+        }
+      };
+      const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
+      // S[j & 1] = Q.K_j^T
+      auto issue_qk = [&](int j) {
+        const uint32_t kb = s_k + (j & 1) * kTileBytes;
+        const uint32_t d = tmem_base + (j & 1) * kBN;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
+        }
+        UmmaCommit(bar_s0 + 8 * (j & 1));
+      };
+      // O += P_j.V_j: K = 16 keys per instruction, V read MN-major where it landed.
+      auto issue_pv = [&](int j) {
+        const uint32_t vb = s_v + (j & 1) * kTileBytes, pb = s_p + (j & 1) * kTileBytes;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint64_t a = TileDesc(pb + h * kRegionBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t b = TileDescMn(vb + (h * 4 + k) * (16 * 128), kRegionBytes);
+            Umma(tmem_o, a + 2 * k, b, idesc_mn, (j | h | k) ? 1u : 0u);
+          }
+        }
+        UmmaCommit(bar_o);
+      };
 
-  float o[kHeadDim];
-#pragma unroll
-  for (int i = 0; i < kHeadDim; ++i) o[i] = 0.0f;
-  float m = -INFINITY, l = 0.0f;
-  const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;   // this warp's quarter of the tensor-memory lanes
-  uint8_t* p_row = smem + kPOff + tid * 128;
-
-#pragma unroll 1
-  for (int j = 0; j < nblk; ++j) {
-    const int buf = j & 1;
-    wait(bar_s, j & 1);
-    TcFenceAfter();
-    // K buffer `buf` is free again: fetch block j + 2 into it
-    if (tid == 0 && j + 2 < nblk) load_block(j + 2, 0);
-    const int key0 = j * kBN;
-    const bool diagonal = key0 + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
-    // pass 1: the row maximum
-    float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < kBN / 16; ++c) {
-      uint32_t raw[16];
-      TmemLoad16(tmem_s + lane_addr + c * 16, raw);
-      TmemWaitLoads(raw);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float s = __uint_as_float(raw[i]) * p.scale_log2e;
-        mx = fmaxf(mx, (!diagonal || key0 + c * 16 + i <= my_pos) ? s : -INFINITY);
+      MbarExpectTx(bar_q, kTileBytes);
+      TmaLoad2D(s_q, &q_map, head * kHeadDim, row0, bar_q, normal);
+      TmaLoad2D(s_q + kRegionBytes, &q_map, head * kHeadDim + 64, row0, bar_q, normal);
+      load_block(0, 0);
+      load_block(0, 1);
+      if (nblk > 1) {
+        load_block(1, 0);
+        load_block(1, 1);
       }
-    }
-    const float m_new = fmaxf(m, mx);            // finite: key 0 is visible to every row
-    const float alpha = exp2f(m - m_new);        // 0 on the first block
-    // pass 2: probabilities, FP16, into the swizzled K-major P tile; their FP32 sum
-    float sum = 0.0f;
-#pragma unroll 1
-    for (int c = 0; c < kBN / 16; ++c) {
-      uint32_t raw[16];
-      TmemLoad16(tmem_s + lane_addr + c * 16, raw);
-      TmemWaitLoads(raw);
-      uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const float s0 = __uint_as_float(raw[i]) * p.scale_log2e, s1 = __uint_as_float(raw[i + 1]) * p.scale_log2e;
-        const float p0 = (!diagonal || key0 + c * 16 + i <= my_pos) ? exp2f(s0 - m_new) : 0.0f;
-        const float p1 = (!diagonal || key0 + c * 16 + i + 1 <= my_pos) ? exp2f(s1 - m_new) : 0.0f;
-        const half2 h2 = __floats2half2_rn(p0, p1);
-        sum += __low2float(h2) + __high2float(h2);   // the sum of what the P.V product will actually use
-        packed[i >> 1] = AsU32(h2);
-      }
-      // keys c*16 .. c*16+15 = 16-byte chunks 2c and 2c+1 of this row; region = keys / 64
-      uint8_t* region = p_row + (c >> 2) * kRegionBytes;
-      const int ch = (2 * c) & 7;
-      *reinterpret_cast<uint4*>(region + (((ch) ^ (tid & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      *reinterpret_cast<uint4*>(region + (((ch + 1) ^ (tid & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    }
-    l = l * alpha + sum;
-    m = m_new;
-    // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
-    // would poison the row: clear them once the block has landed.
-    const int rows_valid = kv_len - key0;
-    if (rows_valid < kBN) {
-      wait(bar_v0 + 8 * buf, (j >> 1) & 1);
-      if (tid >= rows_valid) {
-        uint4* r0 = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + tid * 128);
-        uint4* r1 = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + kRegionBytes + tid * 128);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) r0[i] = r1[i] = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and cleared V rows) visible to the tensor pipe
-    TcFenceBefore();
-    __syncthreads();
-    if (tid == 0) {
-      wait(bar_v0 + 8 * buf, (j >> 1) & 1);
+      wait(bar_q, 0);
+      wait(bar_k0, 0);
       TcFenceAfter();
-      if (ok) issue_pv(j);
-      if (j + 1 < nblk) {
-        wait(bar_k0 + 8 * (buf ^ 1), ((j + 1) >> 1) & 1);
-        if (ok) issue_qk(j + 1);
+      if (ok) issue_qk(0);
+      if (nblk > 1) {
+        wait(bar_k0 + 8, 0);
+        if (ok) issue_qk(1);
       }
+      if (nblk > 2) {          // K buffer 0 is free once Q.K_0^T has completed
+        wait(bar_s0, 0);
+        load_block(2, 0);
+      }
+#pragma unroll 1
+      for (int j = 0; j < nblk; ++j) {
+        const int buf = j & 1, par = (j >> 1) & 1;
+        wait(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
+        wait(bar_v0 + 8 * buf, par);                 // V_j landed
+        TcFenceAfter();
+        if (ok) issue_pv(j);
+        if (j + 2 < nblk) {
+          wait(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
+          if (ok) issue_qk(j + 2);
+        }
+        if (j + 3 < nblk) {                          // K buffer of block j+1 is free once its product has completed
+          wait(bar_s0 + 8 * (buf ^ 1), ((j + 1) >> 1) & 1);
+          load_block(j + 3, 0);
+        }
+        if (j + 2 < nblk) {                          // V buffer `buf` is free once P_j.V_j has completed
+          wait(bar_o, j & 1);
+          load_block(j + 2, 1);
+        }
+      }
+      // One-shot barrier for the readers of the finished output. (bar_o's phases alternate parity; a reader
+      // that has not followed every one of them could mistake an older phase for the last.)
+      if (ok) UmmaCommit(bar_done);
     }
-    wait(bar_o, j & 1);
-    TcFenceAfter();
-    if (tid == 0 && j + 2 < nblk) load_block(j + 2, 1);   // V buffer `buf` is free again
-#pragma unroll
-    for (int c = 0; c < kHeadDim / 16; ++c) {
-      uint32_t raw[16];
-      TmemLoad16(tmem_o + lane_addr + c * 16, raw);
-      TmemWaitLoads(raw);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) o[c * 16 + i] = fmaf(o[c * 16 + i], alpha, __uint_as_float(raw[i]));
-    }
-    TcFenceBefore();
-    if (!__syncthreads_and(ok)) break;   // some wait gave up: every thread leaves together
-  }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax: two threads per query row
+    const int row = (warp & 3) * 32 + lane;          // the tensor-memory lane = query row of the tile
+    const int hw = warp >> 2;                        // which 64 keys of a block (and which 64 output dims at the end)
+    const int my_pos = min(p.chunk_start + row0 + row, kv_len - 1);   // rows past the chunk are computed, never stored
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float m_ref = -INFINITY, l = 0.0f;
 
-  const int row = row0 + tid;
-  if (ok && row < p.chunk_len) {
-    const float inv = 1.0f / l;
-    half* dst = p.out + static_cast<int64_t>(row) * p.out_stride + head * kHeadDim;
+#pragma unroll 1
+    for (int j = 0; j < nblk; ++j) {
+      const int buf = j & 1;
+      wait(bar_s0 + 8 * buf, (j >> 1) & 1);
+      TcFenceAfter();
+      const uint32_t s_addr = tmem_base + buf * kBN + hw * 64 + lane_addr;
+      const int key0 = j * kBN + hw * 64;
+      const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
+      // pass 1: the maximum of this thread's 64 scores (raw: the scale is positive)
+      float mx = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < kHeadDim / 8; ++c) {
-      uint32_t w[4];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        TmemLoad16(s_addr + c * 16, raw);
+        TmemWaitLoads(raw);
+        if (diagonal) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) w[i] = AsU32(__floats2half2_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv));
-      *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[i]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
+        }
+      }
+      float* xm = xmax + buf * 256;
+      xm[hw * 128 + row] = mx;
+      SoftmaxBarrier();
+      mx = fmaxf(mx, xm[(hw ^ 1) * 128 + row]) * p.scale_log2e;
+      // Move the reference when the row's maximum has outgrown it: rescale the row sum and, from the second
+      // block on, this thread's half of the running output row in tensor memory (the previous block's P.V
+      // must have completed). Tensor-memory accesses are warp-wide: rows that keep their reference take
+      // part with a factor of one.
+      const bool move = mx > m_ref + kRescaleThreshold;
+      const float alpha = move ? Ex2(m_ref - mx) : 1.0f;       // 0 on the first block
+      l *= alpha;
+      if (move) m_ref = mx;
+      if (j > 0 && __any_sync(0xffffffffu, move)) {
+        wait(bar_o, (j - 1) & 1);     // at most one phase behind: the product two blocks back completed before S_j did
+        TcFenceAfter();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t raw[16];
+          TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+          TmemWaitLoads(raw);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+          TmemStore16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+        }
+        TmemWaitStores();
+      }
+      // pass 2: probabilities, FP16, into the swizzled K-major P tile; their FP32 sum
+      uint8_t* p_row = smem + kPOff + buf * kTileBytes + hw * kRegionBytes + row * 128;
+      const float neg_ref = -m_ref;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        TmemLoad16(s_addr + c * 16, raw);
+        TmemWaitLoads(raw);
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          float p0 = Ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2e, neg_ref));
+          float p1 = Ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2e, neg_ref));
+          if (diagonal) {
+            p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
+            p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
+          }
+          sum += p0 + p1;
+          packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
+        }
+        *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      }
+      l += sum;
+      // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
+      // would poison the row: clear them once the block has landed.
+      const int rows_valid = kv_len - j * kBN;
+      if (rows_valid < kBN) {
+        wait(bar_v0 + 8 * buf, (j >> 1) & 1);
+        if (row >= rows_valid) {
+          uint4* r = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + hw * kRegionBytes + row * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and cleared V rows) visible to the tensor pipe
+      TcFenceBefore();
+      MbarArrive(bar_p0 + 8 * buf);
     }
-  }
-  // Copies still in flight target this CTA's shared memory: let them land before it is released.
-  if (!ok && tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      MbarWait(bar_k0 + 8 * i, 0);
-      MbarWait(bar_v0 + 8 * i, 0);
+
+    // ---- the running output: this thread's 64 dims of its row, divided by the row's sum
+    // (through the exchange buffer the last block did not use: every read of it lies before that block's barrier)
+    float* xsum = xmax + (nblk & 1) * 256;
+    xsum[hw * 128 + row] = l;
+    SoftmaxBarrier();
+    const float inv = 1.0f / (l + xsum[(hw ^ 1) * 128 + row]);
+    wait(bar_done, 0);
+    TcFenceAfter();
+    const int out_row = row0 + row;
+    half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + hw * 64;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t raw[16];
+      TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+      TmemWaitLoads(raw);
+      if (ok && out_row < p.chunk_len) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          w[i] = AsU32(__floats2half2_rn(__uint_as_float(raw[2 * i]) * inv, __uint_as_float(raw[2 * i + 1]) * inv));
+        *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
     }
   }
   TcFenceBefore();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 8) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }

@@ -68,6 +68,26 @@ def test_chunk_against_the_cpu_checker(own, chunk_start, chunk_len):
     assert K.prefill_attention_health() == 0
 
 
+def test_scores_that_outgrow_the_running_reference_late_in_the_context(own):
+    """The kernel keeps a stale reference maximum per row and rescales its running output (in tensor memory)
+    only when a later score exceeds it by more than 2^8. Keys from position 640 on are made eight times
+    larger, so every row's maximum jumps far beyond that in the middle of the context, twice over the
+    blocks: the rescaling path must give the same result as an exact softmax."""
+    chunk_start, chunk_len = 900, 200
+    case = make_case(chunk_start, chunk_len, 0xFA1)
+    pool = case["pool"].reshape(-1, 2, 2, 16, 128)
+    for g in range(40, (case["kv_len"] + 15) // 16):
+        k = pool[case["row"][g], 0]                     # K tiles of logical page g, both heads
+        live = (k & 0x7FFF) < 0x7C00                    # leave the NaN padding of the last page alone
+        k[live] = ((k[live].view(np.float16).astype(np.float32) * (8.0 if g < 50 else 24.0)).astype(np.float16)).view(np.uint16)
+    got = run_fused(case, chunk_start, chunk_len)
+    ref = reference(own, case, chunk_start, chunk_len)
+    out = oracle.half_bits_to_f64(got[:chunk_len, :1536])
+    assert np.isfinite(out).all()
+    assert np.abs(out - ref).max() <= MAX_ABS + 2.0 ** -11 * max(1.0, np.abs(ref).max())
+    assert K.prefill_attention_health() == 0
+
+
 def test_output_stride_gap_is_untouched_and_inputs_are_read_only(own):
     chunk_start, chunk_len = 200, 150
     case = make_case(chunk_start, chunk_len, 0xF77)
