@@ -206,6 +206,17 @@ int rl_launch_decode_advance(int32_t* input_ids, int32_t* positions, int32_t* se
  */
 int rl_attention_health(int* flag_out);
 
+/*
+ * Test hook for the give-up path of the attention kernel's bounded waits, for launches made after the call:
+ * with drop_first_copy != 0 one warp of the first CTA never requests its first K/V page and so waits for a
+ * copy that cannot arrive; wait_cycles > 0 replaces the limit of every wait (about a second by default) so
+ * that the test takes a millisecond. The kernel then raises the health flag, lets its other copies land,
+ * and returns normally with that launch's output undefined - nothing faults, traps or spins without bound,
+ * and the context stays usable. (0, 0) restores normal operation. Process-wide; not for serving code.
+ * No counterpart in the reference (its kernel has no asynchronous waits).
+ */
+int rl_attention_test_wait_expiry(int drop_first_copy, int64_t wait_cycles);
+
 /* Same contract, one warp per (sequence, query head), two-pass softmax on CUDA
  * cores: a structurally independent cross-check for tests. Replaces
  * LaunchPagedAttentionDecodeOracle, src/kernels/kernels.cuh:152-158. */

@@ -403,6 +403,10 @@ DecodeLinearKernel(const Params p, const __grid_constant__ CUtensorMap w_map,
   }
   if (!MbarWait(recv_bar, 0)) {
     if (tid == 0) atomicExch(p.error_flag, kErrSplitWait);
+    // Peers' slices may still be on their way into this CTA's receive area: give them one more bounded chance
+    // to land before the area is read (the launch is reported as failed either way) and, later, released. A
+    // barrier over the cluster would make this airtight but would have to run in every launch, failed or not.
+    MbarWait(recv_bar, 0);
   }
   if (tid == 0) { RL_LSTAMP(7); }
   if (p.epilogue == kEpilogueQkvRope) {

@@ -119,6 +119,8 @@ struct Params {
   float scale_log2e;
   int* meta;        // workspace meta
   float* partials;  // workspace partial records
+  long long wait_cycles;  // limit of every mbarrier wait (kWaitCycles unless a test shortened it)
+  int drop_first_copy;    // test hook: warp 0 of CTA 0 never requests its first page, so its wait must run out
   unsigned long long* timeline;  // diagnostics build only
 };
 
@@ -145,12 +147,12 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, int parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the phase never completed within kWaitCycles.
-__device__ __forceinline__ bool MbarWait(uint32_t bar, int parity) {
+// Bounded wait: false when the phase never completed within `limit` cycles.
+__device__ __forceinline__ bool MbarWait(uint32_t bar, int parity, long long limit) {
   if (MbarTryWait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!MbarTryWait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
@@ -335,6 +337,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   const uint32_t my_ring = ring + warp * (kStages * kStageBytes);
   const uint32_t my_bars = bars + warp * (kStages * 8);
   bool failed = false;
+  int fail_at = 0;  // index of the page whose wait gave up; copies from there on are drained before exit
 
   // Page metadata is looked up 32 pages at a time, one page per lane: lane j of batch b holds the
   // index of the K tile of this warp's page 32b + j, counted in 4 KiB (block, kv, head) tiles; the V
@@ -370,6 +373,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       const int tile_k = __shfl_sync(0xffffffffu, tiles_cur, i);
       if (tile_k & kNewestPageBit) {
         deferred |= 1 << i;
+      } else if (p.drop_first_copy && blockIdx.x == 0 && warp == 0 && i == 0) {
+        // test hook: this copy is never requested, the wait for it below gives up and raises the flag
       } else if (lane == 0) {
         MbarExpectTx(my_bars + i * 8, kStageBytes);
         TmaLoadPage(my_ring + i * kStageBytes, &tile_map, tile_k, my_bars + i * 8, stream_policy);
@@ -453,8 +458,9 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     for (int rel = warp + kWarps * n_use; rel < seg_end_rel; rel += kWarps) {
       const int stage = n_use % kStages;
       const uint32_t st = my_ring + stage * kStageBytes;
-      if (!failed && !MbarWait(my_bars + stage * 8, (n_use / kStages) & 1)) {
+      if (!failed && !MbarWait(my_bars + stage * 8, (n_use / kStages) & 1, p.wait_cycles)) {
         failed = true;
+        fail_at = n_use;
         if (lane == 0) atomicExch(p.meta, 1);
       }
       if (n_use == 0) { RL_STAMP(2); }
@@ -760,7 +766,7 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   // A warp that gave up on a load still owns copies in flight: give them one more bounded
   // chance to land before the CTA's shared memory is released.
   if (failed) {
-    for (; n_use < n_issue; ++n_use) MbarWait(my_bars + (n_use % kStages) * 8, (n_use / kStages) & 1);
+    for (int k = fail_at; k < n_issue; ++k) MbarWait(my_bars + (k % kStages) * 8, (k / kStages) & 1, p.wait_cycles);
   }
 }
 
@@ -818,6 +824,8 @@ DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 void* g_timeline = nullptr;  // diagnostics build only
 std::mutex g_mutex;
+long long g_wait_cycles = kWaitCycles;   // rl_attention_test_wait_expiry
+int g_drop_first_copy = 0;
 
 // First call per device: driver entry point, shared-memory opt-in, workspace.
 int EnsureReady(DeviceState** out_state) {
@@ -942,6 +950,12 @@ extern "C" int rl_attention_health(int* flag_out) {
   return RL_OK;
 }
 
+extern "C" int rl_attention_test_wait_expiry(int drop_first_copy, int64_t wait_cycles) {
+  rl::attn::g_drop_first_copy = drop_first_copy != 0;
+  rl::attn::g_wait_cycles = wait_cycles > 0 ? wait_cycles : rl::attn::kWaitCycles;
+  return RL_OK;
+}
+
 extern "C" int rl_attention_set_prologue_overlap(int enable) {
   rl::g_launch_overlap = enable != 0;
   return RL_OK;
@@ -987,6 +1001,8 @@ extern "C" int rl_launch_paged_attention_decode(void* out, int64_t out_row_strid
     p.scale_log2e = scale * 1.4426950408889634f;
     p.meta = static_cast<int*>(st->workspace);
     p.partials = reinterpret_cast<float*>(static_cast<int*>(st->workspace) + kMetaInts);
+    p.wait_cycles = g_wait_cycles;
+    p.drop_first_copy = g_drop_first_copy;
     p.timeline = nullptr;
 #ifdef RL_ATTN_TIMELINE
     {  // one region per launch, 32 regions in rotation
@@ -1123,6 +1139,8 @@ extern "C" int rl_launch_paged_attention_decode_static(void* out, int64_t out_ro
   p.scale_log2e = scale * 1.4426950408889634f;
   p.meta = static_cast<int*>(st->scratch);
   p.partials = reinterpret_cast<float*>(static_cast<int*>(st->scratch) + kMetaInts);
+  p.wait_cycles = g_wait_cycles;
+  p.drop_first_copy = g_drop_first_copy;
   p.timeline = nullptr;
   PagedAttentionSplitKernel<<<st->ctas, kThreads, kSmemBytes, s>>>(p, tile_map);
   return LaunchStatus("paged_attention_decode_static");

@@ -179,98 +179,103 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 
   if (warp == 8) {
     // ------------------------------------------------------------ issuer: TMA requests and MMA issue
+    // The whole warp walks the schedule; tile copies are spread over the lanes (a block of K or V is 16 copies of
+    // 2 KiB, one per lane), the MMAs and their commits come from lane 0.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
-      const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
-      // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: 8 pages x 2 halves, each 2 KiB at row 16 * page.
-      auto load_block = [&](int j, int kv) {
-        const int buf = j & 1;
-        const uint32_t base = (kv ? s_v : s_k) + buf * kTileBytes;
-        const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * buf;
-        MbarExpectTx(bar, kTileBytes);
-#pragma unroll 1
-        for (int pg = 0; pg < kPagesPerBlock; ++pg) {
-          const int page = j * kPagesPerBlock + pg;
-          const int block = page < p.max_blocks ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
-          const int tile = (block * 2 + kv) * p.kv_heads + kv_head;
-          TmaLoadHalfTile(base + pg * (kKvBlock * 128), &tile_map, 0, tile, bar, keep);
-          TmaLoadHalfTile(base + kRegionBytes + pg * (kKvBlock * 128), &tile_map, 1, tile, bar, keep);
+    }
+    const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
+    // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: 8 pages x 2 halves, each 2 KiB at row 16 * page.
+    auto load_block = [&](int j, int kv) {
+      const int buf = j & 1;
+      const uint32_t base = (kv ? s_v : s_k) + buf * kTileBytes;
+      const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * buf;
+      if (lane == 0) MbarExpectTx(bar, kTileBytes);
+      __syncwarp();
+      if (lane < 2 * kPagesPerBlock) {
+        const int pg = lane >> 1, hf = lane & 1;
+        const int page = j * kPagesPerBlock + pg;
+        const int block = page < p.max_blocks ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+        const int tile = (block * 2 + kv) * p.kv_heads + kv_head;
+        TmaLoadHalfTile(base + hf * kRegionBytes + pg * (kKvBlock * 128), &tile_map, hf, tile, bar, keep);
+      }
+    };
+    const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
+    // S[j & 1] = Q.K_j^T
+    auto issue_qk = [&](int j) {
+      const uint32_t kb = s_k + (j & 1) * kTileBytes;
+      const uint32_t d = tmem_base + (j & 1) * kBN;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
+      }
+      UmmaCommit(bar_s0 + 8 * (j & 1));
+    };
+    // O += P_j.V_j: K = 16 keys per instruction, V read MN-major where it landed.
+    auto issue_pv = [&](int j) {
+      const uint32_t vb = s_v + (j & 1) * kTileBytes, pb = s_p + (j & 1) * kTileBytes;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint64_t a = TileDesc(pb + h * kRegionBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t b = TileDescMn(vb + (h * 4 + k) * (16 * 128), kRegionBytes);
+          Umma(tmem_o, a + 2 * k, b, idesc_mn, (j | h | k) ? 1u : 0u);
         }
-      };
-      const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
-      // S[j & 1] = Q.K_j^T
-      auto issue_qk = [&](int j) {
-        const uint32_t kb = s_k + (j & 1) * kTileBytes;
-        const uint32_t d = tmem_base + (j & 1) * kBN;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
-        }
-        UmmaCommit(bar_s0 + 8 * (j & 1));
-      };
-      // O += P_j.V_j: K = 16 keys per instruction, V read MN-major where it landed.
-      auto issue_pv = [&](int j) {
-        const uint32_t vb = s_v + (j & 1) * kTileBytes, pb = s_p + (j & 1) * kTileBytes;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint64_t a = TileDesc(pb + h * kRegionBytes);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t b = TileDescMn(vb + (h * 4 + k) * (16 * 128), kRegionBytes);
-            Umma(tmem_o, a + 2 * k, b, idesc_mn, (j | h | k) ? 1u : 0u);
-          }
-        }
-        UmmaCommit(bar_o);
-      };
+      }
+      UmmaCommit(bar_o);
+    };
 
+    if (lane == 0) {
       MbarExpectTx(bar_q, kTileBytes);
       TmaLoad2D(s_q, &q_map, head * kHeadDim, row0, bar_q, normal);
       TmaLoad2D(s_q + kRegionBytes, &q_map, head * kHeadDim + 64, row0, bar_q, normal);
-      load_block(0, 0);
-      load_block(0, 1);
-      if (nblk > 1) {
-        load_block(1, 0);
-        load_block(1, 1);
-      }
-      wait(bar_q, 0);
-      wait(bar_k0, 0);
-      TcFenceAfter();
-      if (ok) issue_qk(0);
-      if (nblk > 1) {
-        wait(bar_k0 + 8, 0);
-        if (ok) issue_qk(1);
-      }
-      if (nblk > 2) {          // K buffer 0 is free once Q.K_0^T has completed
-        wait(bar_s0, 0);
-        load_block(2, 0);
-      }
-#pragma unroll 1
-      for (int j = 0; j < nblk; ++j) {
-        const int buf = j & 1, par = (j >> 1) & 1;
-        wait(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
-        wait(bar_v0 + 8 * buf, par);                 // V_j landed
-        TcFenceAfter();
-        if (ok) issue_pv(j);
-        if (j + 2 < nblk) {
-          wait(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
-          if (ok) issue_qk(j + 2);
-        }
-        if (j + 3 < nblk) {                          // K buffer of block j+1 is free once its product has completed
-          wait(bar_s0 + 8 * (buf ^ 1), ((j + 1) >> 1) & 1);
-          load_block(j + 3, 0);
-        }
-        if (j + 2 < nblk) {                          // V buffer `buf` is free once P_j.V_j has completed
-          wait(bar_o, j & 1);
-          load_block(j + 2, 1);
-        }
-      }
-      // One-shot barrier for the readers of the finished output. (bar_o's phases alternate parity; a reader
-      // that has not followed every one of them could mistake an older phase for the last.)
-      if (ok) UmmaCommit(bar_done);
     }
+    load_block(0, 0);
+    load_block(0, 1);
+    if (nblk > 1) {
+      load_block(1, 0);
+      load_block(1, 1);
+    }
+    wait(bar_q, 0);
+    wait(bar_k0, 0);
+    TcFenceAfter();
+    if (ok && lane == 0) issue_qk(0);
+    if (nblk > 1) {
+      wait(bar_k0 + 8, 0);
+      if (ok && lane == 0) issue_qk(1);
+    }
+    if (nblk > 2) {          // K buffer 0 is free once Q.K_0^T has completed
+      wait(bar_s0, 0);
+      load_block(2, 0);
+    }
+#pragma unroll 1
+    for (int j = 0; j < nblk; ++j) {
+      const int buf = j & 1, par = (j >> 1) & 1;
+      wait(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
+      wait(bar_v0 + 8 * buf, par);                 // V_j landed
+      TcFenceAfter();
+      if (ok && lane == 0) issue_pv(j);
+      if (j + 2 < nblk) {
+        wait(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
+        if (ok && lane == 0) issue_qk(j + 2);
+      }
+      __syncwarp();                                // the waits below follow lane 0's commits
+      if (j + 3 < nblk) {                          // K buffer of block j+1 is free once its product has completed
+        wait(bar_s0 + 8 * (buf ^ 1), ((j + 1) >> 1) & 1);
+        load_block(j + 3, 0);
+      }
+      if (j + 2 < nblk) {                          // V buffer `buf` is free once P_j.V_j has completed
+        wait(bar_o, j & 1);
+        load_block(j + 2, 1);
+      }
+    }
+    // One-shot barrier for the readers of the finished output. (bar_o's phases alternate parity; a reader
+    // that has not followed every one of them could mistake an older phase for the last.)
+    if (ok && lane == 0) UmmaCommit(bar_done);
     __syncwarp();
   } else {
     // ------------------------------------------------------------ softmax: two threads per query row
@@ -288,20 +293,28 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       const uint32_t s_addr = tmem_base + buf * kBN + hw * 64 + lane_addr;
       const int key0 = j * kBN + hw * 64;
       const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
-      // pass 1: the maximum of this thread's 64 scores (raw: the scale is positive)
+      // This thread's 64 scores, fetched from tensor memory once (all four loads in flight together: a load's
+      // round trip is long against the arithmetic), kept in registers for both passes.
+      uint32_t raw[4][16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) TmemLoad16(s_addr + c * 16, raw[c]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) TmemWaitLoads(raw[c]);
+      // pass 1: their maximum (raw: the scale is positive)
       float mx = -INFINITY;
+      if (diagonal) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[16];
-        TmemLoad16(s_addr + c * 16, raw);
-        TmemWaitLoads(raw);
-        if (diagonal) {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[i]) : -INFINITY);
-        } else {
+          for (int i = 0; i < 16; ++i)
+            mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
+      } else {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw[c][i]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       float* xm = xmax + buf * 256;
       xm[hw * 128 + row] = mx;
@@ -332,27 +345,26 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       // pass 2: probabilities, FP16, into the swizzled K-major P tile; their FP32 sum
       uint8_t* p_row = smem + kPOff + buf * kTileBytes + hw * kRegionBytes + row * 128;
       const float neg_ref = -m_ref;
-      float sum = 0.0f;
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t raw[16];
-        TmemLoad16(s_addr + c * 16, raw);
-        TmemWaitLoads(raw);
         uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-          float p0 = Ex2(fmaf(__uint_as_float(raw[i]), p.scale_log2e, neg_ref));
-          float p1 = Ex2(fmaf(__uint_as_float(raw[i + 1]), p.scale_log2e, neg_ref));
+          float p0 = Ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2e, neg_ref));
+          float p1 = Ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2e, neg_ref));
           if (diagonal) {
             p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
             p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
           }
-          sum += p0 + p1;
+          sum0 += p0;
+          sum1 += p1;
           packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
         }
         *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
+      const float sum = sum0 + sum1;
       l += sum;
       // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
       // would poison the row: clear them once the block has landed.

@@ -26,7 +26,7 @@ ABI_SYMBOLS = (
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
     "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter", "rl_launch_decode_advance",
-    "rl_launch_paged_prefill_attention", "rl_prefill_attention_health",
+    "rl_launch_paged_prefill_attention", "rl_prefill_attention_health", "rl_attention_test_wait_expiry",
 )
 
 
@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
         L.rl_launch_decode_advance.argtypes = [vp, vp, vp, vp, vp, i32, vp]
         L.rl_launch_paged_prefill_attention.argtypes = [vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]
         L.rl_prefill_attention_health.argtypes = [C.POINTER(C.c_int)]
+        L.rl_attention_test_wait_expiry.argtypes = [C.c_int, C.c_int64]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -219,6 +220,11 @@ def set_attention_prologue_overlap(enable: bool) -> None:
     dependent launch). seq_lens / block_tables must then not be written by the kernel launched
     immediately before attention."""
     _check(lib().rl_attention_set_prologue_overlap(1 if enable else 0), "rl_attention_set_prologue_overlap")
+
+
+def attention_test_wait_expiry(drop_first_copy: bool, wait_cycles: int = 0) -> None:
+    """Test hook: make one warp's first page copy never start and/or shorten every wait's limit (0 = default)."""
+    _check(lib().rl_attention_test_wait_expiry(1 if drop_first_copy else 0, wait_cycles), "rl_attention_test_wait_expiry")
 
 
 def attention_health() -> int:

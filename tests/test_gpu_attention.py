@@ -261,3 +261,31 @@ def test_second_device_keeps_its_own_state(own):
     expect(own, c, outs[1][0], "device 1")
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][0], outs[2][0])
     assert np.array_equal(outs[0][1], outs[1][1])
+
+
+def test_a_wait_that_runs_out_raises_the_health_flag_and_leaves_the_context_usable(own):
+    """The give-up path of the kernel's bounded waits, exercised without any fault: through the test hook one
+    warp never requests its first page, so its wait (shortened to about a millisecond) runs out. The launch
+    must come back, rl_attention_health must report it once - for the allocating launcher and for the
+    launcher with built-in scratch alike - and the next ordinary launch must be correct again."""
+    c = wl.config_attention(lens=[700, 33, 1500, 64, 257, 2049], num_blocks=400, seed=0x5A77)
+    n = len(c["seq_lens"])
+
+    def launch(entry):
+        d_out = torch.zeros(n, 1536, dtype=torch.int16, device="cuda")
+        entry(d_out, 1536, dev(c["q"]), 1536, dev(c["pool"]), dev(c["tables"]), dev(c["seq_lens"]), n,
+              c["tables"].shape[1], 12, 2, 128, c["scale"])
+        torch.cuda.synchronize()
+        return host(d_out)
+
+    assert K.attention_health() == 0
+    for entry in (K.launch_paged_attention_decode, K.launch_paged_attention_decode_static):
+        try:
+            K.attention_test_wait_expiry(True, 2_000_000)
+            launch(entry)                                # returns: nothing spins without bound
+            assert K.attention_health() == 1, "the wait that ran out was not reported"
+            assert K.attention_health() == 0, "the flag is cleared by the query that reported it"
+        finally:
+            K.attention_test_wait_expiry(False, 0)
+        expect(own, c, launch(entry), "after a reported give-up")
+        assert K.attention_health() == 0
