@@ -284,22 +284,27 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     const int my_pos = min(p.chunk_start + row0 + row, kv_len - 1);   // rows past the chunk are computed, never stored
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     float m_ref = -INFINITY, l = 0.0f;
-
-#pragma unroll 1
-    for (int j = 0; j < nblk; ++j) {
-      const int buf = j & 1;
-      wait(bar_s0 + 8 * buf, (j >> 1) & 1);
+    // This thread's 64 scores of a block are fetched from tensor memory once, all four loads in flight together,
+    // and kept in registers for both passes. The fetch for block j+1 is made at the END of block j, before this
+    // thread reports P_j: the tensor pipe is idle then, whereas a load issued once P_j.V_j and Q.K_{j+2}^T are
+    // running waits behind them.
+    uint32_t raw[4][16];
+    auto fetch_scores = [&](int j) {
+      wait(bar_s0 + 8 * (j & 1), (j >> 1) & 1);
       TcFenceAfter();
-      const uint32_t s_addr = tmem_base + buf * kBN + hw * 64 + lane_addr;
-      const int key0 = j * kBN + hw * 64;
-      const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
-      // This thread's 64 scores, fetched from tensor memory once (all four loads in flight together: a load's
-      // round trip is long against the arithmetic), kept in registers for both passes.
-      uint32_t raw[4][16];
+      const uint32_t s_addr = tmem_base + (j & 1) * kBN + hw * 64 + lane_addr;
 #pragma unroll
       for (int c = 0; c < 4; ++c) TmemLoad16(s_addr + c * 16, raw[c]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) TmemWaitLoads(raw[c]);
+    };
+    fetch_scores(0);
+
+#pragma unroll 1
+    for (int j = 0; j < nblk; ++j) {
+      const int buf = j & 1;
+      const int key0 = j * kBN + hw * 64;
+      const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
       // pass 1: their maximum (raw: the scale is positive)
       float mx = -INFINITY;
       if (diagonal) {
@@ -378,6 +383,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and cleared V rows) visible to the tensor pipe
+      if (j + 1 < nblk) fetch_scores(j + 1);
       TcFenceBefore();
       MbarArrive(bar_p0 + 8 * buf);
     }
