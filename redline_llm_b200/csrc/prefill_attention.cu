@@ -10,15 +10,19 @@
 // probabilities rounded to FP16 for the P.V product, FP32 accumulation, one FP16 rounding of acc / l -
 // with nothing but Q, the pages and the output ever touching global memory.
 //
-// Mapping. One CTA per (128-row query tile, query head); nine warps.
-//  * Warp 8 is the issuer: one lane requests every tile by TMA and issues every tcgen05.mma. Q tile and K/V
+// Mapping. One CTA per (128-row query tile, query head); ten warps.
+//  * Warp 9 requests every tile by TMA (copies spread over its lanes), warp 8 issues every tcgen05.mma: table
+//    reads and copy requests never sit between two products. Q tile and K/V
 //    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
-//    [16 tokens][128 dims]; each 64-dim half of it is one 2 KiB tensor copy landing at row 16 * page of a
-//    [128 rows][128 B] region, so eight pages form exactly the K-major operand tile tcgen05 expects -
-//    block-table indirection costs nothing but the copy's coordinate. K and V blocks are double-buffered;
+//    [16 tokens][128 dims]; one 4 KiB tensor copy lands it as [dim half][16 tokens][128 B] at 4 KiB * page
+//    (the TMA unit is paid per copy, not per byte: 16 copies per block instead of 32 was worth 1.4 x).
+//    Block-table indirection costs nothing but the copy's coordinate. K and V blocks are double-buffered;
 //    the six query heads of a KV group and all query tiles re-read the same pages from L2.
-//  * S = Q.K^T: M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major in shared
-//    memory, FP32 accumulator in tensor memory. Two S buffers (columns 0-127, 128-255): the product of
+//  * S = Q.K^T: M = 128 query rows, K = 16 dims x 8, both operands K-major in shared memory, FP32 accumulator
+//    in tensor memory. In the K buffer the 8-token groups of a dim half are 1 KiB apart inside a page and 4 KiB
+//    from page to page, so the 128 keys are taken as two N = 64 operand tiles with a constant group stride -
+//    tokens 0-7 of every page, tokens 8-15 of every page; the columns of S are permuted accordingly and the
+//    softmax puts P back in natural key order. Two S buffers (columns 0-127, 128-255): the product of
 //    block j+2 is issued as soon as the softmax of block j has released its buffer, so the tensor pipe runs
 //    under the softmax of block j+1.
 //  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
@@ -30,8 +34,9 @@
 //    the running output - a read-modify-write of the row in tensor memory - almost never happens after the
 //    first block; numerator and denominator always share one reference, so the result does not depend on it.
 //  * O += P.V: A = P (K-major) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
-//    8 keys x 64 dims, 1024 B between key groups, one region per 64-dim half - accumulated over all
-//    blocks in tensor-memory columns 256-383; read once at the end, divided by the row sum, rounded once.
+//    8 keys x 64 dims, 1024 B between key groups, 2 KiB between the dim halves, one page per K = 16 slice -
+//    accumulated over all blocks in tensor-memory columns 256-383; read once at the end, divided by the row
+//    sum, rounded once.
 // Every mbarrier wait is bounded and reports through rl_prefill_attention_health.
 #include <cuda.h>
 
@@ -48,7 +53,7 @@ constexpr int kHeadDim = 128;
 constexpr int kBM = 128;                 // query rows per CTA
 constexpr int kBN = 128;                 // keys per block (8 pages)
 constexpr int kSoftmaxThreads = 256;     // warps 0-7: two threads per query row
-constexpr int kThreads = kSoftmaxThreads + 32;   // + the issuer warp
+constexpr int kThreads = kSoftmaxThreads + 64;   // + the MMA-issue warp and the loader warp
 constexpr int kPagesPerBlock = kBN / kKvBlock;
 constexpr int kRegionBytes = 128 * 128;  // [128 rows][64 halves], 128-byte swizzle
 constexpr int kTileBytes = 2 * kRegionBytes;   // two 64-wide halves
@@ -85,15 +90,21 @@ __device__ __forceinline__ uint64_t TileDescMn(uint32_t smem_addr, uint32_t lbo_
 }
 __device__ __forceinline__ uint32_t InstrDescBMn(int n) { return InstrDesc(n) | (1u << 16); }
 
-// One 64-dim half of one (block, kv, head) page tile: [16 tokens][64 halves] = 2 KiB.
-__device__ __forceinline__ void TmaLoadHalfTile(uint32_t dst, const CUtensorMap* map, int half_idx, int tile,
-                                                uint32_t bar, uint64_t policy) {
+// One (block, kv, head) page tile in one copy: [dim half][16 tokens][64 halves] = 4 KiB, 128-byte swizzled.
+__device__ __forceinline__ void TmaLoadPageTile(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar,
+                                                uint64_t policy) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-      "[%0], [%1, {%2, %2, %3, %4}], [%5], %6;" ::"r"(dst),
-      "l"(map), "r"(0), "r"(half_idx), "r"(tile), "r"(bar), "l"(policy)
+      "[%0], [%1, {%2, %2, %2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(map), "r"(0), "r"(tile), "r"(bar), "l"(policy)
       : "memory");
 }
+// K-major operand whose 8-row groups lie `sbo` bytes apart (128-byte swizzle, rows of 128 B).
+__device__ __forceinline__ uint64_t TileDescSbo(uint32_t smem_addr, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+constexpr int kPageTileBytes = kKvBlock * kHeadDim * 2;   // 4096: [2 dim halves][16 tokens][128 B]
 __device__ __forceinline__ void MbarArrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -128,8 +139,11 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   const uint32_t s_q = SmemAddr(smem + kQOff), s_k = SmemAddr(smem + kKOff), s_v = SmemAddr(smem + kVOff);
   const uint32_t s_p = SmemAddr(smem + kPOff);
   const uint32_t bars = SmemAddr(smem + kBarOff);
+  // Every barrier that more than one phase passes through belongs to ONE buffer (index = block & 1): a waiter
+  // names a phase by its parity alone, which is only safe while the barrier cannot run two phases ahead of
+  // it - and the next phase of a buffer's barrier always needs something this waiter itself provides.
   const uint32_t bar_q = bars, bar_k0 = bars + 8, bar_v0 = bars + 24, bar_s0 = bars + 40, bar_p0 = bars + 56,
-                 bar_o = bars + 72, bar_done = bars + 80;
+                 bar_o0 = bars + 72, bar_done = bars + 88;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 96);
   float* xmax = reinterpret_cast<float*>(smem + kXOff);          // [2][2][128]
 
@@ -150,8 +164,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       MbarInit(bar_v0 + 8 * i, 1);
       MbarInit(bar_s0 + 8 * i, 1);
       MbarInit(bar_p0 + 8 * i, kSoftmaxThreads);
+      MbarInit(bar_o0 + 8 * i, 1);
     }
-    MbarInit(bar_o, 1);
     MbarInit(bar_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -177,44 +191,76 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     }
   };
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ issuer: TMA requests and MMA issue
-    // The whole warp walks the schedule; tile copies are spread over the lanes (a block of K or V is 16 copies of
-    // 2 KiB, one per lane), the MMAs and their commits come from lane 0.
+  if (warp == 9) {
+    // ------------------------------------------------------------ loader: every TMA request
+    // A block of K or V is 8 copies of 4 KiB, one per lane and page. The block id of a page serves K and V alike
+    // and is read from the table two blocks ahead of its use.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
     }
     const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
-    // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: 8 pages x 2 halves, each 2 KiB at row 16 * page.
-    auto load_block = [&](int j, int kv) {
-      const int buf = j & 1;
-      const uint32_t base = (kv ? s_v : s_k) + buf * kTileBytes;
-      const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * buf;
+    auto table_entry = [&](int j) {
+      const int page = j * kPagesPerBlock + lane;
+      return (lane < kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+    };
+    // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: page `lane` lands at lane * 4 KiB as
+    // [dim half][16 tokens][128 B] (one copy per page; a copy costs the TMA unit about as much whatever its size).
+    auto load_block = [&](int j, int kv, int block) {
+      const uint32_t base = (kv ? s_v : s_k) + (j & 1) * kTileBytes;
+      const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * (j & 1);
       if (lane == 0) MbarExpectTx(bar, kTileBytes);
       __syncwarp();
-      if (lane < 2 * kPagesPerBlock) {
-        const int pg = lane >> 1, hf = lane & 1;
-        const int page = j * kPagesPerBlock + pg;
-        const int block = page < p.max_blocks ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
-        const int tile = (block * 2 + kv) * p.kv_heads + kv_head;
-        TmaLoadHalfTile(base + hf * kRegionBytes + pg * (kKvBlock * 128), &tile_map, hf, tile, bar, keep);
-      }
+      if (lane < kPagesPerBlock)
+        TmaLoadPageTile(base + lane * kPageTileBytes, &tile_map, (block * 2 + kv) * p.kv_heads + kv_head, bar, keep);
     };
-    const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
-    // S[j & 1] = Q.K_j^T
+    if (lane == 0) {
+      MbarExpectTx(bar_q, kTileBytes);
+      TmaLoad2D(s_q, &q_map, head * kHeadDim, row0, bar_q, normal);
+      TmaLoad2D(s_q + kRegionBytes, &q_map, head * kHeadDim + 64, row0, bar_q, normal);
+    }
+    // K runs one block ahead of V: K_{t+1}'s buffer is free as soon as Q.K_{t-1}^T has completed, long before
+    // P_{t-2}.V_{t-2} - which V_t's buffer waits for - so no K request ever queues behind a V wait.
+    int blk = table_entry(0), blk_next = table_entry(1), blk_next2 = table_entry(2);
+    load_block(0, 0, blk);
+    load_block(0, 1, blk);
+    if (nblk > 1) load_block(1, 0, blk_next);
+#pragma unroll 1
+    for (int t = 1; t < nblk; ++t) {
+      blk = blk_next;                  // block t
+      blk_next = blk_next2;            // block t + 1
+      blk_next2 = table_entry(t + 2);
+      if (t + 1 < nblk) {
+        wait(bar_s0 + 8 * ((t + 1) & 1), ((t - 1) >> 1) & 1);       // K buffer: free once Q.K_{t-1}^T has completed
+        load_block(t + 1, 0, blk_next);
+      }
+      if (t >= 2) wait(bar_o0 + 8 * (t & 1), ((t - 2) >> 1) & 1);   // V buffer: free once P_{t-2}.V_{t-2} has completed
+      load_block(t, 1, blk);
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ MMA issue (lane 0; the warp walks the schedule together)
+    const uint32_t idesc_kk = InstrDesc(kBN / 2), idesc_mn = InstrDescBMn(kHeadDim);
+    // S[j & 1] = Q.K_j^T. In the K buffer the 8-token groups of one dim half lie 1 KiB apart inside a page and 4 KiB
+    // apart from page to page, so one operand tile with a constant group stride is "tokens 0-7 of every page" (g = 0)
+    // or "tokens 8-15 of every page" (g = 1): two N = 64 products per K slice. Column 8 * page + r of product g is
+    // the score of key 16 * page + 8 * g + r; the softmax threads know.
     auto issue_qk = [&](int j) {
       const uint32_t kb = s_k + (j & 1) * kTileBytes;
-      const uint32_t d = tmem_base + (j & 1) * kBN;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t d = tmem_base + (j & 1) * kBN + g * 64;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
+        for (int h = 0; h < 2; ++h) {
+          const uint64_t a = TileDesc(s_q + h * kRegionBytes);
+          const uint64_t b = TileDescSbo(kb + h * (kPageTileBytes / 2) + g * 1024, kPageTileBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
+        }
       }
       UmmaCommit(bar_s0 + 8 * (j & 1));
     };
-    // O += P_j.V_j: K = 16 keys per instruction, V read MN-major where it landed.
+    // O += P_j.V_j: K = 16 keys = one page per instruction; V read MN-major where it landed (8-key groups 1 KiB
+    // apart, the two dim halves 2 KiB apart).
     auto issue_pv = [&](int j) {
       const uint32_t vb = s_v + (j & 1) * kTileBytes, pb = s_p + (j & 1) * kTileBytes;
 #pragma unroll
@@ -222,24 +268,12 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         const uint64_t a = TileDesc(pb + h * kRegionBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t b = TileDescMn(vb + (h * 4 + k) * (16 * 128), kRegionBytes);
+          const uint64_t b = TileDescMn(vb + (h * 4 + k) * kPageTileBytes, kPageTileBytes / 2);
           Umma(tmem_o, a + 2 * k, b, idesc_mn, (j | h | k) ? 1u : 0u);
         }
       }
-      UmmaCommit(bar_o);
+      UmmaCommit(bar_o0 + 8 * (j & 1));
     };
-
-    if (lane == 0) {
-      MbarExpectTx(bar_q, kTileBytes);
-      TmaLoad2D(s_q, &q_map, head * kHeadDim, row0, bar_q, normal);
-      TmaLoad2D(s_q + kRegionBytes, &q_map, head * kHeadDim + 64, row0, bar_q, normal);
-    }
-    load_block(0, 0);
-    load_block(0, 1);
-    if (nblk > 1) {
-      load_block(1, 0);
-      load_block(1, 1);
-    }
     wait(bar_q, 0);
     wait(bar_k0, 0);
     TcFenceAfter();
@@ -247,10 +281,6 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     if (nblk > 1) {
       wait(bar_k0 + 8, 0);
       if (ok && lane == 0) issue_qk(1);
-    }
-    if (nblk > 2) {          // K buffer 0 is free once Q.K_0^T has completed
-      wait(bar_s0, 0);
-      load_block(2, 0);
     }
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
@@ -263,18 +293,9 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         wait(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
         if (ok && lane == 0) issue_qk(j + 2);
       }
-      __syncwarp();                                // the waits below follow lane 0's commits
-      if (j + 3 < nblk) {                          // K buffer of block j+1 is free once its product has completed
-        wait(bar_s0 + 8 * (buf ^ 1), ((j + 1) >> 1) & 1);
-        load_block(j + 3, 0);
-      }
-      if (j + 2 < nblk) {                          // V buffer `buf` is free once P_j.V_j has completed
-        wait(bar_o, j & 1);
-        load_block(j + 2, 1);
-      }
+      __syncwarp();
     }
-    // One-shot barrier for the readers of the finished output. (bar_o's phases alternate parity; a reader
-    // that has not followed every one of them could mistake an older phase for the last.)
+    // One-shot barrier for the readers of the finished output.
     if (ok && lane == 0) UmmaCommit(bar_done);
     __syncwarp();
   } else {
@@ -303,7 +324,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1;
-      const int key0 = j * kBN + hw * 64;
+      // column 16c + i of this thread's half of S is key  key0 + 32c + 16 (i >> 3) + (i & 7)  (see issue_qk)
+      const int key0 = j * kBN + hw * 8;
       const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
       // pass 1: their maximum (raw: the scale is positive)
       float mx = -INFINITY;
@@ -312,7 +334,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
+            mx = fmaxf(mx, key0 + 32 * c + 16 * (i >> 3) + (i & 7) <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
       } else {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
@@ -334,7 +356,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       l *= alpha;
       if (move) m_ref = mx;
       if (j > 0 && __any_sync(0xffffffffu, move)) {
-        wait(bar_o, (j - 1) & 1);     // at most one phase behind: the product two blocks back completed before S_j did
+        wait(bar_o0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
         TcFenceAfter();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -348,7 +370,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         TmemWaitStores();
       }
       // pass 2: probabilities, FP16, into the swizzled K-major P tile; their FP32 sum
-      uint8_t* p_row = smem + kPOff + buf * kTileBytes + hw * kRegionBytes + row * 128;
+      uint8_t* p_row = smem + kPOff + buf * kTileBytes + row * 128;
       const float neg_ref = -m_ref;
       float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
@@ -359,15 +381,19 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
           float p0 = Ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2e, neg_ref));
           float p1 = Ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2e, neg_ref));
           if (diagonal) {
-            p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
-            p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
+            const int key = key0 + 32 * c + 16 * (i >> 3) + (i & 7);
+            p0 = key <= my_pos ? p0 : 0.0f;
+            p1 = key + 1 <= my_pos ? p1 : 0.0f;
           }
           sum0 += p0;
           sum1 += p1;
           packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
         }
-        *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        // P is kept in natural key order: the eight keys 16 * page + 8 * hw .. of page 2c (then 2c + 1) are 16-byte
+        // chunk (2 * page + hw) & 7 of this row in the 64-key region page / 4 = c / 2
+        uint8_t* region = p_row + (c >> 1) * kRegionBytes;
+        *reinterpret_cast<uint4*>(region + ((((4 * c + hw) & 7) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(region + ((((4 * c + 2 + hw) & 7) ^ (row & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
       const float sum = sum0 + sum1;
       l += sum;
@@ -377,7 +403,9 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       if (rows_valid < kBN) {
         wait(bar_v0 + 8 * buf, (j >> 1) & 1);
         if (row >= rows_valid) {
-          uint4* r = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + hw * kRegionBytes + row * 128);
+          // key `row` of the block: page row / 16, token row % 16; this thread clears dim half hw of it
+          uint4* r = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + (row >> 4) * kPageTileBytes +
+                                              hw * (kPageTileBytes / 2) + (row & 15) * 128);
 #pragma unroll
           for (int i = 0; i < 8; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -502,10 +530,10 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: q tensor map (CUresult %d)", static_cast<int>(r));
   }
   {
-    // the pool slice as [tile][dim-half][token][64 halves]; one box = one 64-dim half of one page tile
+    // the pool slice as [tile][dim-half][token][64 halves]; one box = one whole page tile, both dim halves
     const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kKvBlock) * kHeadDim * 2};
-    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 1, 1};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 2, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = g_encode(&tile_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(kv_pool_layer), dims, strides,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
