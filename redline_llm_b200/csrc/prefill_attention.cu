@@ -28,12 +28,13 @@
 //  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
 //    its own quarter of the tensor-memory lanes). Each thread reads its half row of S from tensor memory
 //    (tcgen05.ld 32x32b) twice - the maximum, exchanged with its partner through shared memory, then the
-//    exponentials (ex2.approx in the exp2 domain) - and writes P as FP16 into shared memory in the swizzled
-//    K-major layout by hand (two P buffers). The running reference maximum is only moved when a row's
+//    exponentials (ex2.approx in the exp2 domain) - and writes P as FP16 pairs into tensor memory
+//    (tcgen05.st, two P buffers of 64 columns), from where the P.V product takes its A operand: P never
+//    touches shared memory, whose bandwidth is what bounds this kernel. The running reference maximum is only moved when a row's
 //    maximum exceeds it by more than 2^8: P then stays below 2^8 (exact in FP16's range), and the rescaling of
 //    the running output - a read-modify-write of the row in tensor memory - almost never happens after the
 //    first block; numerator and denominator always share one reference, so the result does not depend on it.
-//  * O += P.V: A = P (K-major) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
+//  * O += P.V: A = P (in tensor memory) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
 //    8 keys x 64 dims, 1024 B between key groups, 2 KiB between the dim halves, one page per K = 16 slice -
 //    accumulated over all blocks in tensor-memory columns 256-383; read once at the end, divided by the row
 //    sum, rounded once.
@@ -60,13 +61,13 @@ constexpr int kTileBytes = 2 * kRegionBytes;   // two 64-wide halves
 constexpr int kQOff = 0;
 constexpr int kKOff = kQOff + kTileBytes;          // 2 buffers
 constexpr int kVOff = kKOff + 2 * kTileBytes;      // 2 buffers
-constexpr int kPOff = kVOff + 2 * kTileBytes;      // 2 buffers
-constexpr int kBarOff = kPOff + 2 * kTileBytes;    // mbarriers, tmem slot
+constexpr int kBarOff = kVOff + 2 * kTileBytes;    // mbarriers, tmem slot
 constexpr int kXOff = kBarOff + 128;               // row maxima [2 iterations][2 halves][128] (row sums reuse one half at the end)
 constexpr int kSmemNeeded = kXOff + 4 * 128 * 4;   // from a 1024-byte aligned base
-constexpr int kSmemBytes = 227 * 1024;             // everything a CTA may have: the rest is slack for aligning the base
-static_assert(kSmemNeeded <= kSmemBytes, "prefill attention shared memory exceeds the per-CTA limit");
-constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383
+constexpr int kSmemBytes = kSmemNeeded + 1024;     // + slack for aligning the base
+static_assert(kSmemBytes <= 227 * 1024, "prefill attention shared memory exceeds the per-CTA limit");
+constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383, P (FP16 pairs): 384-447 and 448-511
+constexpr int kTmemP = 384;
 constexpr float kRescaleThreshold = 8.0f;   // log2: P never exceeds 2^8
 
 struct Params {
@@ -121,6 +122,20 @@ __device__ __forceinline__ void TmemStore16(uint32_t taddr, const uint32_t (&r)[
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void TmemStore4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+// D (+)= A.B with A in tensor memory (row i in lane i, two FP16 per 32-bit column along K) and B in shared memory.
+__device__ __forceinline__ void UmmaTs(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void TmemWaitStores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
 
@@ -137,7 +152,6 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     return;
   }
   const uint32_t s_q = SmemAddr(smem + kQOff), s_k = SmemAddr(smem + kKOff), s_v = SmemAddr(smem + kVOff);
-  const uint32_t s_p = SmemAddr(smem + kPOff);
   const uint32_t bars = SmemAddr(smem + kBarOff);
   // Every barrier that more than one phase passes through belongs to ONE buffer (index = block & 1): a waiter
   // names a phase by its parity alone, which is only safe while the barrier cannot run two phases ahead of
@@ -262,15 +276,12 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // O += P_j.V_j: K = 16 keys = one page per instruction; V read MN-major where it landed (8-key groups 1 KiB
     // apart, the two dim halves 2 KiB apart).
     auto issue_pv = [&](int j) {
-      const uint32_t vb = s_v + (j & 1) * kTileBytes, pb = s_p + (j & 1) * kTileBytes;
+      const uint32_t vb = s_v + (j & 1) * kTileBytes;
+      const uint32_t pt = tmem_base + kTmemP + (j & 1) * (kBN / 2);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint64_t a = TileDesc(pb + h * kRegionBytes);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t b = TileDescMn(vb + (h * 4 + k) * kPageTileBytes, kPageTileBytes / 2);
-          Umma(tmem_o, a + 2 * k, b, idesc_mn, (j | h | k) ? 1u : 0u);
-        }
+      for (int k = 0; k < kPagesPerBlock; ++k) {   // 16 keys = 8 columns of P = one page of V per instruction
+        const uint64_t b = TileDescMn(vb + k * kPageTileBytes, kPageTileBytes / 2);
+        UmmaTs(tmem_o, pt + 8 * k, b, idesc_mn, (j | k) ? 1u : 0u);
       }
       UmmaCommit(bar_o0 + 8 * (j & 1));
     };
@@ -369,8 +380,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         }
         TmemWaitStores();
       }
-      // pass 2: probabilities, FP16, into the swizzled K-major P tile; their FP32 sum
-      uint8_t* p_row = smem + kPOff + buf * kTileBytes + row * 128;
+      // pass 2: probabilities, FP16, into tensor memory (the A operand of P.V); their FP32 sum
+      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 4 * hw;
       const float neg_ref = -m_ref;
       float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
@@ -389,12 +400,12 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
           sum1 += p1;
           packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
         }
-        // P is kept in natural key order: the eight keys 16 * page + 8 * hw .. of page 2c (then 2c + 1) are 16-byte
-        // chunk (2 * page + hw) & 7 of this row in the 64-key region page / 4 = c / 2
-        uint8_t* region = p_row + (c >> 1) * kRegionBytes;
-        *reinterpret_cast<uint4*>(region + ((((4 * c + hw) & 7) ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        *reinterpret_cast<uint4*>(region + ((((4 * c + 2 + hw) & 7) ^ (row & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        // P goes to tensor memory in natural key order, two FP16 per column: the eight keys 16 * page + 8 * hw ..
+        // of page 2c (then 2c + 1) are columns 8 * page + 4 * hw .. + 3 of this row
+        TmemStore4(p_addr + 16 * c, packed[0], packed[1], packed[2], packed[3]);
+        TmemStore4(p_addr + 16 * c + 8, packed[4], packed[5], packed[6], packed[7]);
       }
+      TmemWaitStores();
       const float sum = sum0 + sum1;
       l += sum;
       // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
@@ -409,8 +420,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 #pragma unroll
           for (int i = 0; i < 8; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared rows, visible to the tensor pipe
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and cleared V rows) visible to the tensor pipe
       if (j + 1 < nblk) fetch_scores(j + 1);
       TcFenceBefore();
       MbarArrive(bar_p0 + 8 * buf);
