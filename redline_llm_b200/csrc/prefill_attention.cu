@@ -14,15 +14,14 @@
 //  * Warp 9 requests every tile by TMA (copies spread over its lanes), warp 8 issues every tcgen05.mma: table
 //    reads and copy requests never sit between two products. Q tile and K/V
 //    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
-//    [16 tokens][128 dims]; one 4 KiB tensor copy lands it as [dim half][16 tokens][128 B] at 4 KiB * page
-//    (the TMA unit is paid per copy, not per byte: 16 copies per block instead of 32 was worth 1.4 x).
+//    [16 tokens][128 dims]. A K tile arrives as two 2 KiB copies, one per 64-dim half, landing at row 16 * page of a
+//    [128 rows][128 B] region, so eight pages form exactly the K-major operand tile of an N = 128 product; a V tile
+//    arrives as one 4 KiB copy ([dim half][16 tokens][128 B] at 4 KiB * page), which is what the MN-major operand
+//    of P.V reads one page per K = 16 slice. (The TMA unit is paid per copy, the tensor pipe per instruction.)
 //    Block-table indirection costs nothing but the copy's coordinate. K and V blocks are double-buffered;
 //    the six query heads of a KV group and all query tiles re-read the same pages from L2.
-//  * S = Q.K^T: M = 128 query rows, K = 16 dims x 8, both operands K-major in shared memory, FP32 accumulator
-//    in tensor memory. In the K buffer the 8-token groups of a dim half are 1 KiB apart inside a page and 4 KiB
-//    from page to page, so the 128 keys are taken as two N = 64 operand tiles with a constant group stride -
-//    tokens 0-7 of every page, tokens 8-15 of every page; the columns of S are permuted accordingly and the
-//    softmax puts P back in natural key order. Two S buffers (columns 0-127, 128-255): the product of
+//  * S = Q.K^T: M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major in shared memory,
+//    FP32 accumulator in tensor memory. Two S buffers (columns 0-127, 128-255): the product of
 //    block j+2 is issued as soon as the softmax of block j has released its buffer, so the tensor pipe runs
 //    under the softmax of block j+1.
 //  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
@@ -100,10 +99,14 @@ __device__ __forceinline__ void TmaLoadPageTile(uint32_t dst, const CUtensorMap*
       "l"(map), "r"(0), "r"(tile), "r"(bar), "l"(policy)
       : "memory");
 }
-// K-major operand whose 8-row groups lie `sbo` bytes apart (128-byte swizzle, rows of 128 B).
-__device__ __forceinline__ uint64_t TileDescSbo(uint32_t smem_addr, uint32_t sbo_bytes) {
-  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(sbo_bytes >> 4) << 32) |
-         (1ull << 46) | (2ull << 61);
+// One 64-dim half of a page tile: [16 tokens][64 halves] = 2 KiB (second map: same tensor, box of one dim half).
+__device__ __forceinline__ void TmaLoadHalfTile(uint32_t dst, const CUtensorMap* map, int half_idx, int tile,
+                                                uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %2, %3, %4}], [%5], %6;" ::"r"(dst),
+      "l"(map), "r"(0), "r"(half_idx), "r"(tile), "r"(bar), "l"(policy)
+      : "memory");
 }
 constexpr int kPageTileBytes = kKvBlock * kHeadDim * 2;   // 4096: [2 dim halves][16 tokens][128 B]
 __device__ __forceinline__ void MbarArrive(uint32_t bar) {
@@ -122,8 +125,9 @@ __device__ __forceinline__ void TmemStore16(uint32_t taddr, const uint32_t (&r)[
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-__device__ __forceinline__ void TmemStore4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+__device__ __forceinline__ void TmemStore8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
 }
 // D (+)= A.B with A in tensor memory (row i in lane i, two FP16 per 32-bit column along K) and B in shared memory.
@@ -141,7 +145,7 @@ __device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;
 
 __global__ void __launch_bounds__(kThreads, 1)
 PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap q_map,
-                            const __grid_constant__ CUtensorMap tile_map) {
+                            const __grid_constant__ CUtensorMap tile_map, const __grid_constant__ CUtensorMap half_map) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -207,26 +211,38 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 
   if (warp == 9) {
     // ------------------------------------------------------------ loader: every TMA request
-    // A block of K or V is 8 copies of 4 KiB, one per lane and page. The block id of a page serves K and V alike
-    // and is read from the table two blocks ahead of its use.
+    // A block is 16 copies of 2 KiB for K and 8 of 4 KiB for V (the TMA unit is paid per copy, the tensor pipe per
+    // instruction: K in halves keeps Q.K^T at N = 128). The block id of a page serves K and V alike and is read
+    // from the table two blocks ahead of its use.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&half_map) : "memory");
     }
     const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
+    // lane l < 16 serves page l / 2: K as two copies of 2 KiB (lanes 2p, 2p + 1: one per dim half), V as one copy
+    // of 4 KiB (lane 2p)
     auto table_entry = [&](int j) {
-      const int page = j * kPagesPerBlock + lane;
-      return (lane < kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+      const int page = j * kPagesPerBlock + (lane >> 1);
+      return (lane < 2 * kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
     };
-    // Block j of K (kv = 0) or V (kv = 1) into buffer j & 1: page `lane` lands at lane * 4 KiB as
-    // [dim half][16 tokens][128 B] (one copy per page; a copy costs the TMA unit about as much whatever its size).
-    auto load_block = [&](int j, int kv, int block) {
-      const uint32_t base = (kv ? s_v : s_k) + (j & 1) * kTileBytes;
-      const uint32_t bar = (kv ? bar_v0 : bar_k0) + 8 * (j & 1);
+    // K block j into buffer j & 1 as the K-major operand tile: region `dim half`, rows 16 * page .. + 15.
+    auto load_k = [&](int j, int block) {
+      const uint32_t base = s_k + (j & 1) * kTileBytes, bar = bar_k0 + 8 * (j & 1);
       if (lane == 0) MbarExpectTx(bar, kTileBytes);
       __syncwarp();
-      if (lane < kPagesPerBlock)
-        TmaLoadPageTile(base + lane * kPageTileBytes, &tile_map, (block * 2 + kv) * p.kv_heads + kv_head, bar, keep);
+      if (lane < 2 * kPagesPerBlock)
+        TmaLoadHalfTile(base + (lane & 1) * kRegionBytes + (lane >> 1) * (kKvBlock * 128), &half_map, lane & 1,
+                        (block * 2 + 0) * p.kv_heads + kv_head, bar, keep);
+    };
+    // V block j into buffer j & 1, page p at 4 KiB * p as [dim half][16 tokens][128 B]: what the MN-major operand of
+    // P.V reads one page per K = 16 slice.
+    auto load_v = [&](int j, int block) {
+      const uint32_t base = s_v + (j & 1) * kTileBytes, bar = bar_v0 + 8 * (j & 1);
+      if (lane == 0) MbarExpectTx(bar, kTileBytes);
+      __syncwarp();
+      if (lane < 2 * kPagesPerBlock && !(lane & 1))
+        TmaLoadPageTile(base + (lane >> 1) * kPageTileBytes, &tile_map, (block * 2 + 1) * p.kv_heads + kv_head, bar, keep);
     };
     if (lane == 0) {
       MbarExpectTx(bar_q, kTileBytes);
@@ -236,9 +252,9 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // K runs one block ahead of V: K_{t+1}'s buffer is free as soon as Q.K_{t-1}^T has completed, long before
     // P_{t-2}.V_{t-2} - which V_t's buffer waits for - so no K request ever queues behind a V wait.
     int blk = table_entry(0), blk_next = table_entry(1), blk_next2 = table_entry(2);
-    load_block(0, 0, blk);
-    load_block(0, 1, blk);
-    if (nblk > 1) load_block(1, 0, blk_next);
+    load_k(0, blk);
+    load_v(0, blk);
+    if (nblk > 1) load_k(1, blk_next);
 #pragma unroll 1
     for (int t = 1; t < nblk; ++t) {
       blk = blk_next;                  // block t
@@ -246,30 +262,23 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       blk_next2 = table_entry(t + 2);
       if (t + 1 < nblk) {
         wait(bar_s0 + 8 * ((t + 1) & 1), ((t - 1) >> 1) & 1);       // K buffer: free once Q.K_{t-1}^T has completed
-        load_block(t + 1, 0, blk_next);
+        load_k(t + 1, blk_next);
       }
       if (t >= 2) wait(bar_o0 + 8 * (t & 1), ((t - 2) >> 1) & 1);   // V buffer: free once P_{t-2}.V_{t-2} has completed
-      load_block(t, 1, blk);
+      load_v(t, blk);
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------ MMA issue (lane 0; the warp walks the schedule together)
-    const uint32_t idesc_kk = InstrDesc(kBN / 2), idesc_mn = InstrDescBMn(kHeadDim);
-    // S[j & 1] = Q.K_j^T. In the K buffer the 8-token groups of one dim half lie 1 KiB apart inside a page and 4 KiB
-    // apart from page to page, so one operand tile with a constant group stride is "tokens 0-7 of every page" (g = 0)
-    // or "tokens 8-15 of every page" (g = 1): two N = 64 products per K slice. Column 8 * page + r of product g is
-    // the score of key 16 * page + 8 * g + r; the softmax threads know.
+    const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
+    // S[j & 1] = Q.K_j^T
     auto issue_qk = [&](int j) {
       const uint32_t kb = s_k + (j & 1) * kTileBytes;
+      const uint32_t d = tmem_base + (j & 1) * kBN;
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        const uint32_t d = tmem_base + (j & 1) * kBN + g * 64;
+      for (int h = 0; h < 2; ++h) {
+        const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint64_t a = TileDesc(s_q + h * kRegionBytes);
-          const uint64_t b = TileDescSbo(kb + h * (kPageTileBytes / 2) + g * 1024, kPageTileBytes);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
-        }
+        for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
       }
       UmmaCommit(bar_s0 + 8 * (j & 1));
     };
@@ -335,8 +344,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1;
-      // column 16c + i of this thread's half of S is key  key0 + 32c + 16 (i >> 3) + (i & 7)  (see issue_qk)
-      const int key0 = j * kBN + hw * 8;
+      const int key0 = j * kBN + hw * 64;
       const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
       // pass 1: their maximum (raw: the scale is positive)
       float mx = -INFINITY;
@@ -345,7 +353,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            mx = fmaxf(mx, key0 + 32 * c + 16 * (i >> 3) + (i & 7) <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
+            mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
       } else {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
@@ -381,7 +389,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         TmemWaitStores();
       }
       // pass 2: probabilities, FP16, into tensor memory (the A operand of P.V); their FP32 sum
-      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 4 * hw;
+      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 32 * hw;
       const float neg_ref = -m_ref;
       float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
@@ -392,18 +400,15 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
           float p0 = Ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2e, neg_ref));
           float p1 = Ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2e, neg_ref));
           if (diagonal) {
-            const int key = key0 + 32 * c + 16 * (i >> 3) + (i & 7);
-            p0 = key <= my_pos ? p0 : 0.0f;
-            p1 = key + 1 <= my_pos ? p1 : 0.0f;
+            p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
+            p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
           }
           sum0 += p0;
           sum1 += p1;
           packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
         }
-        // P goes to tensor memory in natural key order, two FP16 per column: the eight keys 16 * page + 8 * hw ..
-        // of page 2c (then 2c + 1) are columns 8 * page + 4 * hw .. + 3 of this row
-        TmemStore4(p_addr + 16 * c, packed[0], packed[1], packed[2], packed[3]);
-        TmemStore4(p_addr + 16 * c + 8, packed[4], packed[5], packed[6], packed[7]);
+        // P goes to tensor memory in key order, two FP16 per column: keys 64 * hw + 16 * c .. + 15 of this row
+        TmemStore8(p_addr + 8 * c, packed);
       }
       TmemWaitStores();
       const float sum = sum0 + sum1;
@@ -551,6 +556,18 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool tensor map (CUresult %d)", static_cast<int>(r));
   }
+  CUtensorMap half_map;
+  {
+    // the same view with a box of one dim half: [16 tokens][64 halves] = 2 KiB
+    const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kKvBlock) * kHeadDim * 2};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = g_encode(&half_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(kv_pool_layer), dims, strides,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool half-tile map (CUresult %d)", static_cast<int>(r));
+  }
   Params p;
   p.out = static_cast<half*>(out);
   p.out_stride = out_row_stride;
@@ -563,7 +580,7 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   p.scale_log2e = scale * 1.4426950408889634f;
   p.error_flag = st->error_flag;
   const dim3 grid((chunk_len + kBM - 1) / kBM, num_q_heads);
-  PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, tile_map);
+  PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, tile_map, half_map);
   return LaunchStatus("paged_prefill_attention");
 }
 
