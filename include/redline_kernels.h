@@ -184,6 +184,15 @@ int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stride, const v
 int rl_prefill_attention_health(int* flag_out);
 
 /*
+ * Tuning knob of rl_launch_paged_prefill_attention: the longest run of 128-key blocks one CTA takes before a
+ * (query tile, head) pair is cut across CTAs (their records are combined in run order by the CTA that arrives
+ * last, so results do not depend on it beyond FP32 summation order). 0 (default) = chosen per launch from the
+ * chunk's shape and the SM count. Process-wide. A launch that cuts pairs keeps a scratch area in device memory
+ * (grown on demand outside stream capture, 66 KB per work item). No counterpart in the reference.
+ */
+int rl_prefill_attention_set_split_blocks(int blocks);
+
+/*
  * Decode input plumbing on the device: after a step's greedy argmax, prepare the next step's inputs in
  * place - input_ids[i] <- control[1 + i] if that is >= 0 (a scripted token), else sampled_tokens[i];
  * positions[i] <- seq_lens[i]; seq_lens[i] += 1 - for every row with seq_len > 0, when control[0] != 0

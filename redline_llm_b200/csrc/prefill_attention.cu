@@ -10,7 +10,10 @@
 // probabilities rounded to FP16 for the P.V product, FP32 accumulation, one FP16 rounding of acc / l -
 // with nothing but Q, the pages and the output ever touching global memory.
 //
-// Mapping. One CTA per (128-row query tile, query head); ten warps.
+// Mapping. One CTA per (128-row query tile, query head) - or per run of at most 16 key blocks of such a pair when
+// its context is longer (2048 keys): the runs' unnormalised outputs meet in a scratch area and the CTA that
+// arrives last combines them in run order, so long contexts fill the machine and the result does not depend
+// on timing. Ten warps.
 //  * Warp 9 requests every tile by TMA (copies spread over its lanes), warp 8 issues every tcgen05.mma: table
 //    reads and copy requests never sit between two products. Q tile and K/V
 //    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
@@ -68,6 +71,7 @@ static_assert(kSmemBytes <= 227 * 1024, "prefill attention shared memory exceeds
 constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383, P (FP16 pairs): 384-447 and 448-511
 constexpr int kTmemP = 384;
 constexpr float kRescaleThreshold = 8.0f;   // log2: P never exceeds 2^8
+constexpr int kPartialFloats = kBM * kHeadDim + 2 * kBM;   // o[128][128] unnormalised, m[128], l[128]
 
 struct Params {
   half* out;
@@ -80,6 +84,10 @@ struct Params {
   int kv_heads;
   float scale_log2e;
   int* error_flag;
+  int n_tiles;        // query tiles of the chunk
+  int split_blocks;   // longest run of key blocks one CTA takes
+  float* partials;    // one record of kPartialFloats per (head, work item) for pairs cut across CTAs
+  int* tickets;       // one counter per (head, query tile), zero between launches
 };
 
 // K/V block operand as a B matrix stored [key][dim] (MN-major, 128-byte swizzle): atoms of 8 key rows x 128 B;
@@ -166,14 +174,28 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   float* xmax = reinterpret_cast<float*>(smem + kXOff);          // [2][2][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // long tiles first: the last query tile of the chunk attends to the most keys
-  const int tile_q = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  // Work items of a head, long tiles first (the last query tile of the chunk attends to the most keys): a tile
+  // whose keys fill more than `split_blocks` blocks is cut into equal runs of blocks, one CTA each; this CTA is
+  // item blockIdx.x = run `split` of `nsplit` of tile `tile_q`, blocks jb0 .. jb0 + nblk - 1 of that tile.
   const int head = blockIdx.y;
   const int kv_head = head / (p.q_heads / p.kv_heads);
-  const int row0 = tile_q * kBM;
   const int kv_len = p.chunk_start + p.chunk_len;
-  const int last_pos = min(p.chunk_start + row0 + kBM, kv_len) - 1;   // newest key any row of this tile sees
-  const int nblk = last_pos / kBN + 1;
+  int tile_q = 0, split = 0, nsplit = 1, tile_blocks = 1;
+  {
+    int item = blockIdx.x;
+    for (int t = p.n_tiles - 1; t >= 0; --t) {
+      const int nb = (min(p.chunk_start + (t + 1) * kBM, kv_len) - 1) / kBN + 1;
+      const int ns = (nb + p.split_blocks - 1) / p.split_blocks;
+      if (item < ns || t == 0) {
+        tile_q = t; split = item; nsplit = ns; tile_blocks = nb;
+        break;
+      }
+      item -= ns;
+    }
+  }
+  const int row0 = tile_q * kBM;
+  const int jb0 = split * tile_blocks / nsplit;
+  const int nblk = (split + 1) * tile_blocks / nsplit - jb0;          // blocks of THIS item, indexed 0 .. nblk - 1 below
 
   if (tid == 0) {
     MbarInit(bar_q, 1);
@@ -223,7 +245,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // lane l < 16 serves page l / 2: K as two copies of 2 KiB (lanes 2p, 2p + 1: one per dim half), V as one copy
     // of 4 KiB (lane 2p)
     auto table_entry = [&](int j) {
-      const int page = j * kPagesPerBlock + (lane >> 1);
+      const int page = (jb0 + j) * kPagesPerBlock + (lane >> 1);
       return (lane < 2 * kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
     };
     // K block j into buffer j & 1 as the K-major operand tile: region `dim half`, rows 16 * page .. + 15.
@@ -344,8 +366,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1;
-      const int key0 = j * kBN + hw * 64;
-      const bool diagonal = j * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
+      const int key0 = (jb0 + j) * kBN + hw * 64;
+      const bool diagonal = (jb0 + j) * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
       // pass 1: their maximum (raw: the scale is positive)
       float mx = -INFINITY;
       if (diagonal) {
@@ -415,7 +437,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       l += sum;
       // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
       // would poison the row: clear them once the block has landed.
-      const int rows_valid = kv_len - j * kBN;
+      const int rows_valid = kv_len - (jb0 + j) * kBN;
       if (rows_valid < kBN) {
         wait(bar_v0 + 8 * buf, (j >> 1) & 1);
         if (row >= rows_valid) {
@@ -432,28 +454,98 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       MbarArrive(bar_p0 + 8 * buf);
     }
 
-    // ---- the running output: this thread's 64 dims of its row, divided by the row's sum
-    // (through the exchange buffer the last block did not use: every read of it lies before that block's barrier)
+    // ---- the running output: this thread's 64 dims of its row
+    // (the row sums of the two key halves meet through the exchange buffer the last block did not use: every
+    // read of it lies before that block's barrier)
     float* xsum = xmax + (nblk & 1) * 256;
     xsum[hw * 128 + row] = l;
     SoftmaxBarrier();
-    const float inv = 1.0f / (l + xsum[(hw ^ 1) * 128 + row]);
+    const float l_row = l + xsum[(hw ^ 1) * 128 + row];
     wait(bar_done, 0);
     TcFenceAfter();
     const int out_row = row0 + row;
     half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + hw * 64;
+    if (nsplit == 1) {
+      // the whole key range was this CTA's: divide by the row's sum, round once, store
+      const float inv = 1.0f / l_row;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t raw[16];
-      TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
-      TmemWaitLoads(raw);
-      if (ok && out_row < p.chunk_len) {
-        uint32_t w[8];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+        TmemWaitLoads(raw);
+        if (ok && out_row < p.chunk_len) {
+          uint32_t w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          w[i] = AsU32(__floats2half2_rn(__uint_as_float(raw[2 * i]) * inv, __uint_as_float(raw[2 * i + 1]) * inv));
-        *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          for (int i = 0; i < 8; ++i)
+            w[i] = AsU32(__floats2half2_rn(__uint_as_float(raw[2 * i]) * inv, __uint_as_float(raw[2 * i + 1]) * inv));
+          *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    } else {
+      // One run of a tile's key blocks: publish (o unnormalised, m, l) and take a ticket; whichever CTA of the
+      // tile comes last combines ALL runs' records, its own included, in run order - so the result does not
+      // depend on who that is.
+      float* rec0 = p.partials + (static_cast<size_t>(head) * gridDim.x + (blockIdx.x - split)) * kPartialFloats;
+      float* rec = rec0 + static_cast<size_t>(split) * kPartialFloats;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[16];
+        TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+        TmemWaitLoads(raw);
+        float4* o4 = reinterpret_cast<float4*>(rec + row * kHeadDim + hw * 64 + c * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          o4[i] = make_float4(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]), __uint_as_float(raw[4 * i + 2]),
+                              __uint_as_float(raw[4 * i + 3]));
+      }
+      if (hw == 0) {
+        rec[kBM * kHeadDim + row] = m_ref;
+        rec[kBM * kHeadDim + kBM + row] = l_row;
+      }
+      __threadfence();
+      SoftmaxBarrier();                       // every thread's part of the record is written and fenced
+      int* last = reinterpret_cast<int*>(xmax + ((nblk + 1) & 1) * 256);
+      if (tid == 0) {
+        int* ticket = p.tickets + head * p.n_tiles + tile_q;
+        const int t = atomicAdd(ticket, 1);
+        if (t == nsplit - 1) *ticket = 0;     // everyone has arrived: re-arm for the next launch
+        *last = t == nsplit - 1;
+      }
+      SoftmaxBarrier();
+      if (*last) {
+        __threadfence();
+        float mx = -INFINITY;
+        for (int sidx = 0; sidx < nsplit; ++sidx) mx = fmaxf(mx, __ldcg(rec0 + sidx * kPartialFloats + kBM * kHeadDim + row));
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        float den = 0.0f;
+#pragma unroll 1
+        for (int sidx = 0; sidx < nsplit; ++sidx) {
+          const float* r = rec0 + static_cast<size_t>(sidx) * kPartialFloats;
+          const float wgt = Ex2(__ldcg(r + kBM * kHeadDim + row) - mx);      // 0 for a run that saw no key of this row
+          den = fmaf(wgt, __ldcg(r + kBM * kHeadDim + kBM + row), den);
+          const float4* o4 = reinterpret_cast<const float4*>(r + row * kHeadDim + hw * 64);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float4 v = __ldcg(o4 + i);
+            acc[4 * i] = fmaf(wgt, v.x, acc[4 * i]);
+            acc[4 * i + 1] = fmaf(wgt, v.y, acc[4 * i + 1]);
+            acc[4 * i + 2] = fmaf(wgt, v.z, acc[4 * i + 2]);
+            acc[4 * i + 3] = fmaf(wgt, v.w, acc[4 * i + 3]);
+          }
+        }
+        if (ok && out_row < p.chunk_len) {
+          const float inv = 1.0f / den;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[i] = AsU32(__floats2half2_rn(acc[c * 8 + 2 * i] * inv, acc[c * 8 + 2 * i + 1] * inv));
+            *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
       }
     }
   }
@@ -473,10 +565,39 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
   bool ready = false;
   int* error_flag = nullptr;
+  // Scratch of launches that cut (tile, head) pairs across CTAs: grown on demand, never shrunk. (Prompt
+  // ingestion is not captured in a graph; a launch that needs more than it has synchronises the device once.)
+  float* partials = nullptr;
+  size_t partial_floats = 0;
+  int* tickets = nullptr;
+  size_t ticket_ints = 0;
 };
 DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 std::mutex g_mutex;
+int g_split_blocks = 0;   // 0: chosen per launch (ChooseSplitBlocks); > 0: forced (rl_prefill_attention_set_split_blocks)
+
+// Longest run of key blocks one CTA should take. A (tile, head) pair is cut into r runs when that fills the machine
+// better: the launch is modelled as ceil(items / SMs) waves of one run each - 1.2 us per block, 6.5 us of set-up and
+// tear-down per CTA, 13 us when the CTA also publishes and merges a record (figures measured on B200) - and r is
+// the value that minimises it. Long prompts' last chunks (few rows, tens of thousands of keys) gain up to 4.5 x,
+// chunks that already fill the machine more than twice over are left whole.
+int ChooseSplitBlocks(int n_tiles, int heads, int max_blocks_per_tile, int sm_count) {
+  const double base = static_cast<double>(n_tiles) * heads;
+  double best = 0.0;
+  int best_r = 1;
+  for (int r = 1; r <= 32 && r <= max_blocks_per_tile; ++r) {
+    const int run = (max_blocks_per_tile + r - 1) / r;
+    if (r > 1 && run < 8) break;
+    const double waves = static_cast<double>((static_cast<long long>(base * r) + sm_count - 1) / sm_count);
+    const double cost = waves * (run * 1.2 + (r > 1 ? 13.0 : 6.5));
+    if (r == 1 || cost < best) {
+      best = cost;
+      best_r = r;
+    }
+  }
+  return (max_blocks_per_tile + best_r - 1) / best_r;
+}
 
 int EnsureReady(DeviceState** out_state) {
   const int dev = CurrentDeviceIndex();
@@ -568,7 +689,54 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool half-tile map (CUresult %d)", static_cast<int>(r));
   }
+  // Work items per head: a tile with more than split_blocks key blocks is cut into ceil(blocks / split_blocks) runs.
+  const int n_tiles_all = (chunk_len + kBM - 1) / kBM;
+  const int max_tile_blocks = static_cast<int>((static_cast<int64_t>(chunk_start) + chunk_len - 1) / kBN) + 1;
+  const int split_blocks = g_split_blocks > 0 ? g_split_blocks
+                                              : ChooseSplitBlocks(n_tiles_all, num_q_heads, max_tile_blocks, CurrentDeviceFacts().sm_count);
+  const int n_tiles = (chunk_len + kBM - 1) / kBM;
+  const int64_t kv_len = static_cast<int64_t>(chunk_start) + chunk_len;
+  int64_t items = 0;
+  bool any_split = false;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int64_t last = (static_cast<int64_t>(chunk_start) + static_cast<int64_t>(t + 1) * kBM < kv_len
+                              ? static_cast<int64_t>(chunk_start) + static_cast<int64_t>(t + 1) * kBM
+                              : kv_len) - 1;
+    const int nb = static_cast<int>(last / kBN) + 1;
+    const int ns = (nb + split_blocks - 1) / split_blocks;
+    items += ns;
+    any_split |= ns > 1;
+  }
+  if (items > 65535 * 32) return Fail(RL_E_TOO_LARGE, "paged_prefill_attention: chunk too large (%lld work items per head)", static_cast<long long>(items));
+  if (any_split) {
+    const size_t need = static_cast<size_t>(num_q_heads) * static_cast<size_t>(items) * kPartialFloats;
+    const size_t need_tickets = static_cast<size_t>(num_q_heads) * n_tiles;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (st->partial_floats < need) {
+      cudaDeviceSynchronize();
+      if (st->partials) cudaFree(st->partials);
+      st->partials = nullptr;
+      st->partial_floats = 0;
+      const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&st->partials), need * sizeof(float));
+      if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_prefill_attention: %zu MB of scratch: %s", need * 4 >> 20, cudaGetErrorString(e));
+      st->partial_floats = need;
+    }
+    if (st->ticket_ints < need_tickets) {
+      cudaDeviceSynchronize();
+      if (st->tickets) cudaFree(st->tickets);
+      st->tickets = nullptr;
+      st->ticket_ints = 0;
+      cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&st->tickets), need_tickets * sizeof(int));
+      if (e == cudaSuccess) e = cudaMemset(st->tickets, 0, need_tickets * sizeof(int));
+      if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_prefill_attention: tickets: %s", cudaGetErrorString(e));
+      st->ticket_ints = need_tickets;
+    }
+  }
   Params p;
+  p.n_tiles = n_tiles;
+  p.split_blocks = split_blocks;
+  p.partials = st->partials;
+  p.tickets = st->tickets;
   p.out = static_cast<half*>(out);
   p.out_stride = out_row_stride;
   p.table_row = block_table_row;
@@ -579,7 +747,7 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   p.kv_heads = num_kv_heads;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.error_flag = st->error_flag;
-  const dim3 grid((chunk_len + kBM - 1) / kBM, num_q_heads);
+  const dim3 grid(static_cast<unsigned>(items), num_q_heads);
   PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, tile_map, half_map);
   return LaunchStatus("paged_prefill_attention");
 }
@@ -595,5 +763,11 @@ extern "C" int rl_prefill_attention_health(int* flag_out) {
   if (e == cudaSuccess) e = cudaMemcpy(flag_out, st.error_flag, sizeof(int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && *flag_out != 0) e = cudaMemset(st.error_flag, 0, sizeof(int));
   if (e != cudaSuccess) return Fail(static_cast<int>(e), "rl_prefill_attention_health: %s", cudaGetErrorString(e));
+  return RL_OK;
+}
+
+extern "C" int rl_prefill_attention_set_split_blocks(int blocks) {
+  if (blocks < 0) return rl::Fail(RL_E_BAD_SHAPE, "rl_prefill_attention_set_split_blocks: 0 (automatic) or a positive block count");
+  rl::pfa::g_split_blocks = blocks;
   return RL_OK;
 }

@@ -26,7 +26,7 @@ ABI_SYMBOLS = (
     "rl_attention_set_prologue_overlap", "rl_launch_kv_gather", "rl_launch_prefill_softmax",
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
     "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter", "rl_launch_decode_advance",
-    "rl_launch_paged_prefill_attention", "rl_prefill_attention_health", "rl_attention_test_wait_expiry",
+    "rl_launch_paged_prefill_attention", "rl_prefill_attention_health", "rl_attention_test_wait_expiry", "rl_prefill_attention_set_split_blocks",
 )
 
 
@@ -72,6 +72,7 @@ def lib() -> C.CDLL:
         L.rl_launch_paged_prefill_attention.argtypes = [vp, i64, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]
         L.rl_prefill_attention_health.argtypes = [C.POINTER(C.c_int)]
         L.rl_attention_test_wait_expiry.argtypes = [C.c_int, C.c_int64]
+        L.rl_prefill_attention_set_split_blocks.argtypes = [C.c_int]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -199,6 +200,11 @@ def launch_paged_prefill_attention(out, out_row_stride, q, q_row_stride, kv_pool
         _ptr(out), out_row_stride, _ptr(q, q_offset), q_row_stride, _ptr(kv_pool_layer), block_table_row.data_ptr(),
         max_blocks_per_seq, chunk_start, chunk_len, num_q_heads, num_kv_heads, head_dim, scale, _stream(stream)),
         "paged prefill attention")
+
+
+def set_prefill_attention_split_blocks(blocks: int) -> None:
+    """Longest run of 128-key blocks per CTA in the prefill attention kernel (0 = chosen per launch)."""
+    _check(lib().rl_prefill_attention_set_split_blocks(blocks), "rl_prefill_attention_set_split_blocks")
 
 
 def prefill_attention_health() -> int:

@@ -55,7 +55,8 @@ def run_fused(case, chunk_start, chunk_len, q_stride=2048, out_stride=1536, extr
 
 
 @pytest.mark.parametrize("chunk_start,chunk_len", [(0, 1), (0, 16), (0, 127), (0, 128), (0, 129), (0, 300), (5, 123),
-                                                   (1000, 257), (1024, 256), (4000, 200), (0, 1024), (3000, 1030)])
+                                                   (1000, 257), (1024, 256), (4000, 200), (0, 1024), (3000, 1030),
+                                                   (8000, 200), (5000, 129), (2040, 40)])
 def test_chunk_against_the_cpu_checker(own, chunk_start, chunk_len):
     case = make_case(chunk_start, chunk_len, 0xF00 + chunk_start + chunk_len)
     got = run_fused(case, chunk_start, chunk_len)
@@ -86,6 +87,36 @@ def test_scores_that_outgrow_the_running_reference_late_in_the_context(own):
     assert np.isfinite(out).all()
     assert np.abs(out - ref).max() <= MAX_ABS + 2.0 ** -11 * max(1.0, np.abs(ref).max())
     assert K.prefill_attention_health() == 0
+
+
+def test_long_contexts_cut_across_ctas_give_the_same_bits_every_time():
+    """A (tile, head) pair with more than 16 key blocks is cut into runs on different CTAs whose records are
+    combined by whichever arrives last, always in run order: two launches must agree bit for bit."""
+    chunk_start, chunk_len = 6000, 300
+    case = make_case(chunk_start, chunk_len, 0xFB3)
+    try:
+        K.set_prefill_attention_split_blocks(8)          # 50 key blocks per tile: seven runs each
+        a = run_fused(case, chunk_start, chunk_len)
+        b = run_fused(case, chunk_start, chunk_len)
+        assert np.array_equal(a, b)
+        K.set_prefill_attention_split_blocks(1000)       # whole pairs: another summation order, same function
+        c = run_fused(case, chunk_start, chunk_len)
+    finally:
+        K.set_prefill_attention_split_blocks(0)
+    assert np.abs(oracle.half_bits_to_f64(a[:chunk_len, :1536]) - oracle.half_bits_to_f64(c[:chunk_len, :1536])).max() <= MAX_ABS
+
+
+@pytest.mark.parametrize("split", [3, 1000])
+def test_forced_run_lengths_against_the_cpu_checker(own, split):
+    chunk_start, chunk_len = 2500, 140
+    case = make_case(chunk_start, chunk_len, 0xFC1 + split)
+    try:
+        K.set_prefill_attention_split_blocks(split)
+        got = run_fused(case, chunk_start, chunk_len)
+    finally:
+        K.set_prefill_attention_split_blocks(0)
+    ref = reference(own, case, chunk_start, chunk_len)
+    assert np.abs(oracle.half_bits_to_f64(got[:chunk_len, :1536]) - ref).max() <= MAX_ABS + 2.0 ** -11
 
 
 def test_output_stride_gap_is_untouched_and_inputs_are_read_only(own):
