@@ -11,10 +11,14 @@
 //
 // Mapping. A decode batch is 64 rows x 151 936 logits = 19.4 MB: one CTA per row
 // (the reference's shape) would use 64 of 148 SMs. Here every row is scanned by
-// a thread-block CLUSTER of 8 CTAs, each taking a contiguous eighth of the row
-// with 16-byte loads; warp champions meet in shared memory, the 8 CTA champions
-// meet in the leader's shared memory through distributed shared memory, and the
-// leader writes the token - one launch, no scratch in global memory, no atomics.
+// a thread-block CLUSTER of 8 CTAs, each taking a contiguous eighth of the row.
+// A thread requests its whole share at once - ten 16-byte loads, all in flight
+// before the first compare - and keeps it in registers. The maximum is found on
+// packed halves (four max instructions per eight logits, no index arithmetic);
+// only then is the lowest position of that value looked up, by equality, in the
+// registers the data already sits in. CTA champions meet in the leader's shared
+// memory through distributed shared memory and the leader writes the token - one
+// launch, no scratch in global memory, no atomics.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -26,6 +30,7 @@ namespace {
 
 constexpr int kClusterCtas = 8;
 constexpr int kThreads = 256;
+constexpr int kRegChunks = 10;  // 16-byte chunks a thread keeps in registers: 8 x 256 x 10 x 8 = 163 840 logits per row
 
 struct Champion {
   float v;
@@ -68,25 +73,76 @@ ArgmaxClusterKernel(int32_t* __restrict__ out_tokens, const half* __restrict__ l
   if (kVec) {
     const int chunks = vocab >> 3;
     const int per = (chunks + kClusterCtas - 1) / kClusterCtas;
-    const int end = min(chunks, (rank + 1) * per);
-    // four independent 16-byte loads in flight per thread before any compare
-    for (int c0 = rank * per + threadIdx.x; c0 < end; c0 += 4 * kThreads) {
-      uint4 w[4];
+    const int begin = rank * per, end = min(chunks, (rank + 1) * per);
+    __shared__ float warp_max[kThreads / 32];
+    __shared__ float cta_max;
+    // The largest value, on packed halves. __hmax2 returns the other operand when one is NaN, so NaN never
+    // displaces the incumbent; the incumbent starts at -inf.
+    const half2 ninf = __float2half2_rn(-INFINITY);
+    half2 mx = ninf;
+    if (per <= kRegChunks * kThreads) {
+      // the whole share of this thread in registers, every load in flight before the first use
+      uint4 w[kRegChunks];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k * kThreads;
-        if (c < end) w[k] = LdgStream16(x + c * 8);
+      for (int k = 0; k < kRegChunks; ++k) {
+        const int c = begin + threadIdx.x + k * kThreads;
+        w[k] = c < end ? LdgStream16(x + c * 8) : make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);  // -inf
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k * kThreads;
-        if (c < end) {
-          const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+      for (int k = 0; k < kRegChunks; ++k)
+        mx = __hmax2(__hmax2(mx, __hmax2(AsHalf2(w[k].x), AsHalf2(w[k].y))), __hmax2(AsHalf2(w[k].z), AsHalf2(w[k].w)));
+      float m = fmaxf(__low2float(mx), __high2float(mx));
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(AsHalf2(words[j]));
-            Offer(best, f.x, c * 8 + 2 * j);
-            Offer(best, f.y, c * 8 + 2 * j + 1);
+      for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+      if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float b = warp_max[0];
+#pragma unroll
+        for (int i = 1; i < kThreads / 32; ++i) b = fmaxf(b, warp_max[i]);
+        cta_max = b;
+      }
+      __syncthreads();
+      // The lowest position holding that value (+0 and -0 compare equal, NaN equals nothing): this thread's
+      // chunks ascend in k, a chunk's halves in position.
+      const float target = cta_max;
+      const half2 t2 = __float2half2_rn(target);
+      best.v = target;
+#pragma unroll
+      for (int k = kRegChunks - 1; k >= 0; --k) {
+        const int c = begin + threadIdx.x + k * kThreads;
+        const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+        if (c < end && (__heq2_mask(AsHalf2(words[0]), t2) | __heq2_mask(AsHalf2(words[1]), t2) |
+                        __heq2_mask(AsHalf2(words[2]), t2) | __heq2_mask(AsHalf2(words[3]), t2))) {
+#pragma unroll
+          for (int j = 3; j >= 0; --j) {
+            const uint32_t hit = __heq2_mask(AsHalf2(words[j]), t2);
+            if (hit & 0xFFFF0000u) best.i = c * 8 + 2 * j + 1;
+            if (hit & 0x0000FFFFu) best.i = c * 8 + 2 * j;
+          }
+        }
+      }
+      if (best.i >= vocab) best.v = -INFINITY;   // this thread does not hold the CTA's maximum
+    } else {
+      // rows too long for the register file: the streaming form
+      for (int c0 = begin + threadIdx.x; c0 < end; c0 += 4 * kThreads) {
+        uint4 w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = c0 + k * kThreads;
+          if (c < end) w[k] = LdgStream16(x + c * 8);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = c0 + k * kThreads;
+          if (c < end) {
+            const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(AsHalf2(words[j]));
+              Offer(best, f.x, c * 8 + 2 * j);
+              Offer(best, f.y, c * 8 + 2 * j + 1);
+            }
           }
         }
       }
