@@ -4,7 +4,7 @@
 // The reference ingests a chunk through a composite (src/core/model_executor.cpp:1219-1290): LaunchKvGather
 // copies the sequence's pages into dense K / V staging, cuBLASLt writes FP32 scores [heads, chunk, ctx] to
 // global memory, LaunchPrefillSoftmax rewrites them as FP16 probabilities, cuBLASLt multiplies by V; its
-// design notes name a fused kernel as the follow-up (docs/DESIGN.md:872-876). This is that kernel: the
+// design notes name a fused kernel as the follow-up (docs/DESIGN.md:872-876 in its tree). This is that kernel: the
 // same function - scores q.k * scale in FP32 from FP16 operands, causal SELECT masking (key position <=
 // query position; slots past the context never reach a result), softmax with FP32 statistics,
 // probabilities rounded to FP16 for the P.V product, FP32 accumulation, one FP16 rounding of acc / l -
