@@ -17,10 +17,12 @@
 //  * Warp 9 requests every tile by TMA (copies spread over its lanes), warp 8 issues every tcgen05.mma: table
 //    reads and copy requests never sit between two products. Q tile and K/V
 //    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
-//    [16 tokens][128 dims]. A K tile arrives as two 2 KiB copies, one per 64-dim half, landing at row 16 * page of a
-//    [128 rows][128 B] region, so eight pages form exactly the K-major operand tile of an N = 128 product; a V tile
-//    arrives as one 4 KiB copy ([dim half][16 tokens][128 B] at 4 KiB * page), which is what the MN-major operand
-//    of P.V reads one page per K = 16 slice. (The TMA unit is paid per copy, the tensor pipe per instruction.)
+//    [16 tokens][128 dims] = 4 KiB and arrives - K and V alike - as ONE copy through a 5-D view of the pool
+//    that lands it as [token group of 8][dim half][8 tokens][128 B] at 4 KiB * page: swizzle atoms of 8 rows x 128 B,
+//    the two dim halves 1 KiB apart, the 8-token groups 2 KiB apart. Eight pages are then the K-major operand
+//    tile of an N = 128 product for Q.K^T (per dim half: sixteen 8-key groups at a stride of 2 KiB), and each page
+//    is one K = 16 slice of the MN-major operand of P.V. (The TMA unit is paid per copy - 16 per block this way,
+//    24 or 32 with K in halves - and the tensor pipe per instruction.)
 //    Block-table indirection costs nothing but the copy's coordinate. K and V blocks are double-buffered;
 //    the six query heads of a KV group and all query tiles re-read the same pages from L2.
 //  * S = Q.K^T: M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major in shared memory,
@@ -37,7 +39,7 @@
 //    the running output - a read-modify-write of the row in tensor memory - almost never happens after the
 //    first block; numerator and denominator always share one reference, so the result does not depend on it.
 //  * O += P.V: A = P (in tensor memory) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
-//    8 keys x 64 dims, 1024 B between key groups, 2 KiB between the dim halves, one page per K = 16 slice -
+//    8 keys x 64 dims, 2 KiB between key groups, 1 KiB between the dim halves, one page per K = 16 slice -
 //    accumulated over all blocks in tensor-memory columns 256-383; read once at the end, divided by the row
 //    sum, rounded once.
 // Every mbarrier wait is bounded and reports through rl_prefill_attention_health.
@@ -90,33 +92,33 @@ struct Params {
   int* tickets;       // one counter per (head, query tile), zero between launches
 };
 
-// K/V block operand as a B matrix stored [key][dim] (MN-major, 128-byte swizzle): atoms of 8 key rows x 128 B;
-// `lbo` bytes between the two 64-dim halves (leading dimension = N), 1024 B between 8-key groups (stride dimension = K).
-__device__ __forceinline__ uint64_t TileDescMn(uint32_t smem_addr, uint32_t lbo_bytes) {
-  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
-         (64ull << 32) | (1ull << 46) | (2ull << 61);
+// Where a page lands in a K or V block buffer: [token group of 8][dim half][8 tokens][128 B].
+constexpr int kHalfStride = 1024;    // between the two 64-dim halves of an 8-token group
+constexpr int kGroupStride = 2048;   // between the two 8-token groups of a page
+// V page as the B operand of P.V, stored [key][dim] (MN-major, 128-byte swizzle): atoms of 8 key rows x 128 B;
+// leading byte offset = between the 64-dim halves (N runs over dims), stride byte offset = between the 8-key
+// groups (K runs over keys).
+__device__ __forceinline__ uint64_t PageDescMn(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(kHalfStride >> 4) << 16) |
+         (static_cast<uint64_t>(kGroupStride >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// K block as the B operand of Q.K^T (K-major, 128-byte swizzle), one dim half: 8-key groups 2 KiB apart.
+__device__ __forceinline__ uint64_t KeyBlockDesc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) |
+         (static_cast<uint64_t>(kGroupStride >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ uint32_t InstrDescBMn(int n) { return InstrDesc(n) | (1u << 16); }
 
-// One (block, kv, head) page tile in one copy: [dim half][16 tokens][64 halves] = 4 KiB, 128-byte swizzled.
-__device__ __forceinline__ void TmaLoadPageTile(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar,
-                                                uint64_t policy) {
+// One (block, kv, head) page tile in one copy of 4 KiB: the pool seen as [tile][token group][dim half][8 tokens]
+// [64 halves], 128-byte swizzled. Into this CTA's own shared memory; no multicast.
+__device__ __forceinline__ void TmaLoadPage(uint32_t dst, const CUtensorMap* map, int tile, uint32_t bar, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-      "[%0], [%1, {%2, %2, %2, %3}], [%4], %5;" ::"r"(dst),
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %2, %2, %2, %3}], [%4], %5;" ::"r"(dst),
       "l"(map), "r"(0), "r"(tile), "r"(bar), "l"(policy)
       : "memory");
 }
-// One 64-dim half of a page tile: [16 tokens][64 halves] = 2 KiB (second map: same tensor, box of one dim half).
-__device__ __forceinline__ void TmaLoadHalfTile(uint32_t dst, const CUtensorMap* map, int half_idx, int tile,
-                                                uint32_t bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-      "[%0], [%1, {%2, %2, %3, %4}], [%5], %6;" ::"r"(dst),
-      "l"(map), "r"(0), "r"(half_idx), "r"(tile), "r"(bar), "l"(policy)
-      : "memory");
-}
-constexpr int kPageTileBytes = kKvBlock * kHeadDim * 2;   // 4096: [2 dim halves][16 tokens][128 B]
+constexpr int kPageTileBytes = kKvBlock * kHeadDim * 2;   // 4096
 __device__ __forceinline__ void MbarArrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -139,12 +141,14 @@ __device__ __forceinline__ void TmemStore8(uint32_t taddr, const uint32_t (&r)[8
                : "memory");
 }
 // D (+)= A.B with A in tensor memory (row i in lane i, two FP16 per 32-bit column along K) and B in shared memory.
-__device__ __forceinline__ void UmmaTs(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
+// Called by all 32 lanes of a converged warp with identical arguments; one elected lane issues (see UmmaElected).
+__device__ __forceinline__ void UmmaTsElected(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -153,7 +157,7 @@ __device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;
 
 __global__ void __launch_bounds__(kThreads, 1)
 PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap q_map,
-                            const __grid_constant__ CUtensorMap tile_map, const __grid_constant__ CUtensorMap half_map) {
+                            const __grid_constant__ CUtensorMap page_map) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -176,13 +180,16 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Work items of a head, long tiles first (the last query tile of the chunk attends to the most keys): a tile
   // whose keys fill more than `split_blocks` blocks is cut into equal runs of blocks, one CTA each; this CTA is
-  // item blockIdx.x = run `split` of `nsplit` of tile `tile_q`, blocks jb0 .. jb0 + nblk - 1 of that tile.
-  const int head = blockIdx.y;
+  // item blockIdx.y = run `split` of `nsplit` of tile `tile_q`, blocks jb0 .. jb0 + nblk - 1 of that tile. The head
+  // is the fast grid index: CTAs start in the order item 0 of every head, item 1 of every head, ... - longest
+  // items first over the WHOLE launch, which is what lets the short ones level the SMs at the end - and the heads
+  // of a KV group read the same pages at the same time.
+  const int head = blockIdx.x;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int kv_len = p.chunk_start + p.chunk_len;
   int tile_q = 0, split = 0, nsplit = 1, tile_blocks = 1;
   {
-    int item = blockIdx.x;
+    int item = blockIdx.y;
     for (int t = p.n_tiles - 1; t >= 0; --t) {
       const int nb = (min(p.chunk_start + (t + 1) * kBM, kv_len) - 1) / kBN + 1;
       const int ns = (nb + p.split_blocks - 1) / p.split_blocks;
@@ -233,38 +240,30 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 
   if (warp == 9) {
     // ------------------------------------------------------------ loader: every TMA request
-    // A block is 16 copies of 2 KiB for K and 8 of 4 KiB for V (the TMA unit is paid per copy, the tensor pipe per
-    // instruction: K in halves keeps Q.K^T at N = 128). The block id of a page serves K and V alike and is read
-    // from the table two blocks ahead of its use.
+    // A block is 8 copies of 4 KiB for K and 8 for V, one per page, spread over the lanes. The block id of a page
+    // serves K and V alike and is read from the table two blocks ahead of its use.
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&tile_map) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&half_map) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&page_map) : "memory");
     }
     const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
-    // lane l < 16 serves page l / 2: K as two copies of 2 KiB (lanes 2p, 2p + 1: one per dim half), V as one copy
-    // of 4 KiB (lane 2p)
-    auto table_entry = [&](int j) {
-      const int page = (jb0 + j) * kPagesPerBlock + (lane >> 1);
-      return (lane < 2 * kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+    auto table_entry = [&](int j) {   // lane l < 8 serves page l of the block
+      const int page = (jb0 + j) * kPagesPerBlock + lane;
+      return (lane < kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
     };
-    // K block j into buffer j & 1 as the K-major operand tile: region `dim half`, rows 16 * page .. + 15.
-    auto load_k = [&](int j, int block) {
+    auto load_k = [&](int j, int block) {   // K block j into buffer j & 1, page l at 4 KiB * l
       const uint32_t base = s_k + (j & 1) * kTileBytes, bar = bar_k0 + 8 * (j & 1);
       if (lane == 0) MbarExpectTx(bar, kTileBytes);
       __syncwarp();
-      if (lane < 2 * kPagesPerBlock)
-        TmaLoadHalfTile(base + (lane & 1) * kRegionBytes + (lane >> 1) * (kKvBlock * 128), &half_map, lane & 1,
-                        (block * 2 + 0) * p.kv_heads + kv_head, bar, keep);
+      if (lane < kPagesPerBlock)
+        TmaLoadPage(base + lane * kPageTileBytes, &page_map, (block * 2 + 0) * p.kv_heads + kv_head, bar, keep);
     };
-    // V block j into buffer j & 1, page p at 4 KiB * p as [dim half][16 tokens][128 B]: what the MN-major operand of
-    // P.V reads one page per K = 16 slice.
-    auto load_v = [&](int j, int block) {
+    auto load_v = [&](int j, int block) {   // V block j likewise
       const uint32_t base = s_v + (j & 1) * kTileBytes, bar = bar_v0 + 8 * (j & 1);
       if (lane == 0) MbarExpectTx(bar, kTileBytes);
       __syncwarp();
-      if (lane < 2 * kPagesPerBlock && !(lane & 1))
-        TmaLoadPageTile(base + (lane >> 1) * kPageTileBytes, &tile_map, (block * 2 + 1) * p.kv_heads + kv_head, bar, keep);
+      if (lane < kPagesPerBlock)
+        TmaLoadPage(base + lane * kPageTileBytes, &page_map, (block * 2 + 1) * p.kv_heads + kv_head, bar, keep);
     };
     if (lane == 0) {
       MbarExpectTx(bar_q, kTileBytes);
@@ -290,55 +289,62 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       load_v(t, blk);
     }
   } else if (warp == 8) {
-    // ------------------------------------------------------------ MMA issue (lane 0; the warp walks the schedule together)
+    // ------------------------------------------------------------ MMA issue
+    // The whole warp walks the schedule converged and every product is issued by one elected lane: the
+    // descriptors depend on the block's buffer, and computed inside a one-lane branch they cost the issue
+    // ~20 cycles more per product than the tensor pipe needs to execute it.
     const uint32_t idesc_kk = InstrDesc(kBN), idesc_mn = InstrDescBMn(kHeadDim);
+    bool good = true;   // warp-uniform: every lane waits on the same barrier and votes
+    auto wait_all = [&](uint32_t bar, int parity) {
+      if (good) {
+        good = __all_sync(0xffffffffu, MbarWait(bar, parity));
+        if (!good && lane == 0) atomicExch(p.error_flag, 2);
+      }
+    };
     // S[j & 1] = Q.K_j^T
     auto issue_qk = [&](int j) {
       const uint32_t kb = s_k + (j & 1) * kTileBytes;
       const uint32_t d = tmem_base + (j & 1) * kBN;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = TileDesc(kb + h * kRegionBytes);
+        const uint64_t a = TileDesc(s_q + h * kRegionBytes), b = KeyBlockDesc(kb + h * kHalfStride);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) Umma(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) UmmaElected(d, a + 2 * k, b + 2 * k, idesc_kk, (h | k) ? 1u : 0u);
       }
-      UmmaCommit(bar_s0 + 8 * (j & 1));
+      UmmaCommitElected(bar_s0 + 8 * (j & 1));
     };
-    // O += P_j.V_j: K = 16 keys = one page per instruction; V read MN-major where it landed (8-key groups 1 KiB
-    // apart, the two dim halves 2 KiB apart).
+    // O += P_j.V_j: K = 16 keys = one page per instruction; V read MN-major where it landed.
     auto issue_pv = [&](int j) {
       const uint32_t vb = s_v + (j & 1) * kTileBytes;
       const uint32_t pt = tmem_base + kTmemP + (j & 1) * (kBN / 2);
 #pragma unroll
       for (int k = 0; k < kPagesPerBlock; ++k) {   // 16 keys = 8 columns of P = one page of V per instruction
-        const uint64_t b = TileDescMn(vb + k * kPageTileBytes, kPageTileBytes / 2);
-        UmmaTs(tmem_o, pt + 8 * k, b, idesc_mn, (j | k) ? 1u : 0u);
+        UmmaTsElected(tmem_o, pt + 8 * k, PageDescMn(vb + k * kPageTileBytes), idesc_mn, (j | k) ? 1u : 0u);
       }
-      UmmaCommit(bar_o0 + 8 * (j & 1));
+      UmmaCommitElected(bar_o0 + 8 * (j & 1));
     };
-    wait(bar_q, 0);
-    wait(bar_k0, 0);
+    wait_all(bar_q, 0);
+    wait_all(bar_k0, 0);
     TcFenceAfter();
-    if (ok && lane == 0) issue_qk(0);
+    if (good) issue_qk(0);
     if (nblk > 1) {
-      wait(bar_k0 + 8, 0);
-      if (ok && lane == 0) issue_qk(1);
+      wait_all(bar_k0 + 8, 0);
+      if (good) issue_qk(1);
     }
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1, par = (j >> 1) & 1;
-      wait(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
-      wait(bar_v0 + 8 * buf, par);                 // V_j landed
+      wait_all(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
+      wait_all(bar_v0 + 8 * buf, par);                 // V_j landed
       TcFenceAfter();
-      if (ok && lane == 0) issue_pv(j);
+      if (good) issue_pv(j);
       if (j + 2 < nblk) {
-        wait(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
-        if (ok && lane == 0) issue_qk(j + 2);
+        wait_all(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
+        if (good) issue_qk(j + 2);
       }
-      __syncwarp();
     }
     // One-shot barrier for the readers of the finished output.
-    if (ok && lane == 0) UmmaCommit(bar_done);
+    if (good) UmmaCommitElected(bar_done);
     __syncwarp();
   } else {
     // ------------------------------------------------------------ softmax: two threads per query row
@@ -349,8 +355,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     float m_ref = -INFINITY, l = 0.0f;
     // This thread's 64 scores of a block are fetched from tensor memory once, all four loads in flight together,
     // and kept in registers for both passes. The fetch for block j+1 is made at the END of block j, before this
-    // thread reports P_j: the tensor pipe is idle then, whereas a load issued once P_j.V_j and Q.K_{j+2}^T are
-    // running waits behind them.
+    // thread reports P_j: that report then also says that S_{j+1}'s buffer may be overwritten.
     uint32_t raw[4][16];
     auto fetch_scores = [&](int j) {
       wait(bar_s0 + 8 * (j & 1), (j >> 1) & 1);
@@ -441,9 +446,10 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       if (rows_valid < kBN) {
         wait(bar_v0 + 8 * buf, (j >> 1) & 1);
         if (row >= rows_valid) {
-          // key `row` of the block: page row / 16, token row % 16; this thread clears dim half hw of it
+          // key `row` of the block: page row / 16, token group (row / 8) % 2, token row % 8; this thread clears
+          // dim half hw of it (the swizzle only permutes 16-byte pieces inside the 128-byte row)
           uint4* r = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + (row >> 4) * kPageTileBytes +
-                                              hw * (kPageTileBytes / 2) + (row & 15) * 128);
+                                              ((row >> 3) & 1) * kGroupStride + hw * kHalfStride + (row & 7) * 128);
 #pragma unroll
           for (int i = 0; i < 8; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -486,7 +492,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       // One run of a tile's key blocks: publish (o unnormalised, m, l) and take a ticket; whichever CTA of the
       // tile comes last combines ALL runs' records, its own included, in run order - so the result does not
       // depend on who that is.
-      float* rec0 = p.partials + (static_cast<size_t>(head) * gridDim.x + (blockIdx.x - split)) * kPartialFloats;
+      float* rec0 = p.partials + (static_cast<size_t>(head) * gridDim.y + (blockIdx.y - split)) * kPartialFloats;
       float* rec = rec0 + static_cast<size_t>(split) * kPartialFloats;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -655,7 +661,7 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   DeviceState* st;
   int rc = EnsureReady(&st);
   if (rc != RL_OK) return rc;
-  CUtensorMap q_map, tile_map;
+  CUtensorMap q_map, page_map;
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(chunk_len)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(q_row_stride) * 2};
@@ -667,27 +673,19 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: q tensor map (CUresult %d)", static_cast<int>(r));
   }
   {
-    // the pool slice as [tile][dim-half][token][64 halves]; one box = one whole page tile, both dim halves
-    const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kKvBlock) * kHeadDim * 2};
-    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 2, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = g_encode(&tile_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(kv_pool_layer), dims, strides,
+    // The pool slice as [tile][token group of 8][dim half][token in group][64 halves] (strides 4096, 2048, 128, 256,
+    // 2 bytes): a box of one whole tile lands as [token group][dim half][8 tokens][128 B]. The tile count is not
+    // part of the launch contract, so the view claims more tiles than a 180 GB device can hold; only tiles of
+    // real pages are ever requested.
+    const cuuint64_t dims[5] = {64, 8, 2, 2, 1ull << 26};
+    const cuuint64_t strides[4] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, 8ull * kHeadDim * 2,
+                                   static_cast<cuuint64_t>(kKvBlock) * kHeadDim * 2};
+    const cuuint32_t box[5] = {64, 8, 2, 2, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    const CUresult r = g_encode(&page_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(kv_pool_layer), dims, strides,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool tensor map (CUresult %d)", static_cast<int>(r));
-  }
-  CUtensorMap half_map;
-  {
-    // the same view with a box of one dim half: [16 tokens][64 halves] = 2 KiB
-    const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(kKvBlock), 2, 1ull << 26};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(kHeadDim) * 2, 128, static_cast<cuuint64_t>(kKvBlock) * kHeadDim * 2};
-    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kKvBlock), 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = g_encode(&half_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(kv_pool_layer), dims, strides,
-                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool half-tile map (CUresult %d)", static_cast<int>(r));
   }
   // Work items per head: a tile with more than split_blocks key blocks is cut into ceil(blocks / split_blocks) runs.
   const int n_tiles_all = (chunk_len + kBM - 1) / kBM;
@@ -707,7 +705,7 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
     items += ns;
     any_split |= ns > 1;
   }
-  if (items > 65535 * 32) return Fail(RL_E_TOO_LARGE, "paged_prefill_attention: chunk too large (%lld work items per head)", static_cast<long long>(items));
+  if (items > 65535) return Fail(RL_E_TOO_LARGE, "paged_prefill_attention: chunk too large (%lld work items per head)", static_cast<long long>(items));
   if (any_split) {
     const size_t need = static_cast<size_t>(num_q_heads) * static_cast<size_t>(items) * kPartialFloats;
     const size_t need_tickets = static_cast<size_t>(num_q_heads) * n_tiles;
@@ -747,8 +745,8 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   p.kv_heads = num_kv_heads;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.error_flag = st->error_flag;
-  const dim3 grid(static_cast<unsigned>(items), num_q_heads);
-  PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, tile_map, half_map);
+  const dim3 grid(num_q_heads, static_cast<unsigned>(items));
+  PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, page_map);
   return LaunchStatus("paged_prefill_attention");
 }
 

@@ -97,6 +97,27 @@ __device__ __forceinline__ void UmmaCommit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
+// The same two, called by ALL 32 lanes of a converged warp with identical arguments: one elected lane
+// issues. Descriptors that change from one loop trip to the next then stay in the warp-uniform
+// datapath; issued from inside a `lane == 0` branch they are moved there one product at a time, which
+// was measured to cost 82 cycles per M = 128, N = 128 product against the tensor pipe's 64.
+__device__ __forceinline__ void UmmaElected(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaCommitElected(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
+      : "memory");
+}
 // 16 consecutive accumulator columns of this thread's tensor-memory lane. The load is asynchronous:
 // the values may be used only after TmemWaitLoads, which takes the registers as read-write operands
 // so that no use can be scheduled ahead of it.
