@@ -45,7 +45,10 @@
 // Every mbarrier wait is bounded and reports through rl_prefill_attention_health.
 #include <cuda.h>
 
+#include <algorithm>
+#include <functional>
 #include <mutex>
+#include <vector>
 
 #include "tc_ptx.cuh"
 
@@ -583,26 +586,69 @@ EncodeTiledFn g_encode = nullptr;
 std::mutex g_mutex;
 int g_split_blocks = 0;   // 0: chosen per launch (ChooseSplitBlocks); > 0: forced (rl_prefill_attention_set_split_blocks)
 
-// Longest run of key blocks one CTA should take. A (tile, head) pair is cut into r runs when that fills the machine
-// better: the launch is modelled as ceil(items / SMs) waves of one run each - 1.2 us per block, 6.5 us of set-up and
-// tear-down per CTA, 13 us when the CTA also publishes and merges a record (figures measured on B200) - and r is
-// the value that minimises it. Long prompts' last chunks (few rows, tens of thousands of keys) gain up to 4.5 x,
-// chunks that already fill the machine more than twice over are left whole.
-int ChooseSplitBlocks(int n_tiles, int heads, int max_blocks_per_tile, int sm_count) {
-  const double base = static_cast<double>(n_tiles) * heads;
-  double best = 0.0;
-  int best_r = 1;
-  for (int r = 1; r <= 32 && r <= max_blocks_per_tile; ++r) {
-    const int run = (max_blocks_per_tile + r - 1) / r;
-    if (r > 1 && run < 8) break;
-    const double waves = static_cast<double>((static_cast<long long>(base * r) + sm_count - 1) / sm_count);
-    const double cost = waves * (run * 1.2 + (r > 1 ? 13.0 : 6.5));
-    if (r == 1 || cost < best) {
-      best = cost;
-      best_r = r;
+// Longest run of key blocks one CTA should take: a (tile, head) pair with more blocks is cut into equal runs.
+// The launch is replayed on the host the way the hardware runs it - CTAs start in grid order, each on the SM that
+// frees first - with costs measured on B200 (1.15 us per key block, 8 us of set-up and tear-down per CTA, 3 us
+// per run for the CTA that combines a pair's records; the model is within a few per cent of measured launch times
+// from 128 rows at context 32768 to 4096 rows at 20480), and the candidate with the shortest makespan wins. Cutting
+// only the LONGEST tiles often does best (2048 rows at context 8192: runs of at most 60 blocks turn 192 items in
+// two waves into 240 that level out, 136 -> 119 us); a prompt's last rows against tens of thousands of keys are
+// cut into a dozen runs each (292 -> 69 us). The choice depends on the chunk alone, so it is remembered across
+// the layers of a model.
+double SimulatedMakespan(int chunk_start, int chunk_len, int heads, int split_blocks, int sm_count, std::vector<double>& free_at) {
+  constexpr double kBlockUs = 1.15, kSetupUs = 8.0, kCombineUsPerRun = 3.0;
+  const int64_t kv_len = static_cast<int64_t>(chunk_start) + chunk_len;
+  const int n_tiles = (chunk_len + kBM - 1) / kBM;
+  free_at.assign(sm_count, 0.0);                       // a min-heap of the times at which the SMs free up
+  double end = 0.0;
+  for (int t = n_tiles - 1; t >= 0; --t) {
+    const int64_t last = std::min<int64_t>(static_cast<int64_t>(chunk_start) + static_cast<int64_t>(t + 1) * kBM, kv_len) - 1;
+    const int nb = static_cast<int>(last / kBN) + 1;
+    const int ns = (nb + split_blocks - 1) / split_blocks;
+    for (int run = 0; run < ns; ++run) {
+      const int blocks = (run + 1) * nb / ns - run * nb / ns;
+      // the run of a pair that starts last is taken to be the one that combines the records
+      const double cost = kSetupUs + blocks * kBlockUs + (ns > 1 && run == ns - 1 ? kCombineUsPerRun * ns : 0.0);
+      for (int h = 0; h < heads; ++h) {
+        std::pop_heap(free_at.begin(), free_at.end(), std::greater<double>());
+        const double done = free_at.back() + cost;
+        free_at.back() = done;
+        std::push_heap(free_at.begin(), free_at.end(), std::greater<double>());
+        end = std::max(end, done);
+      }
     }
   }
-  return (max_blocks_per_tile + best_r - 1) / best_r;
+  return end;
+}
+
+int ChooseSplitBlocks(int chunk_start, int chunk_len, int heads, int sm_count) {
+  struct Memo { int start, len, heads, sms, choice; };
+  static Memo memo = {-1, -1, -1, -1, 0};
+  static std::mutex memo_mutex;
+  std::lock_guard<std::mutex> lock(memo_mutex);
+  if (memo.start == chunk_start && memo.len == chunk_len && memo.heads == heads && memo.sms == sm_count) return memo.choice;
+  const int max_blocks = static_cast<int>((static_cast<int64_t>(chunk_start) + chunk_len - 1) / kBN) + 1;
+  const int n_tiles = (chunk_len + kBM - 1) / kBM;
+  std::vector<double> heap;
+  int best = max_blocks;
+  double best_us = SimulatedMakespan(chunk_start, chunk_len, heads, max_blocks, sm_count, heap);   // every pair whole
+  // A chunk that fills the machine many times over gains nothing from cuts, and replaying it would cost more than it saves.
+  if (static_cast<int64_t>(n_tiles) * heads <= 6LL * sm_count) {
+    const int64_t pairs = static_cast<int64_t>(n_tiles) * heads;
+    auto consider = [&](int run) {
+      if (run < 4 || run >= max_blocks) return;
+      if (pairs * ((max_blocks + run - 1) / run) > 8LL * sm_count) return;   // bounds the replay at ~1200 items
+      const double us = SimulatedMakespan(chunk_start, chunk_len, heads, run, sm_count, heap);
+      if (us < best_us) {
+        best_us = us;
+        best = run;
+      }
+    };
+    for (int r : {2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32}) consider((max_blocks + r - 1) / r);   // equal cuts of the longest tile
+    for (int run = max_blocks - 4; run > max_blocks / 2; run -= 4) consider(run);                   // cuts that only the longer tiles get
+  }
+  memo = {chunk_start, chunk_len, heads, sm_count, best};
+  return best;
 }
 
 int EnsureReady(DeviceState** out_state) {
@@ -688,10 +734,8 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
     if (r != CUDA_SUCCESS) return Fail(RL_E_BAD_SHAPE, "paged_prefill_attention: pool tensor map (CUresult %d)", static_cast<int>(r));
   }
   // Work items per head: a tile with more than split_blocks key blocks is cut into ceil(blocks / split_blocks) runs.
-  const int n_tiles_all = (chunk_len + kBM - 1) / kBM;
-  const int max_tile_blocks = static_cast<int>((static_cast<int64_t>(chunk_start) + chunk_len - 1) / kBN) + 1;
   const int split_blocks = g_split_blocks > 0 ? g_split_blocks
-                                              : ChooseSplitBlocks(n_tiles_all, num_q_heads, max_tile_blocks, CurrentDeviceFacts().sm_count);
+                                              : ChooseSplitBlocks(chunk_start, chunk_len, num_q_heads, CurrentDeviceFacts().sm_count);
   const int n_tiles = (chunk_len + kBM - 1) / kBM;
   const int64_t kv_len = static_cast<int64_t>(chunk_start) + chunk_len;
   int64_t items = 0;
