@@ -130,6 +130,12 @@ __device__ __forceinline__ float Ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// max(a, b, c) in one instruction (sm_100): halves the comparisons of the maximum pass.
+__device__ __forceinline__ float Max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // 16 accumulator columns of this thread's lane back into tensor memory.
 __device__ __forceinline__ void TmemStore16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -385,11 +391,12 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
           for (int i = 0; i < 16; ++i)
             mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
       } else {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, two scores per instruction
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(raw[c][i]));
+          for (int i = 0; i < 16; i += 2)
+            m4[(i >> 1) & 3] = Max3(m4[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       float* xm = xmax + buf * 256;
