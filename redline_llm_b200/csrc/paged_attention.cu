@@ -88,8 +88,10 @@ constexpr int kRingOff = 0;
 constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 196608
 constexpr int kOBufOff = kRingOff + kRingBytes;
 constexpr int kOBufBytes = kWarps * kGroup * kORowPad * 4;  // 25344
-constexpr int kMlOff = kOBufOff + kOBufBytes;               // m[8][8], l[8][8]
-constexpr int kMlBytes = 2 * kWarps * 8 * 4;
+constexpr int kMlStride = (kWarps + 3) & ~3;                // m[head][warp], l[head][warp]: a head's values of all
+constexpr int kMlOff = kOBufOff + kOBufBytes;               // warps are consecutive (read 16 bytes at a time)
+constexpr int kMlBytes = 2 * 8 * kMlStride * 4;
+static_assert(kOBufBytes % 16 == 0, "m / l rows must stay 16-byte aligned");
 constexpr int kBarOff = kMlOff + kMlBytes;
 constexpr int kBarBytes = kWarps * kStages * 8;
 constexpr int kPrefixOff = kBarOff + kBarBytes;
@@ -270,12 +272,11 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
   const uint32_t ring = SmemAddr(smem + kRingOff);
   float* obuf = reinterpret_cast<float*>(smem + kOBufOff);
   float* mbuf = reinterpret_cast<float*>(smem + kMlOff);
-  float* lbuf = mbuf + kWarps * 8;
+  float* lbuf = mbuf + 8 * kMlStride;
   const uint32_t bars = SmemAddr(smem + kBarOff);
   int* prefix = reinterpret_cast<int*>(smem + kPrefixOff);
 
   __shared__ bool merge_here, others_done;
-  __shared__ float fold_scale[kWarps * 8], fold_max[8], fold_den[8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tig = lane & 3;
   const int heads = p.kv_heads;
@@ -437,7 +438,6 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
     const int seq_len = min(p.seq_lens[sc.seq], p.max_blocks * kKvBlock);
     const int seg_end_rel = static_cast<int>(seg_end - share_begin);
     const int item_begin_rel = static_cast<int>(item_begin - share_begin);  // may be negative
-
     // Q fragments of this item: B operand of S^T = K.Q^T, query g (< 6) in column g.
     uint32_t qb[8][2];
     {
@@ -449,6 +449,26 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
         qb[kk][1] = g < kGroup ? __ldg(reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8)) : 0u;
       }
     }
+    // Who else works on this item (uniform over the CTA; worked out here, under the loads of Q, not after the
+    // last page, where nothing would hide the two 64-bit divisions).
+    const bool whole = seg_begin == item_begin && seg_end == item_end;
+    const int ctas = gridDim.x;
+    int c_first = blockIdx.x, c_last = blockIdx.x, contributors = 1;
+    bool sparse = false;
+    if (!whole) {
+      c_first = item_begin < share_begin ? ShareOf(item_begin, total, ctas) : blockIdx.x;
+      c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
+      sparse = total < ctas;  // then every non-empty share is exactly one page
+      contributors = sparse ? sc.pages : c_last - c_first + 1;
+    }
+    // Have all the other contributors of this item published already? (Usual for the tail of a share: the next
+    // CTA met the same item at the very start of its own share.) Then this CTA is the last one, reads their
+    // records - under the fold below - and neither publishes its own nor takes a ticket. Thread 0 looks while
+    // its warp still has two pages of the segment to go, so the answer is there when the last page is done; a
+    // contributor that publishes after the look is simply met through the tickets.
+    const bool may_read_inline = !whole && !sparse && contributors <= kInlineContributors;
+    int seen = -1;
+
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -464,6 +484,8 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
         if (lane == 0) atomicExch(p.meta, 1);
       }
       if (n_use == 0) { RL_STAMP(2); }
+      if (may_read_inline && tid == 0 && seen < 0 && rel + 2 * kWarps >= seg_end_rel)
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.meta + kTicketOff + c_first) : "memory");
       if (!failed) {
         const int valid = seq_len - (rel - item_begin_rel) * kKvBlock;  // >= 1; >= 16 for a full page
 
@@ -541,24 +563,10 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
 
     RL_STAMP(3);
     // ---- the segment is done: fold the warps' (o, m, l); then write the item, or hand it on ----
-    const bool whole = seg_begin == item_begin && seg_end == item_end;
-    const int ctas = gridDim.x;
-    int c_first = blockIdx.x, c_last = blockIdx.x, contributors = 1;
-    bool sparse = false;
-    if (!whole) {  // uniform over the CTA
-      c_first = item_begin < share_begin ? ShareOf(item_begin, total, ctas) : blockIdx.x;
-      c_last = item_end > share_end ? ShareOf(item_end - 1, total, ctas) : blockIdx.x;
-      sparse = total < ctas;  // then every non-empty share is exactly one page
-      contributors = sparse ? sc.pages : c_last - c_first + 1;
-      if (tid == 0) {
-        // Have all the other contributors of this item published already? (Usual for the tail of a
-        // share: the next CTA met the same item at the very start of its own share.) Then this CTA is
-        // the last one, reads their records now - under the fold below - and neither publishes its own
-        // nor takes a ticket.
-        int seen;
+    if (tid == 0) {
+      if (may_read_inline && seen < 0)   // warp 0 had fewer than two pages in this segment
         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.meta + kTicketOff + c_first) : "memory");
-        others_done = !sparse && contributors <= kInlineContributors && seen == contributors - 1;
-      }
+      others_done = may_read_inline && seen == contributors - 1;
     }
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -575,10 +583,10 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
         ob[(2 * tig + 1) * kORowPad + 16 * mt + g + 8] = o[mt][3];
       }
       if (g == 0) {
-        mbuf[warp * 8 + 2 * tig] = m0;
-        mbuf[warp * 8 + 2 * tig + 1] = m1;
-        lbuf[warp * 8 + 2 * tig] = l0;
-        lbuf[warp * 8 + 2 * tig + 1] = l1;
+        mbuf[(2 * tig) * kMlStride + warp] = m0;
+        mbuf[(2 * tig + 1) * kMlStride + warp] = m1;
+        lbuf[(2 * tig) * kMlStride + warp] = l0;
+        lbuf[(2 * tig + 1) * kMlStride + warp] = l1;
       }
     }
     __syncthreads();
@@ -589,7 +597,21 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       // Records of the OTHER contributors (at most two when read inline), in CTA order.
       float om[kInlineContributors - 1][kHeadsPerGroup], ol[kInlineContributors - 1][kHeadsPerGroup],
           oo[kInlineContributors - 1][kHeadsPerGroup];
+      // (An item over exactly two CTAs - the usual case - takes straight-line code: at the end of a share the
+      // fetch of every instruction is on the critical path. Never reached by `sparse` launches.)
       auto load_others = [&]() {
+        if (contributors == 2) {
+          const int c = c_first == static_cast<int>(blockIdx.x) ? c_last : c_first;
+          const float* r = p.partials + (static_cast<size_t>(c) * 2 + (c == c_first ? 1 : 0)) * kPartialFloats;
+#pragma unroll
+          for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+            const int qh = q0 + kMergeGroups * qi;
+            om[0][qi] = __ldcg(r + kGroup * kHeadDim + qh);
+            ol[0][qi] = __ldcg(r + kGroup * kHeadDim + 8 + qh);
+            oo[0][qi] = __ldcg(r + qh * kHeadDim + d);
+          }
+          return;
+        }
         int k = 0;
         for (int c = c_first; c <= c_last; ++c) {
           if (c == static_cast<int>(blockIdx.x)) continue;
@@ -612,38 +634,56 @@ PagedAttentionSplitKernel(const Params p, const __grid_constant__ CUtensorMap ti
       const bool fast = !whole && others_done;
       if (fast) load_others();
 
-      // Scale factors exp2(m_w - max) per (warp, head): six threads, once, instead of every thread.
-      if (tid < kGroup) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mbuf[w * 8 + tid]);
-        float den = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          const float f = Exp2(mbuf[w * 8 + tid] - mx);  // 0 for a warp that saw no page
-          fold_scale[w * 8 + tid] = f;
-          den = fmaf(f, lbuf[w * 8 + tid], den);
-        }
-        fold_max[tid] = mx;
-        fold_den[tid] = den;
-      }
-      __syncthreads();
+      // The warps' (o, m, l) folded in warp order, every thread for its own heads and column: the eight maxima
+      // and sums of a head are broadcast reads, the eight scale factors exp2(m_w - max) are recomputed by each
+      // thread. (Six threads computing them once for all, behind a CTA barrier of its own, was measured at
+      // ~1000 cycles at the end of every share - after the last page nothing hides latency.)
       float acc[kHeadsPerGroup], mxo[kHeadsPerGroup], deno[kHeadsPerGroup];
 #pragma unroll
       for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
         const int qh = q0 + kMergeGroups * qi;
-        float a = 0.0f;
+        float mw[kMlStride], lw[kMlStride];
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) a = fmaf(fold_scale[w * 8 + qh], obuf[(w * kGroup + qh) * kORowPad + d], a);
+        for (int i = 0; i < kMlStride / 4; ++i) {
+          const float4 m4 = reinterpret_cast<const float4*>(mbuf + qh * kMlStride)[i];
+          const float4 l4 = reinterpret_cast<const float4*>(lbuf + qh * kMlStride)[i];
+          mw[4 * i] = m4.x, mw[4 * i + 1] = m4.y, mw[4 * i + 2] = m4.z, mw[4 * i + 3] = m4.w;
+          lw[4 * i] = l4.x, lw[4 * i + 1] = l4.y, lw[4 * i + 2] = l4.z, lw[4 * i + 3] = l4.w;
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, mw[w]);
+        float a = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float f = Exp2(mw[w] - mx);  // 0 for a warp that saw no page
+          a = fmaf(f, obuf[(w * kGroup + qh) * kORowPad + d], a);
+          den = fmaf(f, lw[w], den);
+        }
         acc[qi] = a;
-        mxo[qi] = fold_max[qh];
-        deno[qi] = fold_den[qh];
+        mxo[qi] = mx;
+        deno[qi] = den;
       }
       half* out_row = p.out + static_cast<int64_t>(sc.seq) * p.out_stride +
                       static_cast<int64_t>(sc.head) * kGroup * kHeadDim + d;
       // The item from this CTA's fold and the other contributors' records, always combined in CTA
       // order with the same arithmetic, whichever CTA happens to do it.
       auto combine_inline = [&]() {
+        if (contributors == 2) {  // the same arithmetic in the same (CTA) order, without the loops
+          const bool me_first = c_first == static_cast<int>(blockIdx.x);
+#pragma unroll
+          for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
+            const float mx = fmaxf(mxo[qi], om[0][qi]);
+            const float f_me = Exp2(mxo[qi] - mx), f_other = Exp2(om[0][qi] - mx);
+            const float f1 = me_first ? f_me : f_other, f2 = me_first ? f_other : f_me;
+            const float x1 = me_first ? acc[qi] : oo[0][qi], x2 = me_first ? oo[0][qi] : acc[qi];
+            const float l1 = me_first ? deno[qi] : ol[0][qi], l2 = me_first ? ol[0][qi] : deno[qi];
+            const float a = fmaf(f2, x2, fmaf(f1, x1, 0.0f));
+            const float dn = fmaf(f2, l2, fmaf(f1, l1, 0.0f));
+            out_row[(q0 + kMergeGroups * qi) * kHeadDim] = __float2half_rn(a / dn);
+          }
+          return;
+        }
 #pragma unroll
         for (int qi = 0; qi < kHeadsPerGroup; ++qi) {
           float mx = mxo[qi];
