@@ -30,14 +30,29 @@ f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
 
 
+def _reference_dir() -> str:
+    """Where the reference tree is mounted: $REDLINE_REFERENCE_DIR, else the `reference_path` recorded in the
+    repository's BASELINE.json; '' when neither names an existing directory."""
+    ref = os.environ.get("REDLINE_REFERENCE_DIR", "")
+    if not ref:
+        try:
+            import json
+            with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as f:
+                ref = str(json.load(f).get("reference_path", ""))
+        except (OSError, ValueError):
+            ref = ""
+    return ref if ref and os.path.isdir(ref) else ""
+
+
 def _make(*targets: str) -> None:
     env = dict(os.environ)
+    env["REDLINE_REFERENCE_DIR"] = _reference_dir()
     subprocess.run(["make", "-C", _HERE, "-j8", *targets], check=True, capture_output=True, env=env)
 
 
 def build(force: bool = False, gpu_ref: bool = False) -> None:
-    """Compile the CPU checker and, where the reference tree is mounted (the Makefile's REF, or the
-    environment variable REDLINE_REFERENCE_DIR), the reference's own CPU code into _ref/. With
+    """Compile the CPU checker and, where the reference tree is mounted (the environment variable REDLINE_REFERENCE_DIR, else
+    the `reference_path` of BASELINE.json), the reference's own CPU code into _ref/. With
     `gpu_ref` also the GPU-side comparators of the Makefile's `gpuref` target (the reference's CUDA
     kernels behind a C ABI, and the reference's C++ host over either kernel library); those link
     against this repository's built CUDA library, so it must exist. Where the tree is absent the
