@@ -193,6 +193,15 @@ int rl_prefill_attention_health(int* flag_out);
 int rl_prefill_attention_set_split_blocks(int blocks);
 
 /*
+ * The run length rl_launch_paged_prefill_attention would use for a chunk on a device of `sm_count` SMs: a
+ * (query tile, head) pair with more 128-key blocks than this is cut into equal runs on separate CTAs. Host
+ * arithmetic only (a replay of the launch: work items in grid order, each onto the SM that frees first); needs
+ * no device. No counterpart in the reference.
+ */
+int rl_prefill_attention_run_length(int32_t chunk_start, int32_t chunk_len, int32_t num_q_heads, int32_t sm_count,
+                                    int32_t* run_blocks_out);
+
+/*
  * Decode input plumbing on the device: after a step's greedy argmax, prepare the next step's inputs in
  * place - input_ids[i] <- control[1 + i] if that is >= 0 (a scripted token), else sampled_tokens[i];
  * positions[i] <- seq_lens[i]; seq_lens[i] += 1 - for every row with seq_len > 0, when control[0] != 0

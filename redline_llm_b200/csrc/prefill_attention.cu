@@ -815,6 +815,17 @@ extern "C" int rl_prefill_attention_health(int* flag_out) {
   return RL_OK;
 }
 
+extern "C" int rl_prefill_attention_run_length(int32_t chunk_start, int32_t chunk_len, int32_t num_q_heads,
+                                               int32_t sm_count, int32_t* run_blocks_out) {
+  using namespace rl;
+  if (!run_blocks_out) return Fail(RL_E_NULL_POINTER, "rl_prefill_attention_run_length: null pointer");
+  if (chunk_start < 0 || chunk_len < 1 || num_q_heads < 1 || sm_count < 1)
+    return Fail(RL_E_BAD_SHAPE, "rl_prefill_attention_run_length: chunk_start >= 0, chunk_len, heads and SMs >= 1");
+  *run_blocks_out = rl::pfa::g_split_blocks > 0 ? rl::pfa::g_split_blocks
+                                                : rl::pfa::ChooseSplitBlocks(chunk_start, chunk_len, num_q_heads, sm_count);
+  return RL_OK;
+}
+
 extern "C" int rl_prefill_attention_set_split_blocks(int blocks) {
   if (blocks < 0) return rl::Fail(RL_E_BAD_SHAPE, "rl_prefill_attention_set_split_blocks: 0 (automatic) or a positive block count");
   rl::pfa::g_split_blocks = blocks;

@@ -27,6 +27,7 @@ ABI_SYMBOLS = (
     "rl_launch_decode_linear", "rl_decode_linear_health", "rl_decode_linear_set_stages",
     "rl_decode_linear_set_max_splits", "rl_launch_qkv_rope_kv_scatter", "rl_launch_decode_advance",
     "rl_launch_paged_prefill_attention", "rl_prefill_attention_health", "rl_attention_test_wait_expiry", "rl_prefill_attention_set_split_blocks",
+    "rl_prefill_attention_run_length",
 )
 
 
@@ -73,6 +74,7 @@ def lib() -> C.CDLL:
         L.rl_prefill_attention_health.argtypes = [C.POINTER(C.c_int)]
         L.rl_attention_test_wait_expiry.argtypes = [C.c_int, C.c_int64]
         L.rl_prefill_attention_set_split_blocks.argtypes = [C.c_int]
+        L.rl_prefill_attention_run_length.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
         L.rl_decode_linear_set_max_splits.argtypes = [C.c_int]
         for name in ABI_SYMBOLS[2:]:
             getattr(L, name).restype = C.c_int
@@ -205,6 +207,15 @@ def launch_paged_prefill_attention(out, out_row_stride, q, q_row_stride, kv_pool
 def set_prefill_attention_split_blocks(blocks: int) -> None:
     """Longest run of 128-key blocks per CTA in the prefill attention kernel (0 = chosen per launch)."""
     _check(lib().rl_prefill_attention_set_split_blocks(blocks), "rl_prefill_attention_set_split_blocks")
+
+
+def prefill_attention_run_length(chunk_start: int, chunk_len: int, num_q_heads: int, sm_count: int) -> int:
+    """The longest run of 128-key blocks one CTA would take for this chunk on a device of `sm_count` SMs
+    (host arithmetic; no device needed)."""
+    out = C.c_int32(0)
+    _check(lib().rl_prefill_attention_run_length(chunk_start, chunk_len, num_q_heads, sm_count, C.byref(out)),
+           "rl_prefill_attention_run_length")
+    return int(out.value)
 
 
 def prefill_attention_health() -> int:

@@ -93,3 +93,28 @@ def test_checkpoint_writer_produces_a_well_formed_safetensors_file(tmp_path):
     assert torch.equal(got.view(64, 64), w.layers[1]["qkv"][:64])
     assert hdr["model.layers.0.mlp.up_proj.weight"]["shape"] == [96, 64]
     assert json.load(open(os.path.join(d, "config.json")))["torch_dtype"] == "bfloat16"
+
+
+def test_prefill_run_length_is_chosen_by_a_replay_of_the_launch():
+    """Host arithmetic of the prefill attention launcher, no device: the longest run of 128-key blocks per CTA
+    comes from replaying the launch (items in grid order, each onto the SM that frees first) over candidate
+    run lengths. Shapes whose measured optimum is known on a 148-SM device pin the model."""
+    run = kernels.prefill_attention_run_length
+    # 2048 rows at context 8192: 16 tiles of 49-64 blocks x 12 heads = 192 items in two waves when whole;
+    # cutting only the longest tiles (runs of at most 56-60 blocks) levels them - measured 120 against 136 us
+    assert 56 <= run(6144, 2048, 12, 148) <= 60
+    # a prompt's last 128 rows against 32768 keys: 12 pairs of 256 blocks, cut into a dozen runs each
+    assert 16 <= run(32640, 128, 12, 148) <= 32
+    # the first rows of a prompt and chunks that fill the machine many times over are left whole
+    assert run(0, 128, 12, 148) == 1
+    assert run(0, 2048, 12, 148) == 16
+    assert run(8192, 8192, 12, 148) == 128
+    for start, n in ((0, 1), (5, 123), (1000, 257), (31744, 1024), (16384, 4096), (100000, 300)):
+        r = run(start, n, 12, 148)
+        assert 1 <= r <= (start + n - 1) // 128 + 1
+        assert r == run(start, n, 12, 148), "the choice is a pure function of the chunk"
+    # fewer SMs, fewer cuts: one SM never cuts anything
+    assert run(6144, 2048, 12, 1) == 64
+    L = kernels.lib()
+    out = ctypes.c_int32(0)
+    assert L.rl_prefill_attention_run_length(0, 0, 12, 148, ctypes.byref(out)) == -2
