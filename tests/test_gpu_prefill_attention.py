@@ -119,6 +119,44 @@ def test_forced_run_lengths_against_the_cpu_checker(own, split):
     assert np.abs(oracle.half_bits_to_f64(got[:chunk_len, :1536]) - ref).max() <= MAX_ABS + 2.0 ** -11
 
 
+def test_a_long_context_cut_by_the_launchers_own_choice(own):
+    """130 rows at position 16000: two query tiles of 126-127 key blocks per head, which the launcher's replay of
+    the launch cuts into several runs per pair (24 pairs on 148 SMs otherwise) - records of many runs combined."""
+    chunk_start, chunk_len = 16000, 130
+    assert K.prefill_attention_run_length(chunk_start, chunk_len, 12, 148) < 64
+    case = make_case(chunk_start, chunk_len, 0xFD7)
+    got = run_fused(case, chunk_start, chunk_len)
+    ref = reference(own, case, chunk_start, chunk_len)
+    out = oracle.half_bits_to_f64(got[:chunk_len, :1536])
+    assert np.isfinite(out).all()
+    assert np.abs(out - ref).max() <= MAX_ABS + 2.0 ** -11 * max(1.0, np.abs(ref).max())
+    assert K.prefill_attention_health() == 0
+
+
+@pytest.mark.parametrize("q_heads,kv_heads", [(6, 1), (8, 4), (16, 8)])
+def test_other_head_counts(own, q_heads, kv_heads):
+    """Any number of query heads that is a multiple of the KV heads (up to 8 KV heads): the page tile of a head is
+    picked by the copy's coordinate, the group size only decides which KV head a query head reads."""
+    chunk_start, chunk_len = 300, 200
+    kv_len = chunk_start + chunk_len
+    blocks = (kv_len + 15) // 16
+    c = wl.config_attention(lens=[kv_len], num_blocks=blocks + 9, seed=0xFE0 + q_heads, q_heads=q_heads, kv_heads=kv_heads)
+    row = np.ascontiguousarray(c["tables"][0, :blocks])
+    width = q_heads * 128
+    q = wl.normal_half(0xFE9 + kv_heads, chunk_len * width).reshape(chunk_len, width)
+    d_out = torch.full((chunk_len, width), 0x1234, dtype=torch.int16, device="cuda")
+    K.launch_paged_prefill_attention(d_out, width, dev(q), width, dev(c["pool"]), dev(row), blocks, chunk_start, chunk_len,
+                                     q_heads, kv_heads, 128, c["scale"])
+    torch.cuda.synchronize()
+    lens = np.arange(chunk_start + 1, kv_len + 1, dtype=np.int32)
+    tables = np.ascontiguousarray(np.tile(row, (chunk_len, 1)))
+    ref = own.paged_attention(q, c["pool"], tables, lens, q_heads, kv_heads, 128, c["scale"], f64out=True)
+    out = oracle.half_bits_to_f64(host(d_out))
+    assert np.isfinite(out).all()
+    assert np.abs(out - ref).max() <= MAX_ABS + 2.0 ** -11 * max(1.0, np.abs(ref).max())
+    assert K.prefill_attention_health() == 0
+
+
 def test_output_stride_gap_is_untouched_and_inputs_are_read_only(own):
     chunk_start, chunk_len = 200, 150
     case = make_case(chunk_start, chunk_len, 0xF77)
