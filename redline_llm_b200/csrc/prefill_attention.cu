@@ -130,6 +130,28 @@ __device__ __forceinline__ float Ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two FP32 lanes in one 64-bit register for the packed FP32 pipe (sm_100): one issue slot scales two scores,
+// another adds two probabilities to the two running sums. Each lane is the ordinary IEEE operation.
+__device__ __forceinline__ uint64_t Pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float2 Unpack2(uint64_t v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+__device__ __forceinline__ uint64_t Fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t Add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 // max(a, b, c) in one instruction (sm_100): halves the comparisons of the maximum pass.
 __device__ __forceinline__ float Max3(float a, float b, float c) {
   float d;
@@ -427,28 +449,29 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       }
       // pass 2: probabilities, FP16, into tensor memory (the A operand of P.V); their FP32 sum
       const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 32 * hw;
-      const float neg_ref = -m_ref;
-      float sum0 = 0.0f, sum1 = 0.0f;
+      const uint64_t scale2 = Pack2(p.scale_log2e, p.scale_log2e), neg_ref2 = Pack2(-m_ref, -m_ref);
+      uint64_t sums = Pack2(0.0f, 0.0f);   // even keys, odd keys
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-          float p0 = Ex2(fmaf(__uint_as_float(raw[c][i]), p.scale_log2e, neg_ref));
-          float p1 = Ex2(fmaf(__uint_as_float(raw[c][i + 1]), p.scale_log2e, neg_ref));
+          const float2 x = Unpack2(Fma2(Pack2(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale2, neg_ref2));
+          float p0 = Ex2(x.x);
+          float p1 = Ex2(x.y);
           if (diagonal) {
             p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
             p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
           }
-          sum0 += p0;
-          sum1 += p1;
+          sums = Add2(sums, Pack2(p0, p1));
           packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
         }
         // P goes to tensor memory in key order, two FP16 per column: keys 64 * hw + 16 * c .. + 15 of this row
         TmemStore8(p_addr + 8 * c, packed);
       }
       TmemWaitStores();
-      const float sum = sum0 + sum1;
+      const float2 sum01 = Unpack2(sums);
+      const float sum = sum01.x + sum01.y;
       l += sum;
       // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
       // would poison the row: clear them once the block has landed.
