@@ -30,14 +30,16 @@
 //    block j+2 is issued as soon as the softmax of block j has released its buffer, so the tensor pipe runs
 //    under the softmax of block j+1.
 //  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
-//    its own quarter of the tensor-memory lanes). Each thread reads its half row of S from tensor memory
-//    (tcgen05.ld 32x32b) twice - the maximum, exchanged with its partner through shared memory, then the
-//    exponentials (ex2.approx in the exp2 domain) - and writes P as FP16 pairs into tensor memory
+//    its own quarter of the tensor-memory lanes). Each thread reads its half row of S from tensor memory once
+//    (tcgen05.ld 32x32b) and writes P = exp2(s * scale - reference) as FP16 pairs into tensor memory
 //    (tcgen05.st, two P buffers of 64 columns), from where the P.V product takes its A operand: P never
-//    touches shared memory, whose bandwidth is what bounds this kernel. The running reference maximum is only moved when a row's
-//    maximum exceeds it by more than 2^8: P then stays below 2^8 (exact in FP16's range), and the rescaling of
-//    the running output - a read-modify-write of the row in tensor memory - almost never happens after the
-//    first block; numerator and denominator always share one reference, so the result does not depend on it.
+//    touches shared memory. The sweep is bound by instruction issue, so two scores are scaled per
+//    fma.rn.f32x2 and two probabilities summed per add.rn.f32x2. The reference is the row's maximum of the
+//    FIRST block; later blocks are written against it without looking at their maximum, and only a half row
+//    whose probabilities sum to 2^15 or more (a score more than 2^9 above the reference) sends its two warps
+//    to the full treatment: exact maximum exchanged through shared memory, reference moved, row sum and running
+//    output (a read-modify-write of the row in tensor memory) rescaled, block written again. Numerator and
+//    denominator always share one reference, so the result does not depend on when it moves.
 //  * O += P.V: A = P (in tensor memory) and B = V as it lies in the pool - [key][dim], i.e. MN-major: atoms of
 //    8 keys x 64 dims, 2 KiB between key groups, 1 KiB between the dim halves, one page per K = 16 slice -
 //    accumulated over all blocks in tensor-memory columns 256-383; read once at the end, divided by the row
@@ -75,7 +77,8 @@ constexpr int kSmemBytes = kSmemNeeded + 1024;     // + slack for aligning the b
 static_assert(kSmemBytes <= 227 * 1024, "prefill attention shared memory exceeds the per-CTA limit");
 constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383, P (FP16 pairs): 384-447 and 448-511
 constexpr int kTmemP = 384;
-constexpr float kRescaleThreshold = 8.0f;   // log2: P never exceeds 2^8
+constexpr float kRescaleThreshold = 8.0f;   // log2: when a block's maximum is looked at, the reference moves if it lies more than this above it
+constexpr float kOverflowSum = 32768.0f;    // a half row of P that sums to 2^15 or more may hold a value near FP16's largest: look at the maximum
 constexpr int kPartialFloats = kBM * kHeadDim + 2 * kBM;   // o[128][128] unnormalised, m[128], l[128]
 
 struct Params {
@@ -185,6 +188,21 @@ __device__ __forceinline__ void UmmaTsElected(uint32_t d_tmem, uint32_t a_tmem, 
 }
 __device__ __forceinline__ void TmemWaitStores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
+// The two warps that share 32 query rows (keys 0-63 and 64-127 of a block) meet on a barrier of their own:
+// a plain rendezvous, and one that also tells both whether any of their 64 threads raised `pred`.
+__device__ __forceinline__ void PairBarrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ bool PairAny(int id, bool pred) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %2, 0;\n\t"
+      "bar.red.or.pred p, %1, 64, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any)
+      : "r"(id), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return any != 0;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap q_map,
@@ -404,74 +422,98 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       const int buf = j & 1;
       const int key0 = (jb0 + j) * kBN + hw * 64;
       const bool diagonal = (jb0 + j) * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
-      // pass 1: their maximum (raw: the scale is positive)
-      float mx = -INFINITY;
-      if (diagonal) {
+      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 32 * hw;
+      const int pair_bar = 2 + (warp & 3);
+      // The raw maximum of this thread's 64 scores (raw: the scale is positive), masked keys left out.
+      auto row_max = [&]() {
+        float mx = -INFINITY;
+        if (diagonal) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
-      } else {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, two scores per instruction
+            for (int i = 0; i < 16; ++i)
+              mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
+        } else {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, two scores per instruction
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; i += 2)
-            m4[(i >> 1) & 3] = Max3(m4[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      }
-      float* xm = xmax + buf * 256;
-      xm[hw * 128 + row] = mx;
-      SoftmaxBarrier();
-      mx = fmaxf(mx, xm[(hw ^ 1) * 128 + row]) * p.scale_log2e;
-      // Move the reference when the row's maximum has outgrown it: rescale the row sum and, from the second
-      // block on, this thread's half of the running output row in tensor memory (the previous block's P.V
-      // must have completed). Tensor-memory accesses are warp-wide: rows that keep their reference take
-      // part with a factor of one.
-      const bool move = mx > m_ref + kRescaleThreshold;
-      const float alpha = move ? Ex2(m_ref - mx) : 1.0f;       // 0 on the first block
-      l *= alpha;
-      if (move) m_ref = mx;
-      if (j > 0 && __any_sync(0xffffffffu, move)) {
-        wait(bar_o0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
-        TcFenceAfter();
+            for (int i = 0; i < 16; i += 2)
+              m4[(i >> 1) & 3] = Max3(m4[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
+        return mx;
+      };
+      // Probabilities against the reference, FP16, into tensor memory in key order (two per column: keys
+      // 64 * hw + 16 * c .. + 15 of this row - the A operand of P.V); returns their FP32 sum.
+      auto write_probabilities = [&](float ref) {
+        const uint64_t scale2 = Pack2(p.scale_log2e, p.scale_log2e), neg_ref2 = Pack2(-ref, -ref);
+        uint64_t sums = Pack2(0.0f, 0.0f);   // even keys, odd keys
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t raw[16];
-          TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
-          TmemWaitLoads(raw);
+          uint32_t packed[8];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
-          TmemStore16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
-        }
-        TmemWaitStores();
-      }
-      // pass 2: probabilities, FP16, into tensor memory (the A operand of P.V); their FP32 sum
-      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 32 * hw;
-      const uint64_t scale2 = Pack2(p.scale_log2e, p.scale_log2e), neg_ref2 = Pack2(-m_ref, -m_ref);
-      uint64_t sums = Pack2(0.0f, 0.0f);   // even keys, odd keys
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float2 x = Unpack2(Fma2(Pack2(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale2, neg_ref2));
-          float p0 = Ex2(x.x);
-          float p1 = Ex2(x.y);
-          if (diagonal) {
-            p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
-            p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
+          for (int i = 0; i < 16; i += 2) {
+            const float2 x = Unpack2(Fma2(Pack2(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale2, neg_ref2));
+            float p0 = Ex2(x.x);
+            float p1 = Ex2(x.y);
+            if (diagonal) {
+              p0 = key0 + c * 16 + i <= my_pos ? p0 : 0.0f;
+              p1 = key0 + c * 16 + i + 1 <= my_pos ? p1 : 0.0f;
+            }
+            sums = Add2(sums, Pack2(p0, p1));
+            packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
           }
-          sums = Add2(sums, Pack2(p0, p1));
-          packed[i >> 1] = AsU32(__floats2half2_rn(p0, p1));
+          TmemStore8(p_addr + 8 * c, packed);
         }
-        // P goes to tensor memory in key order, two FP16 per column: keys 64 * hw + 16 * c .. + 15 of this row
-        TmemStore8(p_addr + 8 * c, packed);
+        const float2 sum01 = Unpack2(sums);
+        return sum01.x + sum01.y;
+      };
+      // After the first block the row's maximum is not looked at block by block: the probabilities are written
+      // against the running reference right away, and only a half row whose sum reaches 2^15 - some score lies more
+      // than 2^9 above the reference, so a value may come near FP16's largest - sends its two warps (one barrier
+      // that also carries the vote) to the full treatment: the exact maximum, exchanged with the partner; the
+      // reference moved; row sum and running output rescaled; the block written again. Numerator and denominator
+      // always share one reference, so the result does not depend on when it moves; P stays below 2^16.
+      float sum = 0.0f;
+      bool settle = true;
+      if (j > 0) {
+        sum = write_probabilities(m_ref);
+        settle = PairAny(pair_bar, !(sum < kOverflowSum));
+      }
+      if (settle) {
+        float mx = row_max();
+        float* xm = xmax + buf * 256;
+        xm[hw * 128 + row] = mx;
+        PairBarrier(pair_bar);
+        mx = fmaxf(mx, xm[(hw ^ 1) * 128 + row]) * p.scale_log2e;
+        // Rescale the row sum and, from the second block on, this thread's half of the running output row in
+        // tensor memory (the previous block's P.V must have completed). Tensor-memory accesses are warp-wide:
+        // rows that keep their reference take part with a factor of one.
+        const bool move = mx > m_ref + kRescaleThreshold;
+        const float alpha = move ? Ex2(m_ref - mx) : 1.0f;       // 0 on the first block
+        l *= alpha;
+        if (move) m_ref = mx;
+        if (j > 0) {
+          TmemWaitStores();                                      // the first sweep's P, about to be overwritten
+          if (__any_sync(0xffffffffu, move)) {
+            wait(bar_o0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
+            TcFenceAfter();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t acc[16];
+              TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, acc);
+              TmemWaitLoads(acc);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+              TmemStore16(tmem_o + hw * 64 + lane_addr + c * 16, acc);
+            }
+            TmemWaitStores();
+          }
+        }
+        sum = write_probabilities(m_ref);
       }
       TmemWaitStores();
-      const float2 sum01 = Unpack2(sums);
-      const float sum = sum01.x + sum01.y;
       l += sum;
       // V rows at or past the context end (the last block only) may hold anything, NaN included, and 0 * NaN
       // would poison the row: clear them once the block has landed.

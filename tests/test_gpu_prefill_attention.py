@@ -70,17 +70,19 @@ def test_chunk_against_the_cpu_checker(own, chunk_start, chunk_len):
 
 
 def test_scores_that_outgrow_the_running_reference_late_in_the_context(own):
-    """The kernel keeps a stale reference maximum per row and rescales its running output (in tensor memory)
-    only when a later score exceeds it by more than 2^8. Keys from position 640 on are made eight times
-    larger, so every row's maximum jumps far beyond that in the middle of the context, twice over the
-    blocks: the rescaling path must give the same result as an exact softmax."""
+    """The kernel keeps a stale reference maximum per row: after the first block it only looks at a block's
+    maximum - and moves the reference, rescaling its running output in tensor memory - when a half row of
+    probabilities sums to 2^15 or more. Keys from position 640 on are made 8, then 24, then 96 times larger, so
+    every row's scores jump far beyond the reference three times over the blocks, by more and by less than that
+    limit: the result must be that of an exact softmax either way."""
     chunk_start, chunk_len = 900, 200
     case = make_case(chunk_start, chunk_len, 0xFA1)
     pool = case["pool"].reshape(-1, 2, 2, 16, 128)
     for g in range(40, (case["kv_len"] + 15) // 16):
         k = pool[case["row"][g], 0]                     # K tiles of logical page g, both heads
         live = (k & 0x7FFF) < 0x7C00                    # leave the NaN padding of the last page alone
-        k[live] = ((k[live].view(np.float16).astype(np.float32) * (8.0 if g < 50 else 24.0)).astype(np.float16)).view(np.uint16)
+        factor = 8.0 if g < 50 else (24.0 if g < 60 else 96.0)
+        k[live] = ((k[live].view(np.float16).astype(np.float32) * factor).astype(np.float16)).view(np.uint16)
     got = run_fused(case, chunk_start, chunk_len)
     ref = reference(own, case, chunk_start, chunk_len)
     out = oracle.half_bits_to_f64(got[:chunk_len, :1536])
