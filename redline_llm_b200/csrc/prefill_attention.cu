@@ -62,8 +62,14 @@ using namespace rl::tc;
 constexpr int kHeadDim = 128;
 constexpr int kBM = 128;                 // query rows per CTA
 constexpr int kBN = 128;                 // keys per block (8 pages)
-constexpr int kSoftmaxThreads = 256;     // warps 0-7: two threads per query row
+constexpr int kRowSplit = 2;             // softmax threads per query row (4 - sixteen softmax warps, 96 registers - measured 6 % slower)
+constexpr int kSoftmaxThreads = kBM * kRowSplit;   // warps 0-7: two threads per query row
+constexpr int kMmaWarp = kSoftmaxThreads / 32, kLoadWarp = kMmaWarp + 1;
 constexpr int kThreads = kSoftmaxThreads + 64;   // + the MMA-issue warp and the loader warp
+constexpr int kKeysPerThread = kBN / kRowSplit;        // scores of a block one softmax thread owns
+constexpr int kScoreChunks = kKeysPerThread / 16;      // in tensor-memory loads of 16 columns
+constexpr int kDimsPerThread = kHeadDim / kRowSplit;   // output dims one softmax thread owns at the end
+constexpr int kDimChunks = kDimsPerThread / 16;
 constexpr int kPagesPerBlock = kBN / kKvBlock;
 constexpr int kRegionBytes = 128 * 128;  // [128 rows][64 halves], 128-byte swizzle
 constexpr int kTileBytes = 2 * kRegionBytes;   // two 64-wide halves
@@ -71,8 +77,9 @@ constexpr int kQOff = 0;
 constexpr int kKOff = kQOff + kTileBytes;          // 2 buffers
 constexpr int kVOff = kKOff + 2 * kTileBytes;      // 2 buffers
 constexpr int kBarOff = kVOff + 2 * kTileBytes;    // mbarriers, tmem slot
-constexpr int kXOff = kBarOff + 128;               // row maxima [2 iterations][2 halves][128] (row sums reuse one half at the end)
-constexpr int kSmemNeeded = kXOff + 4 * 128 * 4;   // from a 1024-byte aligned base
+constexpr int kXOff = kBarOff + 128;               // row maxima [2 iterations][threads of a row][128] (row sums reuse one half at the end)
+constexpr int kXFloats = kRowSplit * kBM;          // one iteration's exchange buffer
+constexpr int kSmemNeeded = kXOff + 2 * kXFloats * 4;   // from a 1024-byte aligned base
 constexpr int kSmemBytes = kSmemNeeded + 1024;     // + slack for aligning the base
 static_assert(kSmemBytes <= 227 * 1024, "prefill attention shared memory exceeds the per-CTA limit");
 constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256-383, P (FP16 pairs): 384-447 and 448-511
@@ -190,16 +197,16 @@ __device__ __forceinline__ void TmemWaitStores() { asm volatile("tcgen05.wait::s
 __device__ __forceinline__ void SoftmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
 // The two warps that share 32 query rows (keys 0-63 and 64-127 of a block) meet on a barrier of their own:
 // a plain rendezvous, and one that also tells both whether any of their 64 threads raised `pred`.
-__device__ __forceinline__ void PairBarrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void PairBarrier(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(32 * kRowSplit) : "memory"); }
 __device__ __forceinline__ bool PairAny(int id, bool pred) {
   uint32_t any;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %2, 0;\n\t"
-      "bar.red.or.pred p, %1, 64, q;\n\t"
+      "bar.red.or.pred p, %1, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(any)
-      : "r"(id), "r"(static_cast<uint32_t>(pred))
+      : "r"(id), "r"(static_cast<uint32_t>(pred)), "n"(32 * kRowSplit)
       : "memory");
   return any != 0;
 }
@@ -224,7 +231,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   const uint32_t bar_q = bars, bar_k0 = bars + 8, bar_v0 = bars + 24, bar_s0 = bars + 40, bar_p0 = bars + 56,
                  bar_o0 = bars + 72, bar_done = bars + 88;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kBarOff + 96);
-  float* xmax = reinterpret_cast<float*>(smem + kXOff);          // [2][2][128]
+  float* xmax = reinterpret_cast<float*>(smem + kXOff);          // [2][kRowSplit][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Work items of a head, long tiles first (the last query tile of the chunk attends to the most keys): a tile
@@ -266,7 +273,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      SmemAddr(const_cast<uint32_t*>(tmem_slot))),
                  "r"(kTmemCols)
@@ -287,7 +294,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     }
   };
 
-  if (warp == 9) {
+  if (warp == kLoadWarp) {
     // ------------------------------------------------------------ loader: every TMA request
     // A block is 8 copies of 4 KiB for K and 8 for V, one per page, spread over the lanes. The block id of a page
     // serves K and V alike and is read from the table two blocks ahead of its use.
@@ -337,7 +344,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       if (t >= 2) wait(bar_o0 + 8 * (t & 1), ((t - 2) >> 1) & 1);   // V buffer: free once P_{t-2}.V_{t-2} has completed
       load_v(t, blk);
     }
-  } else if (warp == 8) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issue
     // The whole warp walks the schedule converged and every product is issued by one elected lane: the
     // descriptors depend on the block's buffer, and computed inside a one-lane branch they cost the issue
@@ -405,38 +412,38 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // This thread's 64 scores of a block are fetched from tensor memory once, all four loads in flight together,
     // and kept in registers for both passes. The fetch for block j+1 is made at the END of block j, before this
     // thread reports P_j: that report then also says that S_{j+1}'s buffer may be overwritten.
-    uint32_t raw[4][16];
+    uint32_t raw[kScoreChunks][16];
     auto fetch_scores = [&](int j) {
       wait(bar_s0 + 8 * (j & 1), (j >> 1) & 1);
       TcFenceAfter();
-      const uint32_t s_addr = tmem_base + (j & 1) * kBN + hw * 64 + lane_addr;
+      const uint32_t s_addr = tmem_base + (j & 1) * kBN + hw * kKeysPerThread + lane_addr;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) TmemLoad16(s_addr + c * 16, raw[c]);
+      for (int c = 0; c < kScoreChunks; ++c) TmemLoad16(s_addr + c * 16, raw[c]);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) TmemWaitLoads(raw[c]);
+      for (int c = 0; c < kScoreChunks; ++c) TmemWaitLoads(raw[c]);
     };
     fetch_scores(0);
 
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1;
-      const int key0 = (jb0 + j) * kBN + hw * 64;
+      const int key0 = (jb0 + j) * kBN + hw * kKeysPerThread;
       const bool diagonal = (jb0 + j) * kBN + kBN - 1 > p.chunk_start + row0;   // some row of the tile is masked inside this block
-      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + 32 * hw;
+      const uint32_t p_addr = tmem_base + kTmemP + buf * (kBN / 2) + lane_addr + (kKeysPerThread / 2) * hw;
       const int pair_bar = 2 + (warp & 3);
       // The raw maximum of this thread's 64 scores (raw: the scale is positive), masked keys left out.
       auto row_max = [&]() {
         float mx = -INFINITY;
         if (diagonal) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < kScoreChunks; ++c)
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               mx = fmaxf(mx, key0 + c * 16 + i <= my_pos ? __uint_as_float(raw[c][i]) : -INFINITY);
         } else {
           float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, two scores per instruction
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < kScoreChunks; ++c)
 #pragma unroll
             for (int i = 0; i < 16; i += 2)
               m4[(i >> 1) & 3] = Max3(m4[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
@@ -450,7 +457,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         const uint64_t scale2 = Pack2(p.scale_log2e, p.scale_log2e), neg_ref2 = Pack2(-ref, -ref);
         uint64_t sums = Pack2(0.0f, 0.0f);   // even keys, odd keys
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kScoreChunks; ++c) {
           uint32_t packed[8];
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
@@ -483,10 +490,12 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       }
       if (settle) {
         float mx = row_max();
-        float* xm = xmax + buf * 256;
-        xm[hw * 128 + row] = mx;
+        float* xm = xmax + buf * kXFloats;
+        xm[hw * kBM + row] = mx;
         PairBarrier(pair_bar);
-        mx = fmaxf(mx, xm[(hw ^ 1) * 128 + row]) * p.scale_log2e;
+#pragma unroll
+        for (int o = 1; o < kRowSplit; ++o) mx = fmaxf(mx, xm[((hw + o) % kRowSplit) * kBM + row]);
+        mx *= p.scale_log2e;
         // Rescale the row sum and, from the second block on, this thread's half of the running output row in
         // tensor memory (the previous block's P.V must have completed). Tensor-memory accesses are warp-wide:
         // rows that keep their reference take part with a factor of one.
@@ -500,13 +509,13 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
             wait(bar_o0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1);
             TcFenceAfter();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kDimChunks; ++c) {
               uint32_t acc[16];
-              TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, acc);
+              TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, acc);
               TmemWaitLoads(acc);
 #pragma unroll
               for (int i = 0; i < 16; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
-              TmemStore16(tmem_o + hw * 64 + lane_addr + c * 16, acc);
+              TmemStore16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, acc);
             }
             TmemWaitStores();
           }
@@ -521,12 +530,16 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       if (rows_valid < kBN) {
         wait(bar_v0 + 8 * buf, (j >> 1) & 1);
         if (row >= rows_valid) {
-          // key `row` of the block: page row / 16, token group (row / 8) % 2, token row % 8; this thread clears
-          // dim half hw of it (the swizzle only permutes 16-byte pieces inside the 128-byte row)
+          // key `row` of the block: page row / 16, token group (row / 8) % 2, token row % 8; the row's threads
+          // clear its 256 bytes between them (the swizzle only permutes 16-byte pieces inside a 128-byte row, and
+          // all of them are cleared)
+          constexpr int kClearBytes = 2 * kHeadDim / kRowSplit;
+          const int byte0 = hw * kClearBytes;
           uint4* r = reinterpret_cast<uint4*>(smem + kVOff + buf * kTileBytes + (row >> 4) * kPageTileBytes +
-                                              ((row >> 3) & 1) * kGroupStride + hw * kHalfStride + (row & 7) * 128);
+                                              ((row >> 3) & 1) * kGroupStride + (byte0 >> 7) * kHalfStride +
+                                              (row & 7) * 128 + (byte0 & 127));
 #pragma unroll
-          for (int i = 0; i < 8; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
+          for (int i = 0; i < kClearBytes / 16; ++i) r[i] = make_uint4(0u, 0u, 0u, 0u);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared rows, visible to the tensor pipe
       }
@@ -538,21 +551,23 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // ---- the running output: this thread's 64 dims of its row
     // (the row sums of the two key halves meet through the exchange buffer the last block did not use: every
     // read of it lies before that block's barrier)
-    float* xsum = xmax + (nblk & 1) * 256;
-    xsum[hw * 128 + row] = l;
+    float* xsum = xmax + (nblk & 1) * kXFloats;
+    xsum[hw * kBM + row] = l;
     SoftmaxBarrier();
-    const float l_row = l + xsum[(hw ^ 1) * 128 + row];
+    float l_row = 0.0f;   // the same order in every thread of the row
+#pragma unroll
+    for (int o = 0; o < kRowSplit; ++o) l_row += xsum[o * kBM + row];
     wait(bar_done, 0);
     TcFenceAfter();
     const int out_row = row0 + row;
-    half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + hw * 64;
+    half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + hw * kDimsPerThread;
     if (nsplit == 1) {
       // the whole key range was this CTA's: divide by the row's sum, round once, store
       const float inv = 1.0f / l_row;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kDimChunks; ++c) {
         uint32_t raw[16];
-        TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+        TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, raw);
         TmemWaitLoads(raw);
         if (ok && out_row < p.chunk_len) {
           uint32_t w[8];
@@ -570,11 +585,11 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       float* rec0 = p.partials + (static_cast<size_t>(head) * gridDim.y + (blockIdx.y - split)) * kPartialFloats;
       float* rec = rec0 + static_cast<size_t>(split) * kPartialFloats;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kDimChunks; ++c) {
         uint32_t raw[16];
-        TmemLoad16(tmem_o + hw * 64 + lane_addr + c * 16, raw);
+        TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, raw);
         TmemWaitLoads(raw);
-        float4* o4 = reinterpret_cast<float4*>(rec + row * kHeadDim + hw * 64 + c * 16);
+        float4* o4 = reinterpret_cast<float4*>(rec + row * kHeadDim + hw * kDimsPerThread + c * 16);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           o4[i] = make_float4(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]), __uint_as_float(raw[4 * i + 2]),
@@ -586,7 +601,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       }
       __threadfence();
       SoftmaxBarrier();                       // every thread's part of the record is written and fenced
-      int* last = reinterpret_cast<int*>(xmax + ((nblk + 1) & 1) * 256);
+      int* last = reinterpret_cast<int*>(xmax + ((nblk + 1) & 1) * kXFloats);
       if (tid == 0) {
         int* ticket = p.tickets + head * p.n_tiles + tile_q;
         const int t = atomicAdd(ticket, 1);
@@ -598,18 +613,18 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         __threadfence();
         float mx = -INFINITY;
         for (int sidx = 0; sidx < nsplit; ++sidx) mx = fmaxf(mx, __ldcg(rec0 + sidx * kPartialFloats + kBM * kHeadDim + row));
-        float acc[64];
+        float acc[kDimsPerThread];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < kDimsPerThread; ++i) acc[i] = 0.0f;
         float den = 0.0f;
 #pragma unroll 1
         for (int sidx = 0; sidx < nsplit; ++sidx) {
           const float* r = rec0 + static_cast<size_t>(sidx) * kPartialFloats;
           const float wgt = Ex2(__ldcg(r + kBM * kHeadDim + row) - mx);      // 0 for a run that saw no key of this row
           den = fmaf(wgt, __ldcg(r + kBM * kHeadDim + kBM + row), den);
-          const float4* o4 = reinterpret_cast<const float4*>(r + row * kHeadDim + hw * 64);
+          const float4* o4 = reinterpret_cast<const float4*>(r + row * kHeadDim + hw * kDimsPerThread);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < kDimsPerThread / 4; ++i) {
             const float4 v = __ldcg(o4 + i);
             acc[4 * i] = fmaf(wgt, v.x, acc[4 * i]);
             acc[4 * i + 1] = fmaf(wgt, v.y, acc[4 * i + 1]);
@@ -620,7 +635,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         if (ok && out_row < p.chunk_len) {
           const float inv = 1.0f / den;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < kDimsPerThread / 8; ++c) {
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) w[i] = AsU32(__floats2half2_rn(acc[c * 8 + 2 * i] * inv, acc[c * 8 + 2 * i + 1] * inv));
@@ -632,7 +647,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   }
   TcFenceBefore();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
