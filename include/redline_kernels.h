@@ -185,8 +185,8 @@ int rl_prefill_attention_health(int* flag_out);
 
 /*
  * Tuning knob of rl_launch_paged_prefill_attention: the longest run of 128-key blocks one CTA takes before a
- * (query tile, head) pair is cut across CTAs (their records are combined in run order by the CTA that arrives
- * last, so results do not depend on it beyond FP32 summation order). 0 (default) = chosen per launch from the
+ * (query tile, head) pair is cut across CTAs (their records are combined in run order by a second kernel of the
+ * same launch call, so results do not depend on it beyond FP32 summation order). 0 (default) = chosen per launch from the
  * chunk's shape and the SM count. Process-wide. A launch that cuts pairs keeps a scratch area in device memory
  * (grown on demand outside stream capture, 66 KB per work item). No counterpart in the reference.
  */

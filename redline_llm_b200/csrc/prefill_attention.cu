@@ -10,10 +10,10 @@
 // probabilities rounded to FP16 for the P.V product, FP32 accumulation, one FP16 rounding of acc / l -
 // with nothing but Q, the pages and the output ever touching global memory.
 //
-// Mapping. One CTA per (128-row query tile, query head) - or per run of at most 16 key blocks of such a pair when
-// its context is longer (2048 keys): the runs' unnormalised outputs meet in a scratch area and the CTA that
-// arrives last combines them in run order, so long contexts fill the machine and the result does not depend
-// on timing. Ten warps.
+// Mapping. One CTA per (128-row query tile, query head) - or per run of key blocks of such a pair when the launch
+// would otherwise leave SMs idle (the run length is chosen per launch): the runs' unnormalised outputs meet in a
+// scratch area and a small second kernel, launched behind this one, combines them in run
+// order, so long contexts fill the machine and the result does not depend on timing. Ten warps.
 //  * Warp 9 requests every tile by TMA (copies spread over its lanes), warp 8 issues every tcgen05.mma: table
 //    reads and copy requests never sit between two products. Q tile and K/V
 //    blocks of 128 keys (8 pages) arrive with the 128-byte swizzle. A page tile of the pool is
@@ -86,7 +86,9 @@ constexpr int kTmemCols = 512;           // S: columns 0-127 and 128-255, O: 256
 constexpr int kTmemP = 384;
 constexpr float kRescaleThreshold = 8.0f;   // log2: when a block's maximum is looked at, the reference moves if it lies more than this above it
 constexpr float kOverflowSum = 32768.0f;    // a half row of P that sums to 2^15 or more may hold a value near FP16's largest: look at the maximum
-constexpr int kPartialFloats = kBM * kHeadDim + 2 * kBM;   // o[128][128] unnormalised, m[128], l[128]
+// A run's record: o unnormalised as [dim / 4][row][4] - the 32 rows of a warp write, and later read, 512 contiguous
+// bytes per instruction - then m[128], l[128].
+constexpr int kPartialFloats = kBM * kHeadDim + 2 * kBM;
 
 struct Params {
   half* out;
@@ -102,7 +104,6 @@ struct Params {
   int n_tiles;        // query tiles of the chunk
   int split_blocks;   // longest run of key blocks one CTA takes
   float* partials;    // one record of kPartialFloats per (head, work item) for pairs cut across CTAs
-  int* tickets;       // one counter per (head, query tile), zero between launches
 };
 
 // Where a page lands in a K or V block buffer: [token group of 8][dim half][8 tokens][128 B].
@@ -579,69 +580,23 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
         }
       }
     } else {
-      // One run of a tile's key blocks: publish (o unnormalised, m, l) and take a ticket; whichever CTA of the
-      // tile comes last combines ALL runs' records, its own included, in run order - so the result does not
-      // depend on who that is.
-      float* rec0 = p.partials + (static_cast<size_t>(head) * gridDim.y + (blockIdx.y - split)) * kPartialFloats;
-      float* rec = rec0 + static_cast<size_t>(split) * kPartialFloats;
+      // One run of a tile's key blocks: leave (o unnormalised, reference, row sum) for the kernel that follows this
+      // one in the stream and combines a pair's runs in run order.
+      float* rec = p.partials + (static_cast<size_t>(head) * gridDim.y + blockIdx.y) * kPartialFloats;
 #pragma unroll
       for (int c = 0; c < kDimChunks; ++c) {
         uint32_t raw[16];
         TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, raw);
         TmemWaitLoads(raw);
-        float4* o4 = reinterpret_cast<float4*>(rec + row * kHeadDim + hw * kDimsPerThread + c * 16);
+        float4* o4 = reinterpret_cast<float4*>(rec) + ((hw * kDimsPerThread + c * 16) / 4) * kBM + row;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          o4[i] = make_float4(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]), __uint_as_float(raw[4 * i + 2]),
-                              __uint_as_float(raw[4 * i + 3]));
+          o4[i * kBM] = make_float4(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]), __uint_as_float(raw[4 * i + 2]),
+                                    __uint_as_float(raw[4 * i + 3]));
       }
       if (hw == 0) {
         rec[kBM * kHeadDim + row] = m_ref;
         rec[kBM * kHeadDim + kBM + row] = l_row;
-      }
-      __threadfence();
-      SoftmaxBarrier();                       // every thread's part of the record is written and fenced
-      int* last = reinterpret_cast<int*>(xmax + ((nblk + 1) & 1) * kXFloats);
-      if (tid == 0) {
-        int* ticket = p.tickets + head * p.n_tiles + tile_q;
-        const int t = atomicAdd(ticket, 1);
-        if (t == nsplit - 1) *ticket = 0;     // everyone has arrived: re-arm for the next launch
-        *last = t == nsplit - 1;
-      }
-      SoftmaxBarrier();
-      if (*last) {
-        __threadfence();
-        float mx = -INFINITY;
-        for (int sidx = 0; sidx < nsplit; ++sidx) mx = fmaxf(mx, __ldcg(rec0 + sidx * kPartialFloats + kBM * kHeadDim + row));
-        float acc[kDimsPerThread];
-#pragma unroll
-        for (int i = 0; i < kDimsPerThread; ++i) acc[i] = 0.0f;
-        float den = 0.0f;
-#pragma unroll 1
-        for (int sidx = 0; sidx < nsplit; ++sidx) {
-          const float* r = rec0 + static_cast<size_t>(sidx) * kPartialFloats;
-          const float wgt = Ex2(__ldcg(r + kBM * kHeadDim + row) - mx);      // 0 for a run that saw no key of this row
-          den = fmaf(wgt, __ldcg(r + kBM * kHeadDim + kBM + row), den);
-          const float4* o4 = reinterpret_cast<const float4*>(r + row * kHeadDim + hw * kDimsPerThread);
-#pragma unroll
-          for (int i = 0; i < kDimsPerThread / 4; ++i) {
-            const float4 v = __ldcg(o4 + i);
-            acc[4 * i] = fmaf(wgt, v.x, acc[4 * i]);
-            acc[4 * i + 1] = fmaf(wgt, v.y, acc[4 * i + 1]);
-            acc[4 * i + 2] = fmaf(wgt, v.z, acc[4 * i + 2]);
-            acc[4 * i + 3] = fmaf(wgt, v.w, acc[4 * i + 3]);
-          }
-        }
-        if (ok && out_row < p.chunk_len) {
-          const float inv = 1.0f / den;
-#pragma unroll
-          for (int c = 0; c < kDimsPerThread / 8; ++c) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) w[i] = AsU32(__floats2half2_rn(acc[c * 8 + 2 * i] * inv, acc[c * 8 + 2 * i + 1] * inv));
-            *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
       }
     }
   }
@@ -650,6 +605,74 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+// The pairs that were cut into runs: their records - unnormalised output, reference and row sum against that
+// reference - are combined in run order, so the result does not depend on which CTA ran when. One CTA per (head,
+// tile, 32 query rows); a warp takes 16 dims of those rows, one row per lane; every row of a cut pair is handled by
+// exactly one thread group, and pairs that one CTA held whole were stored by the main kernel and are left alone. Launched
+// behind the main kernel in the same stream, over the chunk's last tiles only (the cut ones). (As a dependent
+// launch that the main kernel releases when its CTAs start, it measured 4-6 us SLOWER on launches of 20-40 us.)
+constexpr int kCombineThreads = 256;
+constexpr int kCombineRows = 32;
+static_assert(kCombineThreads / 32 * 16 == kHeadDim, "one warp per 16 dims");
+__global__ void __launch_bounds__(kCombineThreads)
+PrefillCombineKernel(const Params p, int items) {
+  const int head = blockIdx.x, tile = p.n_tiles - 1 - blockIdx.y;
+  const int kv_len = p.chunk_start + p.chunk_len;
+  int runs = 1, item0 = 0;   // the pair's runs and its first work item: the items of later tiles come first
+  for (int t = p.n_tiles - 1; t >= tile; --t) {
+    const int nb = (min(p.chunk_start + (t + 1) * kBM, kv_len) - 1) / kBN + 1;
+    runs = (nb + p.split_blocks - 1) / p.split_blocks;
+    if (t > tile) item0 += runs;
+  }
+  if (runs == 1) return;
+  const int row = blockIdx.z * kCombineRows + threadIdx.x % 32, d0 = (threadIdx.x / 32) * 16;
+  const int out_row = tile * kBM + row;
+  if (out_row >= p.chunk_len) return;
+  const float* rec0 = p.partials + (static_cast<size_t>(head) * items + item0) * kPartialFloats;
+  float mx = -INFINITY;
+  for (int r = 0; r < runs; ++r) mx = fmaxf(mx, __ldcg(rec0 + static_cast<size_t>(r) * kPartialFloats + kBM * kHeadDim + row));
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+  float den = 0.0f;
+  // (the next run's values are requested before the present run's are used: one L2 latency for all runs, not one each)
+  float m_next, l_next;
+  float4 v_next[4];
+  auto request = [&](int r) {
+    const float* rec = rec0 + static_cast<size_t>(r) * kPartialFloats;
+    m_next = __ldcg(rec + kBM * kHeadDim + row);
+    l_next = __ldcg(rec + kBM * kHeadDim + kBM + row);
+    const float4* o4 = reinterpret_cast<const float4*>(rec) + (d0 / 4) * kBM + row;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v_next[i] = __ldcg(o4 + i * kBM);
+  };
+  request(0);
+#pragma unroll 1
+  for (int r = 0; r < runs; ++r) {
+    const float m_run = m_next, l_run = l_next;
+    float4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = v_next[i];
+    if (r + 1 < runs) request(r + 1);
+    const float wgt = Ex2(m_run - mx);      // 0 for a run that saw no key of this row
+    den = fmaf(wgt, l_run, den);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[4 * i] = fmaf(wgt, v[i].x, acc[4 * i]);
+      acc[4 * i + 1] = fmaf(wgt, v[i].y, acc[4 * i + 1]);
+      acc[4 * i + 2] = fmaf(wgt, v[i].z, acc[4 * i + 2]);
+      acc[4 * i + 3] = fmaf(wgt, v[i].w, acc[4 * i + 3]);
+    }
+  }
+  const float inv = 1.0f / den;
+  half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + d0;
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = AsU32(__floats2half2_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv));
+  *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 // ------------------------------------------------------------------ host
@@ -665,8 +688,6 @@ struct DeviceState {
   // ingestion is not captured in a graph; a launch that needs more than it has synchronises the device once.)
   float* partials = nullptr;
   size_t partial_floats = 0;
-  int* tickets = nullptr;
-  size_t ticket_ints = 0;
 };
 DeviceState g_state[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
@@ -675,27 +696,28 @@ int g_split_blocks = 0;   // 0: chosen per launch (ChooseSplitBlocks); > 0: forc
 
 // Longest run of key blocks one CTA should take: a (tile, head) pair with more blocks is cut into equal runs.
 // The launch is replayed on the host the way the hardware runs it - CTAs start in grid order, each on the SM that
-// frees first - with costs measured on B200 (1.15 us per key block, 8 us of set-up and tear-down per CTA, 3 us
-// per run for the CTA that combines a pair's records; the model is within a few per cent of measured launch times
-// from 128 rows at context 32768 to 4096 rows at 20480), and the candidate with the shortest makespan wins. Cutting
+// frees first - with costs measured on B200 (1.15 us per key block, 8 us of set-up and tear-down per CTA, kPublishUs
+// for a run's record, kCombineUs once for the kernel that combines the records), and the candidate with the shortest
+// makespan wins. Cutting
 // only the LONGEST tiles often does best (2048 rows at context 8192: runs of at most 60 blocks turn 192 items in
 // two waves into 240 that level out, 136 -> 119 us); a prompt's last rows against tens of thousands of keys are
 // cut into a dozen runs each (292 -> 69 us). The choice depends on the chunk alone, so it is remembered across
 // the layers of a model.
 double SimulatedMakespan(int chunk_start, int chunk_len, int heads, int split_blocks, int sm_count, std::vector<double>& free_at) {
-  constexpr double kBlockUs = 1.15, kSetupUs = 8.0, kCombineUsPerRun = 3.0;
+  constexpr double kBlockUs = 1.15, kSetupUs = 8.0, kPublishUs = 1.5, kCombineUs = 4.0;
   const int64_t kv_len = static_cast<int64_t>(chunk_start) + chunk_len;
   const int n_tiles = (chunk_len + kBM - 1) / kBM;
   free_at.assign(sm_count, 0.0);                       // a min-heap of the times at which the SMs free up
   double end = 0.0;
+  bool any_cut = false;
   for (int t = n_tiles - 1; t >= 0; --t) {
     const int64_t last = std::min<int64_t>(static_cast<int64_t>(chunk_start) + static_cast<int64_t>(t + 1) * kBM, kv_len) - 1;
     const int nb = static_cast<int>(last / kBN) + 1;
     const int ns = (nb + split_blocks - 1) / split_blocks;
     for (int run = 0; run < ns; ++run) {
       const int blocks = (run + 1) * nb / ns - run * nb / ns;
-      // the run of a pair that starts last is taken to be the one that combines the records
-      const double cost = kSetupUs + blocks * kBlockUs + (ns > 1 && run == ns - 1 ? kCombineUsPerRun * ns : 0.0);
+      const double cost = kSetupUs + blocks * kBlockUs + (ns > 1 ? kPublishUs : 0.0);
+      any_cut |= ns > 1;
       for (int h = 0; h < heads; ++h) {
         std::pop_heap(free_at.begin(), free_at.end(), std::greater<double>());
         const double done = free_at.back() + cost;
@@ -705,7 +727,7 @@ double SimulatedMakespan(int chunk_start, int chunk_len, int heads, int split_bl
       }
     }
   }
-  return end;
+  return end + (any_cut ? kCombineUs : 0.0);
 }
 
 int ChooseSplitBlocks(int chunk_start, int chunk_len, int heads, int sm_count) {
@@ -839,7 +861,6 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   if (items > 65535) return Fail(RL_E_TOO_LARGE, "paged_prefill_attention: chunk too large (%lld work items per head)", static_cast<long long>(items));
   if (any_split) {
     const size_t need = static_cast<size_t>(num_q_heads) * static_cast<size_t>(items) * kPartialFloats;
-    const size_t need_tickets = static_cast<size_t>(num_q_heads) * n_tiles;
     std::lock_guard<std::mutex> lock(g_mutex);
     if (st->partial_floats < need) {
       cudaDeviceSynchronize();
@@ -850,22 +871,11 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
       if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_prefill_attention: %zu MB of scratch: %s", need * 4 >> 20, cudaGetErrorString(e));
       st->partial_floats = need;
     }
-    if (st->ticket_ints < need_tickets) {
-      cudaDeviceSynchronize();
-      if (st->tickets) cudaFree(st->tickets);
-      st->tickets = nullptr;
-      st->ticket_ints = 0;
-      cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&st->tickets), need_tickets * sizeof(int));
-      if (e == cudaSuccess) e = cudaMemset(st->tickets, 0, need_tickets * sizeof(int));
-      if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_prefill_attention: tickets: %s", cudaGetErrorString(e));
-      st->ticket_ints = need_tickets;
-    }
   }
   Params p;
   p.n_tiles = n_tiles;
   p.split_blocks = split_blocks;
   p.partials = st->partials;
-  p.tickets = st->tickets;
   p.out = static_cast<half*>(out);
   p.out_stride = out_row_stride;
   p.table_row = block_table_row;
@@ -878,9 +888,19 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
   p.error_flag = st->error_flag;
   const dim3 grid(num_q_heads, static_cast<unsigned>(items));
   PagedPrefillAttentionKernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, q_map, page_map);
-  return LaunchStatus("paged_prefill_attention");
+  rc = LaunchStatus("paged_prefill_attention");
+  if (rc != RL_OK || !any_split) return rc;
+  // Only the chunk's last tiles - the ones with more key blocks than the run length - were cut.
+  int cut_tiles = 0;
+  for (int t = n_tiles - 1; t >= 0; --t) {
+    const int64_t last = std::min<int64_t>(static_cast<int64_t>(chunk_start) + static_cast<int64_t>(t + 1) * kBM, kv_len) - 1;
+    if (static_cast<int>(last / kBN) + 1 <= split_blocks) break;
+    ++cut_tiles;
+  }
+  PrefillCombineKernel<<<dim3(num_q_heads, cut_tiles, kBM / kCombineRows), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, static_cast<int>(items));
+  return LaunchStatus("paged_prefill_attention (combine)");
 }
-
 extern "C" int rl_prefill_attention_health(int* flag_out) {
   using namespace rl;
   using namespace rl::pfa;

@@ -92,8 +92,8 @@ def test_scores_that_outgrow_the_running_reference_late_in_the_context(own):
 
 
 def test_long_contexts_cut_across_ctas_give_the_same_bits_every_time():
-    """A (tile, head) pair with more than 16 key blocks is cut into runs on different CTAs whose records are
-    combined by whichever arrives last, always in run order: two launches must agree bit for bit."""
+    """A (tile, head) pair with more key blocks than the run length is cut into runs on different CTAs whose
+    records a second kernel combines, always in run order: two launches must agree bit for bit."""
     chunk_start, chunk_len = 6000, 300
     case = make_case(chunk_start, chunk_len, 0xFB3)
     try:
