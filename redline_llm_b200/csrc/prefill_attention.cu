@@ -70,6 +70,7 @@ constexpr int kKeysPerThread = kBN / kRowSplit;        // scores of a block one 
 constexpr int kScoreChunks = kKeysPerThread / 16;      // in tensor-memory loads of 16 columns
 constexpr int kDimsPerThread = kHeadDim / kRowSplit;   // output dims one softmax thread owns at the end
 constexpr int kDimChunks = kDimsPerThread / 16;
+static_assert(kDimChunks == kScoreChunks, "the registers that held a block's scores take the output row at the end");
 constexpr int kPagesPerBlock = kBN / kKvBlock;
 constexpr int kRegionBytes = 128 * 128;  // [128 rows][64 halves], 128-byte swizzle
 constexpr int kTileBytes = 2 * kRegionBytes;   // two 64-wide halves
@@ -244,23 +245,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   const int head = blockIdx.x;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int kv_len = p.chunk_start + p.chunk_len;
-  int tile_q = 0, split = 0, nsplit = 1, tile_blocks = 1;
-  {
-    int item = blockIdx.y;
-    for (int t = p.n_tiles - 1; t >= 0; --t) {
-      const int nb = (min(p.chunk_start + (t + 1) * kBM, kv_len) - 1) / kBN + 1;
-      const int ns = (nb + p.split_blocks - 1) / p.split_blocks;
-      if (item < ns || t == 0) {
-        tile_q = t; split = item; nsplit = ns; tile_blocks = nb;
-        break;
-      }
-      item -= ns;
-    }
-  }
-  const int row0 = tile_q * kBM;
-  const int jb0 = split * tile_blocks / nsplit;
-  const int nblk = (split + 1) * tile_blocks / nsplit - jb0;          // blocks of THIS item, indexed 0 .. nblk - 1 below
 
+  // Barriers and tensor memory first: both take a while and need nothing of what follows.
   if (tid == 0) {
     MbarInit(bar_q, 1);
     for (int i = 0; i < 2; ++i) {
@@ -281,6 +267,62 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+
+  // Which item: every warp works it out for itself, 32 tiles at a time - lane i takes the i-th tile from the end,
+  // a shuffle scan sums the runs before it, a ballot finds the tile that holds the item. (One tile after the other,
+  // with its integer division, this took a microsecond of every CTA's life at 16 tiles.)
+  int tile_q = 0, split = 0, nsplit = 1, tile_blocks = 1;
+  {
+    const int item = blockIdx.y;
+    int before = 0;                       // runs of the tiles already passed
+    bool found = false;
+    for (int base = 0; base < p.n_tiles && !found; base += 32) {
+      const int t = p.n_tiles - 1 - base - lane;
+      const int nb = t >= 0 ? (min(p.chunk_start + (t + 1) * kBM, kv_len) - 1) / kBN + 1 : 0;
+      const int ns = t >= 0 ? (nb + p.split_blocks - 1) / p.split_blocks : 0;
+      int upto = ns;                      // inclusive scan over the lanes
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, upto, d);
+        if (lane >= d) upto += v;
+      }
+      const unsigned holds = __ballot_sync(0xffffffffu, t >= 0 && item < before + upto);
+      if (holds) {
+        const int src = __ffs(holds) - 1;
+        tile_q = __shfl_sync(0xffffffffu, t, src);
+        nsplit = __shfl_sync(0xffffffffu, ns, src);
+        tile_blocks = __shfl_sync(0xffffffffu, nb, src);
+        split = item - (before + __shfl_sync(0xffffffffu, upto - ns, src));
+        found = true;
+      }
+      before += __shfl_sync(0xffffffffu, upto, 31);
+    }
+    if (!found) {                         // an item past the last one: the launcher never asks for it
+      tile_q = 0;
+      tile_blocks = (min(p.chunk_start + kBM, kv_len) - 1) / kBN + 1;
+      nsplit = 1;
+      split = 0;
+    }
+  }
+  const int row0 = tile_q * kBM;
+  const int jb0 = split * tile_blocks / nsplit;
+  const int nblk = (split + 1) * tile_blocks / nsplit - jb0;          // blocks of THIS item, indexed 0 .. nblk - 1 below
+
+  // The loader's first table reads (lane l < 8 serves page l of a block) are under way before the CTA's barrier.
+  auto table_entry = [&](int j) {
+    const int page = (jb0 + j) * kPagesPerBlock + lane;
+    return (lane < kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
+  };
+  int blk = 0, blk_next = 0, blk_next2 = 0;
+  if (warp == kLoadWarp) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&page_map) : "memory");
+    }
+    blk = table_entry(0);
+    blk_next = table_entry(1);
+    blk_next2 = table_entry(2);
+  }
   TcFenceBefore();
   __syncthreads();
   TcFenceAfter();
@@ -299,15 +341,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     // ------------------------------------------------------------ loader: every TMA request
     // A block is 8 copies of 4 KiB for K and 8 for V, one per page, spread over the lanes. The block id of a page
     // serves K and V alike and is read from the table two blocks ahead of its use.
-    if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&q_map) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&page_map) : "memory");
-    }
     const uint64_t keep = L2PolicyEvictLast(), normal = L2PolicyEvictNormal();
-    auto table_entry = [&](int j) {   // lane l < 8 serves page l of the block
-      const int page = (jb0 + j) * kPagesPerBlock + lane;
-      return (lane < kPagesPerBlock && j < nblk && page < p.max_blocks) ? __ldg(p.table_row + page) : 0;   // past the table: the dummy block
-    };
     auto load_k = [&](int j, int block) {   // K block j into buffer j & 1, page l at 4 KiB * l
       const uint32_t base = s_k + (j & 1) * kTileBytes, bar = bar_k0 + 8 * (j & 1);
       if (lane == 0) MbarExpectTx(bar, kTileBytes);
@@ -329,7 +363,6 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     }
     // K runs one block ahead of V: K_{t+1}'s buffer is free as soon as Q.K_{t-1}^T has completed, long before
     // P_{t-2}.V_{t-2} - which V_t's buffer waits for - so no K request ever queues behind a V wait.
-    int blk = table_entry(0), blk_next = table_entry(1), blk_next2 = table_entry(2);
     load_k(0, blk);
     load_v(0, blk);
     if (nblk > 1) load_k(1, blk_next);
@@ -560,24 +593,35 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     for (int o = 0; o < kRowSplit; ++o) l_row += xsum[o * kBM + row];
     wait(bar_done, 0);
     TcFenceAfter();
-    const int out_row = row0 + row;
-    half* dst = p.out + static_cast<int64_t>(out_row) * p.out_stride + head * kHeadDim + hw * kDimsPerThread;
     if (nsplit == 1) {
-      // the whole key range was this CTA's: divide by the row's sum, round once, store
+      // The whole key range was this CTA's: divide by the row's sum, round once - and hand the tile to the warps
+      // row by row through shared memory (K buffer 0: every copy has landed, every product has completed), so that
+      // a store instruction writes two whole 256-byte rows instead of 16 bytes of each of 32 rows. 16-byte pieces
+      // of a row are permuted by the row number, which keeps both sides free of bank conflicts.
       const float inv = 1.0f / l_row;
+      uint8_t* stage = smem + kKOff;
+#pragma unroll
+      for (int c = 0; c < kDimChunks; ++c) TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, raw[c]);
+#pragma unroll
+      for (int c = 0; c < kDimChunks; ++c) TmemWaitLoads(raw[c]);
 #pragma unroll
       for (int c = 0; c < kDimChunks; ++c) {
-        uint32_t raw[16];
-        TmemLoad16(tmem_o + hw * kDimsPerThread + lane_addr + c * 16, raw);
-        TmemWaitLoads(raw);
-        if (ok && out_row < p.chunk_len) {
-          uint32_t w[8];
+        uint32_t w[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            w[i] = AsU32(__floats2half2_rn(__uint_as_float(raw[2 * i]) * inv, __uint_as_float(raw[2 * i + 1]) * inv));
-          *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-        }
+        for (int i = 0; i < 8; ++i)
+          w[i] = AsU32(__floats2half2_rn(__uint_as_float(raw[c][2 * i]) * inv, __uint_as_float(raw[c][2 * i + 1]) * inv));
+        const int piece = (hw * kDimsPerThread + c * 16) / 8;
+        *reinterpret_cast<uint4*>(stage + row * 256 + (((piece + 0) ^ (row & 15)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(stage + row * 256 + (((piece + 1) ^ (row & 15)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      SoftmaxBarrier();
+      constexpr int kRowsPerPass = kSoftmaxThreads / 32 * 2;
+#pragma unroll
+      for (int i = 0; i < kBM / kRowsPerPass; ++i) {
+        const int r = i * kRowsPerPass + warp * 2 + (lane >> 4), piece = lane & 15;
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((piece ^ (r & 15)) << 4));
+        if (ok && row0 + r < p.chunk_len)
+          *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(row0 + r) * p.out_stride + head * kHeadDim + piece * 8) = v;
       }
     } else {
       // One run of a tile's key blocks: leave (o unnormalised, reference, row sum) for the kernel that follows this
@@ -602,6 +646,7 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
   }
   TcFenceBefore();
   __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the combining kernel may be set up (it waits for this grid to complete)
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
@@ -611,13 +656,16 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 // reference - are combined in run order, so the result does not depend on which CTA ran when. One CTA per (head,
 // tile, 32 query rows); a warp takes 16 dims of those rows, one row per lane; every row of a cut pair is handled by
 // exactly one thread group, and pairs that one CTA held whole were stored by the main kernel and are left alone. Launched
-// behind the main kernel in the same stream, over the chunk's last tiles only (the cut ones). (As a dependent
-// launch that the main kernel releases when its CTAs start, it measured 4-6 us SLOWER on launches of 20-40 us.)
+// behind the main kernel in the same stream, over the chunk's last tiles only (the cut ones), as a dependent launch
+// that every main CTA releases as its last act: the CTAs of this kernel are then set up while the main grid drains
+// and wait (griddepcontrol.wait) until it has completed - 0.4-0.7 us on launches of 15-40 us. (Released when the
+// main CTAs START, it measured 4-6 us slower.)
 constexpr int kCombineThreads = 256;
 constexpr int kCombineRows = 32;
 static_assert(kCombineThreads / 32 * 16 == kHeadDim, "one warp per 16 dims");
 __global__ void __launch_bounds__(kCombineThreads)
 PrefillCombineKernel(const Params p, int items) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, tile = p.n_tiles - 1 - blockIdx.y;
   const int kv_len = p.chunk_start + p.chunk_len;
   int runs = 1, item0 = 0;   // the pair's runs and its first work item: the items of later tiles come first
@@ -897,8 +945,19 @@ extern "C" int rl_launch_paged_prefill_attention(void* out, int64_t out_row_stri
     if (static_cast<int>(last / kBN) + 1 <= split_blocks) break;
     ++cut_tiles;
   }
-  PrefillCombineKernel<<<dim3(num_q_heads, cut_tiles, kBM / kCombineRows), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      p, static_cast<int>(items));
+  // (a dependent launch whatever the process-wide switch says: the kernel begins with the wait for the stream's
+  // previous kernel, which is the one above)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_q_heads, cut_tiles, kBM / kCombineRows);
+  cfg.blockDim = dim3(kCombineThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, PrefillCombineKernel, p, static_cast<int>(items));
+  if (e != cudaSuccess) return Fail(static_cast<int>(e), "paged_prefill_attention (combine): %s", cudaGetErrorString(e));
   return LaunchStatus("paged_prefill_attention (combine)");
 }
 extern "C" int rl_prefill_attention_health(int* flag_out) {
