@@ -27,8 +27,9 @@
 //    the six query heads of a KV group and all query tiles re-read the same pages from L2.
 //  * S = Q.K^T: M = 128 query rows, N = 128 keys, K = 16 dims x 8, both operands K-major in shared memory,
 //    FP32 accumulator in tensor memory. Two S buffers (columns 0-127, 128-255): the product of
-//    block j+2 is issued as soon as the softmax of block j has released its buffer, so the tensor pipe runs
-//    under the softmax of block j+1.
+//    block j+2 is issued as soon as the softmax of block j has released its buffer - ahead of P_j.V_j, because
+//    the softmax warps wait for scores and never for the output - so the tensor pipe runs under the softmax of
+//    block j+1.
 //  * Softmax: warps 0-7, two threads per query row (keys 0-63 and 64-127 of the block; a warp may only touch
 //    its own quarter of the tensor-memory lanes). Each thread reads its half row of S from tensor memory once
 //    (tcgen05.ld 32x32b) and writes P = exp2(s * scale - reference) as FP16 pairs into tensor memory
@@ -424,14 +425,17 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
 #pragma unroll 1
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1, par = (j >> 1) & 1;
+      // Q.K_{j+2}^T FIRST: the softmax warps wait for scores, never for the output. (With P_j.V_j first, S_{j+1} became
+      // visible ~1700 cycles after P_{j-1} was reported - two groups of eight products and the latencies around
+      // them - while the softmax of block j had finished after ~1500 and stood waiting 220-350 cycles every block.)
       wait_all(bar_p0 + 8 * buf, par);                 // P_j written, S[buf] read out
-      wait_all(bar_v0 + 8 * buf, par);                 // V_j landed
       TcFenceAfter();
-      if (good) issue_pv(j);
       if (j + 2 < nblk) {
         wait_all(bar_k0 + 8 * buf, ((j + 2) >> 1) & 1);
         if (good) issue_qk(j + 2);
       }
+      wait_all(bar_v0 + 8 * buf, par);                 // V_j landed
+      if (good) issue_pv(j);
     }
     // One-shot barrier for the readers of the finished output.
     if (good) UmmaCommitElected(bar_done);
@@ -518,6 +522,9 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
       // always share one reference, so the result does not depend on when it moves; P stays below 2^16.
       float sum = 0.0f;
       bool settle = true;
+      // P_j goes where P_{j-2} was: that product must have completed. (Scores no longer imply it: Q.K_j^T was issued
+      // ahead of P_{j-2}.V_{j-2}.)
+      if (j >= 2) wait(bar_o0 + 8 * buf, ((j - 2) >> 1) & 1);
       if (j > 0) {
         sum = write_probabilities(m_ref);
         settle = PairAny(pair_bar, !(sum < kOverflowSum));
