@@ -159,11 +159,19 @@ def test_other_head_counts(own, q_heads, kv_heads):
     assert K.prefill_attention_health() == 0
 
 
-def test_output_stride_gap_is_untouched_and_inputs_are_read_only(own):
+@pytest.mark.parametrize("split", [0, 2])
+def test_output_stride_gap_and_rows_past_the_chunk_are_untouched(own, split):
+    """Whole pairs leave through the kernel's staged row stores, cut pairs (run length 2: two runs per pair) through
+    the combining kernel: neither may write the stride gap or a row past the chunk (the last tile has 22 of 128 rows)."""
     chunk_start, chunk_len = 200, 150
     case = make_case(chunk_start, chunk_len, 0xF77)
-    got = run_fused(case, chunk_start, chunk_len, q_stride=2048, out_stride=2048)
+    try:
+        K.set_prefill_attention_split_blocks(split)
+        got = run_fused(case, chunk_start, chunk_len, q_stride=2048, out_stride=2048)
+    finally:
+        K.set_prefill_attention_split_blocks(0)
     assert (got[:, 1536:] == 0x1234).all()
+    assert (got[chunk_len:, :] == 0x1234).all()
     ref = reference(own, case, chunk_start, chunk_len)
     assert np.abs(oracle.half_bits_to_f64(got[:chunk_len, :1536]) - ref).max() <= MAX_ABS + 2.0 ** -11
 
