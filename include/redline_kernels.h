@@ -168,8 +168,9 @@ int rl_launch_paged_attention_decode_static(void* out, int64_t out_row_stride, c
  * softmax with FP32 statistics, probabilities rounded to FP16 for P.V, FP32 accumulation, one FP16
  * rounding; out[row, head * 128 ..] is written for the chunk's rows only. head_dim must be 128,
  * num_q_heads a multiple of num_kv_heads (<= 8 KV heads); q, out and the pool slice 16-byte aligned, row
- * strides multiples of 8. One CTA per (128-row query tile, query head): TMA page tiles, tcgen05 for
- * Q.K^T and P.V with accumulators in tensor memory.
+ * strides multiples of 8. One CTA per (128-row query tile, query head) or per run of key blocks of such a
+ * pair: TMA page tiles, tcgen05 for Q.K^T and P.V with accumulators in tensor memory. The call enqueues one
+ * kernel, or two when pairs were cut into runs (the second combines the runs' records in run order).
  * No single launcher of the reference corresponds: this replaces its prefill composite LaunchKvGather ->
  * cuBLASLt scores -> LaunchPrefillSoftmax -> cuBLASLt P.V (src/core/model_executor.cpp:1219-1290), the
  * fused kernel its design notes name as the follow-up (docs/DESIGN.md:872-876 of the reference).
