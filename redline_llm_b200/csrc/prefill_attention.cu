@@ -753,11 +753,11 @@ int g_split_blocks = 0;   // 0: chosen per launch (ChooseSplitBlocks); > 0: forc
 // The launch is replayed on the host the way the hardware runs it - CTAs start in grid order, each on the SM that
 // frees first - with costs measured on B200 (1.15 us per key block, 8 us of set-up and tear-down per CTA, kPublishUs
 // for a run's record, kCombineUs once for the kernel that combines the records), and the candidate with the shortest
-// makespan wins. Cutting
-// only the LONGEST tiles often does best (2048 rows at context 8192: runs of at most 60 blocks turn 192 items in
-// two waves into 240 that level out, 136 -> 119 us); a prompt's last rows against tens of thousands of keys are
-// cut into a dozen runs each (292 -> 69 us). The choice depends on the chunk alone, so it is remembered across
-// the layers of a model.
+// makespan wins; on every chunk shape swept on B200 that choice was the best forced run length or level with it.
+// Cutting only the LONGEST tiles often does best (2048 rows at context 8192: runs of at most 60 blocks turn 192
+// items in two waves into 240 that level out, 120 -> 104 us); a prompt's last 128 rows against 32768 keys are cut
+// into a dozen runs each (263 -> 37 us). The choice depends on the chunk alone, so it is remembered across the
+// layers of a model.
 double SimulatedMakespan(int chunk_start, int chunk_len, int heads, int split_blocks, int sm_count, std::vector<double>& free_at) {
   constexpr double kBlockUs = 1.15, kSetupUs = 8.0, kPublishUs = 1.5, kCombineUs = 4.0;
   const int64_t kv_len = static_cast<int64_t>(chunk_start) + chunk_len;
