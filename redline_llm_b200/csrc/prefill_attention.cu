@@ -449,7 +449,8 @@ PagedPrefillAttentionKernel(const Params p, const __grid_constant__ CUtensorMap 
     float m_ref = -INFINITY, l = 0.0f;
     // This thread's 64 scores of a block are fetched from tensor memory once, all four loads in flight together,
     // and kept in registers for both passes. The fetch for block j+1 is made at the END of block j, before this
-    // thread reports P_j: that report then also says that S_{j+1}'s buffer may be overwritten.
+    // thread reports P_j: when all have reported P_j, both S buffers have been read out, and the MMA warp writes
+    // S_{j+2} over S_j (and, one report later, S_{j+3} over S_{j+1}).
     uint32_t raw[kScoreChunks][16];
     auto fetch_scores = [&](int j) {
       wait(bar_s0 + 8 * (j & 1), (j >> 1) & 1);
